@@ -1,0 +1,117 @@
+/*
+ * b200q -- C ABI of the B200 (sm_100a) quantized-linear kernels.
+ *
+ * This is the boundary a host runtime binds instead of the reference's Python /
+ * Triton operators.  Each entry point below names the reference routine it
+ * stands in for (paths are relative to the reference project).
+ *
+ * Conventions (modelled on the reference's native runtime ABI,
+ * include/linnet/runtime/runtime.h:35-67): every call returns an int32 status
+ * (B200Q_OK / B200Q_ERROR / B200Q_UNAVAILABLE); the message of the last failure
+ * on the calling thread is read with b200q_last_error().  All pointers are
+ * device pointers on the current CUDA device unless stated otherwise; tensors are
+ * dense and row-major; sizes are element counts.  `stream` is a cudaStream_t
+ * passed as void*.  Unless an entry says otherwise it allocates nothing, never
+ * synchronises and keeps no state between calls, so it can be recorded into a
+ * CUDA graph and called from several host threads on different streams.
+ */
+#ifndef B200Q_H
+#define B200Q_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200Q_ABI_VERSION 1
+
+enum { B200Q_OK = 0, B200Q_ERROR = 1, B200Q_UNAVAILABLE = 2 };
+
+/* Element types of activations, scales and outputs. */
+enum { B200Q_F32 = 0, B200Q_BF16 = 1, B200Q_F16 = 2 };
+
+int32_t b200q_abi_version(void);
+
+/* Message of the last call that failed on this host thread ("" if none). */
+const char* b200q_last_error(void);
+
+/* B200Q_OK when the current device can run these kernels (compute capability
+ * 10.x), B200Q_UNAVAILABLE otherwise. */
+int32_t b200q_device_ok(void);
+
+/* ---- quantize / pack ------------------------------------------------------
+ * Replaces linnet.quant.quantize_int4_groups + pack_int4_groups
+ * (python/linnet/src/linnet/quant.py:83-99, :242-248).  Bit-exact.
+ *   weight      [out, in], B200Q_F32 or B200Q_BF16 (bf16 is widened exactly)
+ *   packed      [out, in/group, group/2] bytes, even k in the low nibble
+ *   scale       [out, in/group] f32 (unrounded, as the reference returns it)
+ *   scale_store [out, in/group] in `store_dtype`, the value a checkpoint holds
+ *               (quant.py:205-209; weights.py:74-79 for bf16); may be NULL
+ *   zero        [out, in/group] u8 in 0..15
+ * `group` must be even and divide `in`. */
+int32_t b200q_quantize_int4_groups(const void* weight, int32_t weight_dtype,
+                                   int64_t out, int64_t in, int64_t group,
+                                   uint8_t* packed, float* scale,
+                                   void* scale_store, int32_t store_dtype,
+                                   uint8_t* zero, void* stream);
+
+/* Replaces linnet.quant.quantize_int8_groups (quant.py:102-120).  Bit-exact.
+ * The scale is rounded through `scale_dtype` before the levels are chosen;
+ * `group == in` gives one scale per output channel.
+ *   q     [out, in] i8 in -127..127      scale [out, in/group] f32 */
+int32_t b200q_quantize_int8_groups(const void* weight, int32_t weight_dtype,
+                                   int64_t out, int64_t in, int64_t group,
+                                   int32_t scale_dtype, int8_t* q, float* scale,
+                                   void* stream);
+
+/* ---- int4 group-quantized linear ------------------------------------------
+ * y[rows, out] = x[rows, in] . dequant(packed, scale, zero)^T, f32 accumulate.
+ *   x, y, scale in `dtype` (B200Q_BF16 or B200Q_F16); zero u8.
+ * Replaces the torch op linnet::int4_linear
+ * (python/linnet/src/linnet/torch/kernels.py:277-323), ATen's
+ * _weight_int4pack_mm as the generated source calls it for fewer than 8 rows
+ * (src/backend/torch_source.cpp:1556-1558) and the dequantize-then-cuBLAS route
+ * for more than 128 rows (:1563-1566).  Picks the kernel from `rows`. */
+int32_t b200q_int4_linear(const void* x, const uint8_t* packed, const void* scale,
+                          const uint8_t* zero, void* y, int64_t rows, int64_t in,
+                          int64_t out, int64_t group, int32_t dtype, void* stream);
+
+/* The decode kernel alone: rows <= 16, HBM-bound weight streaming. */
+int32_t b200q_int4_gemv(const void* x, const uint8_t* packed, const void* scale,
+                        const uint8_t* zero, void* y, int64_t rows, int64_t in,
+                        int64_t out, int64_t group, int32_t dtype, void* stream);
+
+/* The prefill kernel alone: TMA + tcgen05/TMEM dequant-GEMM (bf16, group a
+ * multiple of 64, in a multiple of 64, out a multiple of 16). */
+int32_t b200q_int4_gemm(const void* x, const uint8_t* packed, const void* scale,
+                        const uint8_t* zero, void* y, int64_t rows, int64_t in,
+                        int64_t out, int64_t group, int32_t dtype, void* stream);
+
+/* Replaces the generated `_int4_weight` / Triton `_int4_unpack`
+ * (src/backend/torch_source.cpp:1519-1551): the [out, in] weight in `dtype`,
+ * (q - zero) * scale computed in f32 and rounded once. */
+int32_t b200q_int4_dequantize(const uint8_t* packed, const void* scale,
+                              const uint8_t* zero, void* weight, int64_t out,
+                              int64_t in, int64_t group, int32_t dtype, void* stream);
+
+/* ---- int8 weight-only linear ----------------------------------------------
+ * y[rows, out] = x[rows, in] . (w * scale)^T, f32 accumulate.
+ *   w [out, in] i8; scale f32: [out] when group == 0, else [out, in/group].
+ * Replaces linnet::gemv8 (kernels.py:336-434, one row) and linnet::w8a16
+ * (kernels.py:437-592, 2..64 rows) for the int8 formats; more rows run the same
+ * tiles in passes until the tcgen05 path covers them. */
+int32_t b200q_int8_linear(const void* x, const int8_t* w, const float* scale,
+                          void* y, int64_t rows, int64_t in, int64_t out,
+                          int64_t group, int32_t dtype, void* stream);
+
+/* Replaces dequantize8 (kernels.py:595-666) for int8: weight[out, in] in `dtype`
+ * = round(f32(w) * scale). */
+int32_t b200q_int8_dequantize(const int8_t* w, const float* scale, void* weight,
+                              int64_t out, int64_t in, int64_t group, int32_t dtype,
+                              void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200Q_H */

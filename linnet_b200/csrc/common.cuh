@@ -1,0 +1,66 @@
+// Shared helpers of the b200q kernels: error reporting, argument checks and a
+// few PTX wrappers.  Device code here targets sm_100a only.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/b200q.h"
+
+namespace b200q {
+
+// Message of the last failure on this host thread (read by b200q_last_error).
+char* error_buffer();
+int32_t fail(const char* format, ...);
+int32_t unavailable(const char* format, ...);
+
+// After a launch: turns a launch error into a status + message.  Never
+// synchronises (an asynchronous fault shows at the caller's next sync).
+int32_t launched(const char* what);
+
+inline bool aligned(const void* p, size_t bytes) {
+    return (reinterpret_cast<uintptr_t>(p) % bytes) == 0;
+}
+
+// Shared argument validation of the int4 linear entry points.
+int32_t check_int4_args(const char* who, const void* x, const uint8_t* packed, const void* scale,
+                        const uint8_t* zero, void* y, int64_t rows, int64_t in, int64_t out,
+                        int64_t group, int32_t dtype);
+
+// Multiprocessor count of the current device (cached per device).
+int sm_count();
+
+#define B200Q_REQUIRE(cond, ...)                 \
+    do {                                         \
+        if (!(cond)) return ::b200q::fail(__VA_ARGS__); \
+    } while (0)
+
+// ---- device helpers -------------------------------------------------------
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+    // 128-bit read-only load that does not allocate in L1: weight bytes are
+    // used exactly once.
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t bits) {
+    // (a & mask) | bits in one LOP3.
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(bits));
+    return r;
+}
+
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) {
+    return __uint_as_float(bits16 << 16);
+}
+
+}  // namespace b200q

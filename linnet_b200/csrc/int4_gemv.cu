@@ -1,0 +1,455 @@
+// int4 group-quantized decode product for up to 16 activation rows.
+//
+//   y[m, n] = sum_k x[m, k] * (q[n, k] - zero[n, k/G]) * scale[n, k/G]
+//
+// Stands in for linnet::int4_linear (python/linnet/src/linnet/torch/kernels.py:212-323)
+// and for ATen's _weight_int4pack_mm as the generated source calls it
+// (src/backend/torch_source.cpp:1553-1562), on the reference's own weight layout:
+// packed [N, K/G, G/2] bytes (a row is K/2 contiguous bytes, even k in the low
+// nibble), scale [N, K/G] in the activation type, zero [N, K/G] u8.
+//
+// The kernel is HBM-bound: 0.5234 B per weight at G=128.  Design:
+//   * every thread streams 16-byte pieces of two weight rows (g and g+8 of a
+//     16-row tile) straight into registers with L1-bypassing loads, D k-blocks
+//     (128 inputs) in flight, so no shared-memory hop sits on the weight path;
+//   * nibbles become 16-bit floats with one LOP3 per pair ((w >> s) & 0x000F000F
+//     | magic gives magic + q for k and k + 4); (magic + q) - (magic + zero) is the
+//     exact integer q - zero, and one multiply by the scale rounds it once to the
+//     16-bit type: bit for bit the weight the reference multiplies by
+//     ((q - zero) * scale in f32, cast once).  The pair is already an A fragment of
+//     mma.m16n8k16; the activations are staged once per warp in shared memory,
+//     permuted to the matching (k, k + 4) pairing, as B fragments; accumulation is
+//     f32 in the tensor cores;
+//   * the warps of a block split K; a cluster of blocks may split it further, the
+//     partial sums meeting in (distributed) shared memory, so no global scratch
+//     and no atomics are used.
+#include "gemv_common.cuh"
+
+namespace b200q {
+namespace {
+
+struct GemvArgs {
+    const void* x;          // [M, K]
+    const uint8_t* packed;  // [N, K/2]
+    const void* scale;      // [N, K/G]
+    const uint8_t* zero;    // [N, K/G]
+    void* y;                // [M, N]
+    int M, K, N, G;
+    int kblocks;            // K / 128
+    int kb_per_cta;         // k-blocks each block of a cluster handles
+    int ksplit;             // blocks per cluster (along grid.y)
+};
+
+// How the zero point and scale reach the product.
+//   kExactBlock: groups that are multiples of 128.  Every pair of weights is
+//                dequantized exactly as the reference does ((q - zero) * scale, one
+//                rounding to the 16-bit type) with one HSUB2 + one HMUL2; the group's
+//                scale and zero point travel with the k-block's weight loads.
+//   kExactWord:  groups of 16, 32 or 64: the same arithmetic, the scale looked up per
+//                8 weights.
+//   kPost:       (tuning builds only) zero point and scale applied in f32 after each
+//                k-block's products; cheaper but not the reference's rounding.
+enum { kExactBlock = 0, kExactWord = 1, kPost = 2 };
+
+// One k-block of one 16-row tile as loaded: 16 bytes of rows g and g+8, and the
+// (scale bits | zero << 16) words of the group the k-block lies in.
+template <int NT>
+struct Stage {
+    uint4 q[NT][2];
+    uint32_t sz[NT][2];
+};
+
+template <typename T, int MODE, int MB, int NT, int W, int D>
+__global__ void __launch_bounds__(W * 32)
+int4_gemv_kernel(const GemvArgs a) {
+    using H = Half16<T>;
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+    const int g = lane / 4, t = lane % 4;
+    const int M = a.M, K = a.K, N = a.N, G = a.G;
+    const int groups = K / G;
+    const int tile_row = blockIdx.x * (16 * NT);
+    const int kb0 = min(int(blockIdx.y) * a.kb_per_cta, a.kblocks);
+    const int kb1 = min(kb0 + a.kb_per_cta, a.kblocks);
+    const int nkb = kb1 - kb0;  // k-blocks of this block (the last of a cluster may have fewer)
+    // This warp's contiguous share of them.  `cap` (from kb_per_cta) sizes the shared
+    // memory regions so that they sit at the same offsets in every block of a cluster.
+    const int cap = (a.kb_per_cta + W - 1) / W;
+    const int per_warp = (nkb + W - 1) / W;
+    const int wb0 = min(warp * per_warp, nkb), wb1 = min(wb0 + per_warp, nkb);
+    const int nw = wb1 - wb0;
+
+    // Shared memory, per warp: activations as B fragments [cap][4 words][M][4 lanes] x
+    // 16 B and (kPost) per-k-block activation sums [cap][16] f32; then the block's
+    // reduction buffer.
+    uint4* xs = reinterpret_cast<uint4*>(smem) + size_t(warp) * cap * 16 * M;
+    float* xsum_all = reinterpret_cast<float*>(reinterpret_cast<uint4*>(smem) + size_t(W) * cap * 16 * M);
+    float* xsum = xsum_all + size_t(warp) * cap * 16;
+    float* red = xsum_all + (MODE == kPost ? size_t(W) * cap * 16 : 0);  // [W][NT*16][MB*8]
+
+    const uint16_t* scale16 = static_cast<const uint16_t*>(a.scale);
+    const uint8_t* rowp[NT][2];
+    size_t srow[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = min(tile_row + nt * 16 + h * 8 + g, N - 1);  // ragged tile: clamp
+            rowp[nt][h] = a.packed + size_t(r) * (K / 2) + t * 16;
+            srow[nt][h] = size_t(r) * groups;
+        }
+
+    auto load_stage = [&](Stage<NT>& s, int kb_local) {
+        const int kb = kb0 + kb_local;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) s.q[nt][h] = ldg_stream(rowp[nt][h] + size_t(kb) * 64);
+        if (MODE != kExactWord) {
+            const int grp = (kb * 128) / G;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    s.sz[nt][h] = uint32_t(__ldg(scale16 + srow[nt][h] + grp)) |
+                                  (uint32_t(__ldg(a.zero + srow[nt][h] + grp)) << 16);
+        }
+    };
+
+    // 1. Put the first weight loads in flight before anything else.
+    Stage<NT> st[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d)
+        if (d < nw) load_stage(st[d], wb0 + d);
+
+    // 2. Each warp stages the activations of its own K range (no block barrier):
+    //    16-byte pieces, permuted to the (k, k+4) pairing of the A fragments.
+    {
+        const uint4* xg = static_cast<const uint4*>(a.x);
+        const int per_row = nw * 16;  // 16-byte pieces per activation row
+        const int pieces = M * per_row;
+        constexpr int U = 4;
+        for (int base = 0; base < pieces; base += 32 * U) {
+            uint4 raw[U];
+            int where[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int e = base + u * 32 + lane;
+                where[u] = -1;
+                raw[u] = make_uint4(0, 0, 0, 0);
+                if (e < pieces) {
+                    const int m = e / per_row, rem = e - m * per_row;
+                    const int j = rem / 16, c = rem % 16;
+                    raw[u] = __ldg(xg + (size_t(m) * K + size_t(kb0 + wb0 + j) * 128) / 8 + c);
+                    where[u] = ((j * 4 + (c % 4)) * M + m) * 4 + c / 4;
+                    if (MODE == kPost && c == 0) where[u] |= (j * 16 + m) << 16;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (MODE == kPost) {
+                    const uint4 r = raw[u];
+                    float sum = H::to_float(r.x & 0xFFFF) + H::to_float(r.x >> 16);
+                    sum += H::to_float(r.y & 0xFFFF); sum += H::to_float(r.y >> 16);
+                    sum += H::to_float(r.z & 0xFFFF); sum += H::to_float(r.z >> 16);
+                    sum += H::to_float(r.w & 0xFFFF); sum += H::to_float(r.w >> 16);
+#pragma unroll
+                    for (int d = 8; d >= 1; d >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, d);
+                    if (where[u] >= 0 && (lane % 16) == 0) xsum[where[u] >> 16] = sum;
+                }
+                if (where[u] >= 0) {
+                    uint4 out;
+                    out.x = __byte_perm(raw[u].x, raw[u].z, 0x5410);  // (x0, x4)
+                    out.y = __byte_perm(raw[u].x, raw[u].z, 0x7632);  // (x1, x5)
+                    out.z = __byte_perm(raw[u].y, raw[u].w, 0x5410);  // (x2, x6)
+                    out.w = __byte_perm(raw[u].y, raw[u].w, 0x7632);  // (x3, x7)
+                    xs[where[u] & 0xFFFF] = out;
+                }
+            }
+        }
+    }
+    __syncwarp();
+
+    // 3. Main loop over this warp's k-blocks.
+    float total[NT][MB][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) total[nt][mb][i] = 0.0f;
+
+    const uint32_t kMask = 0x000F000Fu;
+    for (int base = 0; base < nw; base += D) {
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            const int j = base + d;  // this warp's j-th k-block
+            if (j < nw) {
+                const Stage<NT> cur = st[d];
+                if (j + D < nw) load_stage(st[d], wb0 + j + D);
+                // B fragments of this k-block.
+                uint4 b[MB][4];
+#pragma unroll
+                for (int mb = 0; mb < MB; ++mb) {
+                    const int m = mb * 8 + g;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        b[mb][i] = m < M ? xs[(size_t(j * 4 + i) * M + m) * 4 + t]
+                                         : make_uint4(0, 0, 0, 0);
+                }
+                float2 xs2[MB];
+                if (MODE == kPost) {
+#pragma unroll
+                    for (int mb = 0; mb < MB; ++mb)
+                        xs2[mb] = *reinterpret_cast<const float2*>(xsum + j * 16 + mb * 8 + 2 * t);
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    float acc[MB][4];
+#pragma unroll
+                    for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) acc[mb][i] = 0.0f;
+                    const uint32_t w0[4] = {cur.q[nt][0].x, cur.q[nt][0].y, cur.q[nt][0].z, cur.q[nt][0].w};
+                    const uint32_t w1[4] = {cur.q[nt][1].x, cur.q[nt][1].y, cur.q[nt][1].z, cur.q[nt][1].w};
+                    uint32_t bias0 = 0, bias1 = 0, sc0 = 0, sc1 = 0;  // 16-bit pairs (x, x)
+                    if (MODE == kExactBlock) {
+                        bias0 = H::kMagic + (cur.sz[nt][0] >> 16) * 0x00010001u;
+                        bias1 = H::kMagic + (cur.sz[nt][1] >> 16) * 0x00010001u;
+                        sc0 = (cur.sz[nt][0] & 0xFFFFu) * 0x00010001u;
+                        sc1 = (cur.sz[nt][1] & 0xFFFFu) * 0x00010001u;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint32_t f0[4], f1[4];  // (k0,k4) (k1,k5) (k2,k6) (k3,k7) of rows g, g+8
+                        f0[0] = lop3_and_or(w0[i], kMask, H::kMagic);
+                        f0[1] = lop3_and_or(w0[i] >> 4, kMask, H::kMagic);
+                        f0[2] = lop3_and_or(w0[i] >> 8, kMask, H::kMagic);
+                        f0[3] = lop3_and_or(w0[i] >> 12, kMask, H::kMagic);
+                        f1[0] = lop3_and_or(w1[i], kMask, H::kMagic);
+                        f1[1] = lop3_and_or(w1[i] >> 4, kMask, H::kMagic);
+                        f1[2] = lop3_and_or(w1[i] >> 8, kMask, H::kMagic);
+                        f1[3] = lop3_and_or(w1[i] >> 12, kMask, H::kMagic);
+                        if (MODE == kExactWord) {
+                            const int grp = ((kb0 + wb0 + j) * 128 + t * 32 + i * 8) / G;
+                            sc0 = uint32_t(__ldg(scale16 + srow[nt][0] + grp)) * 0x00010001u;
+                            sc1 = uint32_t(__ldg(scale16 + srow[nt][1] + grp)) * 0x00010001u;
+                            bias0 = H::kMagic + uint32_t(__ldg(a.zero + srow[nt][0] + grp)) * 0x00010001u;
+                            bias1 = H::kMagic + uint32_t(__ldg(a.zero + srow[nt][1] + grp)) * 0x00010001u;
+                        }
+                        if (MODE != kPost) {
+#pragma unroll
+                            for (int p = 0; p < 4; ++p) {
+                                f0[p] = sub_mul<T>(f0[p], bias0, sc0);
+                                f1[p] = sub_mul<T>(f1[p], bias1, sc1);
+                            }
+                        }
+                        const uint32_t a_lo[4] = {f0[0], f1[0], f0[1], f1[1]};
+                        const uint32_t a_hi[4] = {f0[2], f1[2], f0[3], f1[3]};
+#pragma unroll
+                        for (int mb = 0; mb < MB; ++mb) {
+                            if (MODE == kPost) {
+                                H::mma(acc[mb], a_lo, b[mb][i].x, b[mb][i].y);
+                                H::mma(acc[mb], a_hi, b[mb][i].z, b[mb][i].w);
+                            } else {
+                                H::mma(total[nt][mb], a_lo, b[mb][i].x, b[mb][i].y);
+                                H::mma(total[nt][mb], a_hi, b[mb][i].z, b[mb][i].w);
+                            }
+                        }
+                    }
+                    if (MODE == kPost) {
+                        const float s0 = H::to_float(cur.sz[nt][0] & 0xFFFF);
+                        const float s1 = H::to_float(cur.sz[nt][1] & 0xFFFF);
+                        const float z0 = H::kBias + float(cur.sz[nt][0] >> 16);
+                        const float z1 = H::kBias + float(cur.sz[nt][1] >> 16);
+#pragma unroll
+                        for (int mb = 0; mb < MB; ++mb) {
+                            total[nt][mb][0] = fmaf(s0, fmaf(-z0, xs2[mb].x, acc[mb][0]), total[nt][mb][0]);
+                            total[nt][mb][1] = fmaf(s0, fmaf(-z0, xs2[mb].y, acc[mb][1]), total[nt][mb][1]);
+                            total[nt][mb][2] = fmaf(s1, fmaf(-z1, xs2[mb].x, acc[mb][2]), total[nt][mb][2]);
+                            total[nt][mb][3] = fmaf(s1, fmaf(-z1, xs2[mb].y, acc[mb][3]), total[nt][mb][3]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    // 4. Sum the warps' partial results, then the cluster's, and write y.
+    reduce_and_store<H, MB, NT, W>(total, red, a.ksplit, tile_row, M, N, static_cast<uint16_t*>(a.y));
+}
+
+// Any shape the tensor-core kernel does not take (K not a multiple of 128): one
+// warp per output column, f32 multiply-adds, up to 8 activation rows at a time.
+template <typename T>
+__global__ void int4_linear_simple_kernel(const GemvArgs a, int m0) {
+    using H = Half16<T>;
+    const int n = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+    if (n >= a.N) return;
+    const int rows = min(8, a.M - m0);
+    const uint16_t* x = static_cast<const uint16_t*>(a.x);
+    const uint16_t* scale16 = static_cast<const uint16_t*>(a.scale);
+    const int groups = a.K / a.G;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int byte = lane; byte < a.K / 2; byte += 32) {
+        const uint32_t v = a.packed[size_t(n) * (a.K / 2) + byte];
+        const int grp = (2 * byte) / a.G;
+        const float s = H::to_float(scale16[size_t(n) * groups + grp]);
+        const float z = float(a.zero[size_t(n) * groups + grp]);
+        // Round the weight once to the activation type, as the reference does.
+        const float w0 = H::to_float(H::from_float((float(v & 15) - z) * s));
+        const float w1 = H::to_float(H::from_float((float(v >> 4) - z) * s));
+        for (int r = 0; r < rows; ++r) {
+            const uint16_t* xr = x + size_t(m0 + r) * a.K + 2 * byte;
+            acc[r] = fmaf(H::to_float(xr[0]), w0, acc[r]);
+            acc[r] = fmaf(H::to_float(xr[1]), w1, acc[r]);
+        }
+    }
+    uint16_t* y = static_cast<uint16_t*>(a.y);
+    for (int r = 0; r < rows; ++r) {
+        float v = acc[r];
+        for (int d = 16; d >= 1; d >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, d);
+        if (lane == 0) y[size_t(m0 + r) * a.N + n] = H::from_float(v);
+    }
+}
+
+struct Plan {
+    int nt, w, d, ksplit;
+};
+
+// Launch geometry: enough warps in flight to cover HBM latency (about 24 per
+// multiprocessor), each with at least two k-blocks, and activations staged in
+// under ~48 KB of shared memory per block.
+Plan choose_plan(int M, int K, int N) {
+    const int sms = sm_count();
+    const int kblocks = K / 128;
+    Plan p{1, 4, 3, 1};
+    if (M > 8) p.nt = 2;
+    const int tiles = (N + 16 * p.nt - 1) / (16 * p.nt);
+    // Split K over a cluster while the grid is short of ~3 blocks per SM or the
+    // staged activations are too large.
+    while (p.ksplit < 8 && kblocks / (p.ksplit * 2) >= p.w &&
+           (tiles * p.ksplit < 3 * sms || size_t(kblocks / p.ksplit) * 256 * M > 48 * 1024))
+        p.ksplit *= 2;
+    return p;
+}
+
+template <typename T, int MODE, int MB, int NT, int W, int D>
+int32_t launch_gemv(const GemvArgs& args, int ksplit, cudaStream_t stream) {
+    GemvArgs a = args;
+    a.ksplit = ksplit;
+    a.kb_per_cta = (a.kblocks + ksplit - 1) / ksplit;
+    const int tiles = (a.N + 16 * NT - 1) / (16 * NT);
+    const size_t cap = (a.kb_per_cta + W - 1) / W;  // k-blocks per warp, at most
+    const size_t smem = size_t(W) * cap * 16 * a.M * 16 + (MODE == kPost ? size_t(W) * cap * 16 * 4 : 0) +
+                        size_t(W) * NT * 16 * MB * 8 * 4;
+    return launch_clustered("int4_gemv", int4_gemv_kernel<T, MODE, MB, NT, W, D>, a, tiles, ksplit,
+                            W * 32, smem, stream);
+}
+
+template <typename T, int MODE>
+int32_t dispatch_gemv(const GemvArgs& a, const Plan& p, cudaStream_t stream) {
+    if (a.M <= 8) return launch_gemv<T, MODE, 1, 1, 4, 2>(a, p.ksplit, stream);
+    return launch_gemv<T, MODE, 2, 2, 4, 2>(a, p.ksplit, stream);
+}
+
+template <typename T>
+int32_t run_gemv(GemvArgs a, int64_t rows, cudaStream_t stream) {
+    const size_t elt = 2;
+    const uint8_t* x = static_cast<const uint8_t*>(a.x);
+    uint8_t* y = static_cast<uint8_t*>(a.y);
+    for (int64_t m0 = 0; m0 < rows; m0 += 16) {
+        a.M = int(rows - m0 < 16 ? rows - m0 : 16);
+        a.x = x + size_t(m0) * a.K * elt;
+        a.y = y + size_t(m0) * a.N * elt;
+        int32_t status;
+        if (a.K % 128 == 0) {
+            const Plan p = choose_plan(a.M, a.K, a.N);
+            status = a.G % 128 == 0 ? dispatch_gemv<T, kExactBlock>(a, p, stream)
+                                    : dispatch_gemv<T, kExactWord>(a, p, stream);
+        } else {
+            for (int sub = 0; sub < a.M; sub += 8) {
+                int4_linear_simple_kernel<T><<<(a.N + 3) / 4, 128, 0, stream>>>(a, sub);
+            }
+            status = launched("int4_linear (general kernel)");
+        }
+        if (status != B200Q_OK) return status;
+    }
+    return B200Q_OK;
+}
+
+#ifdef B200Q_TUNING
+// Sweep hook (only in tuning builds): runs one named instantiation.
+#define B200Q_VARIANT(id, MB, NT, W, D)                                                   \
+    case id: return launch_gemv<__nv_bfloat16, kExactBlock, MB, NT, W, D>(a, ksplit, stream); \
+    case 100 + id: return launch_gemv<__nv_bfloat16, kPost, MB, NT, W, D>(a, ksplit, stream);
+int32_t tune_gemv(const GemvArgs& a, int variant, int ksplit, cudaStream_t stream) {
+    switch (variant) {
+        B200Q_VARIANT(0, 1, 1, 4, 3)
+        B200Q_VARIANT(1, 1, 1, 4, 2)
+        B200Q_VARIANT(2, 1, 1, 4, 4)
+        B200Q_VARIANT(3, 1, 1, 4, 6)
+        B200Q_VARIANT(4, 1, 1, 2, 4)
+        B200Q_VARIANT(5, 1, 1, 8, 2)
+        B200Q_VARIANT(6, 1, 1, 8, 4)
+        B200Q_VARIANT(7, 1, 2, 4, 2)
+        B200Q_VARIANT(8, 1, 2, 4, 3)
+        B200Q_VARIANT(9, 1, 2, 8, 2)
+        B200Q_VARIANT(10, 1, 1, 16, 2)
+        B200Q_VARIANT(11, 1, 4, 4, 2)
+        B200Q_VARIANT(20, 2, 1, 4, 2)
+        B200Q_VARIANT(21, 2, 1, 4, 3)
+        B200Q_VARIANT(22, 2, 2, 4, 2)
+        B200Q_VARIANT(23, 2, 2, 8, 2)
+        B200Q_VARIANT(24, 2, 1, 8, 2)
+        B200Q_VARIANT(25, 2, 4, 4, 1)
+        B200Q_VARIANT(26, 2, 2, 4, 1)
+        B200Q_VARIANT(27, 2, 1, 8, 4)
+    }
+    return fail("no such variant");
+}
+#endif
+
+}  // namespace
+
+int32_t check_int4_args(const char* who, const void* x, const uint8_t* packed, const void* scale,
+                        const uint8_t* zero, void* y, int64_t rows, int64_t in, int64_t out,
+                        int64_t group, int32_t dtype) {
+    B200Q_REQUIRE(dtype == B200Q_BF16 || dtype == B200Q_F16, "%s: activations are bf16 or f16", who);
+    B200Q_REQUIRE(rows >= 0 && in > 0 && out > 0, "%s: bad shape rows=%lld in=%lld out=%lld", who,
+                  (long long)rows, (long long)in, (long long)out);
+    B200Q_REQUIRE(group > 0 && group % 2 == 0 && in % group == 0,
+                  "%s: a group of %lld must be even and divide the %lld inputs", who, (long long)group,
+                  (long long)in);
+    B200Q_REQUIRE(in < (int64_t(1) << 30) && out < (int64_t(1) << 30), "%s: dimension too large", who);
+    if (rows == 0) return B200Q_OK;
+    B200Q_REQUIRE(x && packed && scale && zero && y, "%s: null tensor", who);
+    B200Q_REQUIRE(aligned(x, 16) && aligned(packed, 16) && aligned(scale, 2) && aligned(y, 2),
+                  "%s: x and packed must be 16-byte aligned", who);
+    return B200Q_OK;
+}
+
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" int32_t b200q_int4_gemv(const void* x, const uint8_t* packed, const void* scale,
+                                   const uint8_t* zero, void* y, int64_t rows, int64_t in,
+                                   int64_t out, int64_t group, int32_t dtype, void* stream) {
+    const int32_t ok = check_int4_args("int4_gemv", x, packed, scale, zero, y, rows, in, out, group, dtype);
+    if (ok != B200Q_OK || rows == 0) return ok;
+    GemvArgs a{x, packed, scale, zero, y, 0, int(in), int(out), int(group), int(in / 128), 0, 1};
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return dtype == B200Q_BF16 ? run_gemv<__nv_bfloat16>(a, rows, s) : run_gemv<__half>(a, rows, s);
+}
+
+#ifdef B200Q_TUNING
+extern "C" int32_t b200q_tune_int4_gemv(const void* x, const uint8_t* packed, const void* scale,
+                                        const uint8_t* zero, void* y, int64_t rows, int64_t in,
+                                        int64_t out, int64_t group, int32_t variant, int32_t ksplit,
+                                        void* stream) {
+    GemvArgs a{x, packed, scale, zero, y, int(rows), int(in), int(out), int(group), int(in / 128), 0, 1};
+    return tune_gemv(a, variant, ksplit, static_cast<cudaStream_t>(stream));
+}
+#endif

@@ -1,0 +1,426 @@
+// Group quantize / pack kernels, bit-exact with the reference's NumPy quantizer
+// (python/linnet/src/linnet/quant.py:83-120, :242-248).
+//
+// Everything is IEEE binary32 with explicit round-to-nearest intrinsics: a true
+// division (the reference divides; multiplying by a reciprocal flips codes), rintf
+// for NumPy's half-to-even `round`, and no fused multiply-add.  This translation
+// unit must be compiled with -fmad=false -prec-div=true -ftz=false.
+//
+// HBM-bound: 2 B read + 0.52 B written per weight for int4-g128 from bf16,
+// 2 B + 1 B for int8.  Two kernels:
+//   * team kernel  - groups of 16..256 elements: a team of group/8 lanes holds one
+//     group in registers (one 16-byte load per lane for bf16), reduces min/max with
+//     shuffles and writes 4 packed bytes (or 8 int8) per lane; four chunks are in
+//     flight per lane.
+//   * group kernel - any other group size: one warp or one 256-thread block per
+//     group; the group stays in registers (up to 8 chunks per thread) between the
+//     reduction and the rounding, the rest is read again (from L2).
+#include "common.cuh"
+
+namespace b200q {
+namespace {
+
+constexpr int kInt4 = 0;
+constexpr int kInt8 = 1;
+
+struct Chunk {  // eight consecutive weights as f32
+    float v[8];
+};
+
+__device__ __forceinline__ Chunk widen(const uint4& raw) {  // 8 x bf16
+    Chunk c;
+    c.v[0] = __uint_as_float(raw.x << 16);
+    c.v[1] = __uint_as_float(raw.x & 0xFFFF0000u);
+    c.v[2] = __uint_as_float(raw.y << 16);
+    c.v[3] = __uint_as_float(raw.y & 0xFFFF0000u);
+    c.v[4] = __uint_as_float(raw.z << 16);
+    c.v[5] = __uint_as_float(raw.z & 0xFFFF0000u);
+    c.v[6] = __uint_as_float(raw.w << 16);
+    c.v[7] = __uint_as_float(raw.w & 0xFFFF0000u);
+    return c;
+}
+
+template <typename In>
+struct Raw;  // the bytes of one chunk as loaded
+template <>
+struct Raw<__nv_bfloat16> {
+    uint4 a;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { a = ldg_stream(p); }
+    __device__ __forceinline__ Chunk get() const { return widen(a); }
+};
+template <>
+struct Raw<float> {
+    uint4 a, b;
+    __device__ __forceinline__ void load(const float* p) {
+        a = ldg_stream(p);
+        b = ldg_stream(p + 4);
+    }
+    __device__ __forceinline__ Chunk get() const {
+        Chunk c;
+        c.v[0] = __uint_as_float(a.x); c.v[1] = __uint_as_float(a.y);
+        c.v[2] = __uint_as_float(a.z); c.v[3] = __uint_as_float(a.w);
+        c.v[4] = __uint_as_float(b.x); c.v[5] = __uint_as_float(b.y);
+        c.v[6] = __uint_as_float(b.z); c.v[7] = __uint_as_float(b.w);
+        return c;
+    }
+};
+
+__device__ __forceinline__ float widen_one(const float* p) { return *p; }
+__device__ __forceinline__ float widen_one(const __nv_bfloat16* p) {
+    return __uint_as_float(uint32_t(*reinterpret_cast<const uint16_t*>(p)) << 16);
+}
+
+// ---- the reference's arithmetic ---------------------------------------------
+
+// quant.py:93-94: scale = (high - low) / 15, replaced by 1 where not positive.
+__device__ __forceinline__ float int4_step(float lo, float hi) {
+    float s = __fdiv_rn(__fsub_rn(hi, lo), 15.0f);
+    return s > 0.0f ? s : 1.0f;
+}
+// quant.py:95: zero = clip(round(-low / scale), 0, 15).
+__device__ __forceinline__ float int4_zero(float lo, float step) {
+    float z = rintf(__fdiv_rn(-lo, step));
+    return fminf(fmaxf(z, 0.0f), 15.0f);
+}
+// quant.py:96: q = clip(round(g / scale) + zero, 0, 15).
+__device__ __forceinline__ uint32_t int4_level(float v, float step, float zero) {
+    float q = __fadd_rn(rintf(__fdiv_rn(v, step)), zero);
+    return uint32_t(fminf(fmaxf(q, 0.0f), 15.0f));
+}
+// weights.py:74-79: bf16 bits, round to nearest even by the integer trick.
+__device__ __forceinline__ uint32_t bf16_bits_rne(float v) {
+    uint32_t bits = __float_as_uint(v);
+    return (bits + 0x7FFFu + ((bits >> 16) & 1u)) >> 16;
+}
+// quant.py:115-118: absmax / 127, 1 where not positive, through the stored dtype.
+__device__ __forceinline__ float int8_scale(float absmax, int scale_dtype) {
+    float s = __fdiv_rn(absmax, 127.0f);
+    s = s > 0.0f ? s : 1.0f;
+    if (scale_dtype == B200Q_BF16) return __uint_as_float(bf16_bits_rne(s) << 16);
+    if (scale_dtype == B200Q_F16) return __half2float(__float2half_rn(s));
+    return s;
+}
+// quant.py:119: q = clip(round(g / scale), -127, 127).
+__device__ __forceinline__ int int8_level(float v, float scale) {
+    float q = rintf(__fdiv_rn(v, scale));
+    return int(fminf(fmaxf(q, -127.0f), 127.0f));
+}
+
+__device__ __forceinline__ void store_scale(void* dst, int dtype, int64_t i, float s) {
+    if (dst == nullptr) return;
+    if (dtype == B200Q_BF16) {
+        reinterpret_cast<uint16_t*>(dst)[i] = uint16_t(bf16_bits_rne(s));
+    } else if (dtype == B200Q_F16) {
+        reinterpret_cast<__half*>(dst)[i] = __float2half_rn(s);
+    } else {
+        reinterpret_cast<float*>(dst)[i] = s;
+    }
+}
+
+__device__ __forceinline__ uint32_t pack8_int4(const Chunk& c, float step, float zero) {
+    uint32_t word = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) word |= int4_level(c.v[j], step, zero) << (4 * j);
+    return word;  // little endian: byte j/2 holds element j (even) low, j+1 high
+}
+
+__device__ __forceinline__ uint2 pack8_int8(const Chunk& c, float scale) {
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        lo |= (uint32_t(int8_level(c.v[j], scale)) & 0xFFu) << (8 * j);
+        hi |= (uint32_t(int8_level(c.v[4 + j], scale)) & 0xFFu) << (8 * j);
+    }
+    return make_uint2(lo, hi);
+}
+
+struct Outputs {
+    uint8_t* packed;    // int4: [groups, G/2] bytes; int8: [groups, G] bytes
+    float* scale;       // [groups]
+    void* scale_store;  // int4 only, may be null
+    int store_dtype;    // int4: dtype of scale_store; int8: dtype the scale is rounded through
+    uint8_t* zero;      // int4 only
+};
+
+// ---- team kernel ------------------------------------------------------------
+// T lanes per group, one 8-element chunk per lane, U chunks in flight per lane.
+template <int MODE, int T, typename In, int U>
+__global__ void __launch_bounds__(256)
+quantize_team_kernel(const In* __restrict__ w, int64_t chunks, Outputs o) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    const int64_t first = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    const bool leader = (threadIdx.x % T) == 0;
+    for (int64_t base = first; base - threadIdx.x % 32 < chunks; base += U * stride) {
+        Raw<In> raw[U];
+        bool live[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t c = base + u * stride;
+            live[u] = c < chunks;  // uniform over a team: chunks % T == 0
+            if (live[u]) raw[u].load(w + c * 8);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t c = base + u * stride;
+            Chunk v;
+            if (live[u]) {
+                v = raw[u].get();
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v.v[j] = 0.0f;
+            }
+            if (MODE == kInt4) {
+                float lo = v.v[0], hi = v.v[0];
+#pragma unroll
+                for (int j = 1; j < 8; ++j) {
+                    lo = fminf(lo, v.v[j]);
+                    hi = fmaxf(hi, v.v[j]);
+                }
+#pragma unroll
+                for (int d = T / 2; d >= 1; d >>= 1) {
+                    lo = fminf(lo, __shfl_xor_sync(0xFFFFFFFFu, lo, d));
+                    hi = fmaxf(hi, __shfl_xor_sync(0xFFFFFFFFu, hi, d));
+                }
+                if (live[u]) {
+                    const float step = int4_step(lo, hi);
+                    const float zero = int4_zero(lo, step);
+                    reinterpret_cast<uint32_t*>(o.packed)[c] = pack8_int4(v, step, zero);
+                    if (leader) {
+                        const int64_t g = c / T;
+                        o.scale[g] = step;
+                        o.zero[g] = uint8_t(zero);
+                        store_scale(o.scale_store, o.store_dtype, g, step);
+                    }
+                }
+            } else {
+                float top = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) top = fmaxf(top, fabsf(v.v[j]));
+#pragma unroll
+                for (int d = T / 2; d >= 1; d >>= 1)
+                    top = fmaxf(top, __shfl_xor_sync(0xFFFFFFFFu, top, d));
+                if (live[u]) {
+                    const float scale = int8_scale(top, o.store_dtype);
+                    reinterpret_cast<uint2*>(o.packed)[c] = pack8_int8(v, scale);
+                    if (leader) o.scale[c / T] = scale;
+                }
+            }
+        }
+    }
+}
+
+// ---- group kernel -----------------------------------------------------------
+// THREADS == 32: one warp per group (blocks of 4 warps); otherwise one block per
+// group.  VEC: the group is a whole number of aligned 8-element chunks.
+template <int THREADS>
+__device__ __forceinline__ float reduce_max(float v, float* scratch) {
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, d));
+    if (THREADS > 32) {
+        const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+        __syncthreads();  // scratch may still be read from the previous use
+        if (lane == 0) scratch[warp] = v;
+        __syncthreads();
+        v = scratch[0];
+#pragma unroll
+        for (int i = 1; i < THREADS / 32; ++i) v = fmaxf(v, scratch[i]);
+    }
+    return v;
+}
+
+template <int MODE, int THREADS, typename In, bool VEC>
+__global__ void __launch_bounds__(THREADS == 32 ? 128 : THREADS)
+quantize_group_kernel(const In* __restrict__ w, int64_t groups, int64_t G, Outputs o) {
+    constexpr int CACHED = 8;
+    __shared__ float scratch[32];
+    const int lane = THREADS == 32 ? threadIdx.x % 32 : threadIdx.x;
+    const int64_t first = THREADS == 32 ? int64_t(blockIdx.x) * 4 + threadIdx.x / 32 : blockIdx.x;
+    const int64_t step_groups = THREADS == 32 ? int64_t(gridDim.x) * 4 : gridDim.x;
+    for (int64_t g = first; g < groups; g += step_groups) {
+        const In* src = w + g * G;
+        float lo = __int_as_float(0x7F800000), hi = __int_as_float(0xFF800000), top = 0.0f;
+        Raw<In> cache[CACHED];
+        const int64_t nchunks = G / 8;
+        if (VEC) {
+#pragma unroll
+            for (int i = 0; i < CACHED; ++i) {
+                const int64_t c = lane + int64_t(i) * THREADS;
+                if (c < nchunks) cache[i].load(src + c * 8);
+            }
+#pragma unroll
+            for (int i = 0; i < CACHED; ++i) {
+                const int64_t c = lane + int64_t(i) * THREADS;
+                if (c < nchunks) {
+                    const Chunk v = cache[i].get();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        lo = fminf(lo, v.v[j]);
+                        hi = fmaxf(hi, v.v[j]);
+                        top = fmaxf(top, fabsf(v.v[j]));
+                    }
+                }
+            }
+            for (int64_t c = lane + int64_t(CACHED) * THREADS; c < nchunks; c += THREADS) {
+                Raw<In> r;
+                r.load(src + c * 8);
+                const Chunk v = r.get();
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    lo = fminf(lo, v.v[j]);
+                    hi = fmaxf(hi, v.v[j]);
+                    top = fmaxf(top, fabsf(v.v[j]));
+                }
+            }
+        } else {
+            for (int64_t e = lane; e < G; e += THREADS) {
+                const float v = widen_one(src + e);
+                lo = fminf(lo, v);
+                hi = fmaxf(hi, v);
+                top = fmaxf(top, fabsf(v));
+            }
+        }
+        if (MODE == kInt4) {
+            lo = -reduce_max<THREADS>(-lo, scratch);
+            hi = reduce_max<THREADS>(hi, scratch);
+            const float step = int4_step(lo, hi);
+            const float zero = int4_zero(lo, step);
+            if (lane == 0) {
+                o.scale[g] = step;
+                o.zero[g] = uint8_t(zero);
+                store_scale(o.scale_store, o.store_dtype, g, step);
+            }
+            uint8_t* dst = o.packed + g * (G / 2);
+            if (VEC) {
+#pragma unroll
+                for (int i = 0; i < CACHED; ++i) {
+                    const int64_t c = lane + int64_t(i) * THREADS;
+                    if (c < nchunks)
+                        reinterpret_cast<uint32_t*>(dst)[c] = pack8_int4(cache[i].get(), step, zero);
+                }
+                for (int64_t c = lane + int64_t(CACHED) * THREADS; c < nchunks; c += THREADS) {
+                    Raw<In> r;
+                    r.load(src + c * 8);
+                    reinterpret_cast<uint32_t*>(dst)[c] = pack8_int4(r.get(), step, zero);
+                }
+            } else {
+                for (int64_t b = lane; b < G / 2; b += THREADS) {
+                    const uint32_t even = int4_level(widen_one(src + 2 * b), step, zero);
+                    const uint32_t odd = int4_level(widen_one(src + 2 * b + 1), step, zero);
+                    dst[b] = uint8_t(even | (odd << 4));
+                }
+            }
+        } else {
+            top = reduce_max<THREADS>(top, scratch);
+            const float scale = int8_scale(top, o.store_dtype);
+            if (lane == 0) o.scale[g] = scale;
+            uint8_t* dst = o.packed + g * G;
+            if (VEC) {
+#pragma unroll
+                for (int i = 0; i < CACHED; ++i) {
+                    const int64_t c = lane + int64_t(i) * THREADS;
+                    if (c < nchunks)
+                        reinterpret_cast<uint2*>(dst)[c] = pack8_int8(cache[i].get(), scale);
+                }
+                for (int64_t c = lane + int64_t(CACHED) * THREADS; c < nchunks; c += THREADS) {
+                    Raw<In> r;
+                    r.load(src + c * 8);
+                    reinterpret_cast<uint2*>(dst)[c] = pack8_int8(r.get(), scale);
+                }
+            } else {
+                for (int64_t e = lane; e < G; e += THREADS)
+                    dst[e] = uint8_t(int8_level(widen_one(src + e), scale));
+            }
+        }
+    }
+}
+
+template <int MODE, typename In>
+int32_t launch_quantize(const In* w, int64_t out, int64_t in, int64_t G, Outputs o,
+                        cudaStream_t stream) {
+    const int64_t total = out * in;
+    if (total == 0) return B200Q_OK;
+    const int64_t groups = total / G;
+    const bool vec = (G % 8 == 0) && aligned(w, 16) &&
+                     aligned(o.packed, MODE == kInt4 ? 4 : 8);
+    const int sms = sm_count();
+    if (vec && (G == 16 || G == 32 || G == 64 || G == 128 || G == 256)) {
+        constexpr int U = 4;
+        const int64_t chunks = total / 8;
+        int64_t blocks = (chunks + 256 * U - 1) / (256 * U);
+        if (blocks > (int64_t(1) << 30)) blocks = int64_t(1) << 30;
+        const dim3 grid{unsigned(blocks)};
+        switch (G) {
+            case 16: quantize_team_kernel<MODE, 2, In, U><<<grid, 256, 0, stream>>>(w, chunks, o); break;
+            case 32: quantize_team_kernel<MODE, 4, In, U><<<grid, 256, 0, stream>>>(w, chunks, o); break;
+            case 64: quantize_team_kernel<MODE, 8, In, U><<<grid, 256, 0, stream>>>(w, chunks, o); break;
+            case 128: quantize_team_kernel<MODE, 16, In, U><<<grid, 256, 0, stream>>>(w, chunks, o); break;
+            default: quantize_team_kernel<MODE, 32, In, U><<<grid, 256, 0, stream>>>(w, chunks, o); break;
+        }
+        return launched("quantize (team kernel)");
+    }
+    if (G < 2048) {
+        int64_t blocks = (groups + 3) / 4;
+        if (blocks > int64_t(sms) * 64) blocks = int64_t(sms) * 64;
+        if (vec)
+            quantize_group_kernel<MODE, 32, In, true><<<unsigned(blocks), 128, 0, stream>>>(w, groups, G, o);
+        else
+            quantize_group_kernel<MODE, 32, In, false><<<unsigned(blocks), 128, 0, stream>>>(w, groups, G, o);
+    } else {
+        int64_t blocks = groups;
+        if (blocks > int64_t(sms) * 32) blocks = int64_t(sms) * 32;
+        if (vec)
+            quantize_group_kernel<MODE, 256, In, true><<<unsigned(blocks), 256, 0, stream>>>(w, groups, G, o);
+        else
+            quantize_group_kernel<MODE, 256, In, false><<<unsigned(blocks), 256, 0, stream>>>(w, groups, G, o);
+    }
+    return launched("quantize (group kernel)");
+}
+
+}  // namespace
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" int32_t b200q_quantize_int4_groups(const void* weight, int32_t weight_dtype,
+                                              int64_t out, int64_t in, int64_t group,
+                                              uint8_t* packed, float* scale, void* scale_store,
+                                              int32_t store_dtype, uint8_t* zero, void* stream) {
+    B200Q_REQUIRE(out >= 0 && in >= 0, "quantize_int4_groups: a linear weight is [Out, In]; got [%lld, %lld]",
+                  (long long)out, (long long)in);
+    B200Q_REQUIRE(group > 0 && group % 2 == 0 && in % group == 0,
+                  "quantize_int4_groups: groups of %lld must be even and divide the %lld inputs",
+                  (long long)group, (long long)in);
+    B200Q_REQUIRE(weight_dtype == B200Q_F32 || weight_dtype == B200Q_BF16,
+                  "quantize_int4_groups: weights are f32 or bf16");
+    B200Q_REQUIRE(store_dtype == B200Q_F32 || store_dtype == B200Q_BF16 || store_dtype == B200Q_F16,
+                  "quantize_int4_groups: scales are stored as bf16, f16, or f32");
+    if (out * in == 0) return B200Q_OK;
+    B200Q_REQUIRE(weight && packed && scale && zero, "quantize_int4_groups: null tensor");
+    Outputs o{packed, scale, scale_store, store_dtype, zero};
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (weight_dtype == B200Q_BF16)
+        return launch_quantize<kInt4>(static_cast<const __nv_bfloat16*>(weight), out, in, group, o, s);
+    return launch_quantize<kInt4>(static_cast<const float*>(weight), out, in, group, o, s);
+}
+
+extern "C" int32_t b200q_quantize_int8_groups(const void* weight, int32_t weight_dtype,
+                                              int64_t out, int64_t in, int64_t group,
+                                              int32_t scale_dtype, int8_t* q, float* scale,
+                                              void* stream) {
+    B200Q_REQUIRE(out >= 0 && in >= 0, "quantize_int8_groups: a linear weight is [Out, In]; got [%lld, %lld]",
+                  (long long)out, (long long)in);
+    B200Q_REQUIRE(group > 0 && in % group == 0,
+                  "quantize_int8_groups: groups of %lld must divide the %lld inputs",
+                  (long long)group, (long long)in);
+    B200Q_REQUIRE(weight_dtype == B200Q_F32 || weight_dtype == B200Q_BF16,
+                  "quantize_int8_groups: weights are f32 or bf16");
+    B200Q_REQUIRE(scale_dtype == B200Q_F32 || scale_dtype == B200Q_BF16 || scale_dtype == B200Q_F16,
+                  "quantize_int8_groups: scales are stored as bf16, f16, or f32");
+    if (out * in == 0) return B200Q_OK;
+    B200Q_REQUIRE(weight && q && scale, "quantize_int8_groups: null tensor");
+    Outputs o{reinterpret_cast<uint8_t*>(q), scale, nullptr, scale_dtype, nullptr};
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (weight_dtype == B200Q_BF16)
+        return launch_quantize<kInt8>(static_cast<const __nv_bfloat16*>(weight), out, in, group, o, s);
+    return launch_quantize<kInt8>(static_cast<const float*>(weight), out, in, group, o, s);
+}

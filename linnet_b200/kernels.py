@@ -1,0 +1,220 @@
+"""The torch operators of the quantized-linear path, backed by sm_100a CUDA kernels.
+
+Same names, arguments and results as the reference's Triton operators
+(python/linnet/src/linnet/torch/kernels.py): `int4_linear` (`linnet::int4_linear`,
+:277-323), `gemv8` (`linnet::gemv8`, :375-434), `w8a16` (`linnet::w8a16`, :526-592)
+and `dequantize8` (:619-666).  Each is a `torch.library` custom op with a fake
+implementation, so it is opaque to `torch.compile` and recordable into a CUDA graph;
+outside `torch.compile` the kernel is launched directly (the reference does the same
+to keep the host cost of a decoding step low, kernels.py:43-55).
+
+All launches go to PyTorch's current stream, never synchronise and never mutate
+their arguments.  There is no fallback: tensors must live on a B200.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+_CODES = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16, torch.float32: _lib.F32}
+
+
+def _code(dtype: torch.dtype, who: str) -> int:
+    if dtype not in (torch.bfloat16, torch.float16):
+        raise ValueError(f"{who}: activations are bf16 or f16, not {dtype}")
+    return _CODES[dtype]
+
+
+def _on_gpu(who: str, *tensors: torch.Tensor) -> torch.device:
+    device = tensors[0].device
+    for t in tensors:
+        if not t.is_cuda or t.device != device:
+            raise RuntimeError(
+                f"{who}: every tensor must be on one CUDA device (there is no CPU path in "
+                f"this build); got {[str(t.device) for t in tensors]}")
+    return device
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+class _Device:
+    """Makes `device` current for the launch when it is not already."""
+
+    def __init__(self, device: torch.device) -> None:
+        self.guard = None if device.index == torch.cuda.current_device() else torch.cuda.device(device)
+
+    def __enter__(self) -> None:
+        if self.guard is not None:
+            self.guard.__enter__()
+
+    def __exit__(self, *exc: object) -> None:
+        if self.guard is not None:
+            self.guard.__exit__(*exc)
+
+
+# ---- int4 ----------------------------------------------------------------------
+
+
+def _int4_linear(x: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor,
+                 zero: torch.Tensor) -> torch.Tensor:
+    rows, depth = x.shape
+    width, groups, half = packed.shape
+    group = 2 * half
+    block_k = min(group, 128)
+    if block_k < 16 or group % block_k or block_k & (block_k - 1):
+        # The reference's own limit and message (kernels.py:292-294).
+        raise ValueError(f"int4_linear: a group of {group} is not 16, 32, 64, or a multiple of 128")
+    if depth != groups * group:
+        raise ValueError(f"int4_linear: x has {depth} inputs, the weight {groups * group}")
+    if scale.dtype != x.dtype:
+        raise ValueError(f"int4_linear: scales are {scale.dtype}, activations {x.dtype}")
+    if packed.dtype != torch.uint8 or zero.dtype != torch.uint8:
+        raise ValueError("int4_linear: packed weights and zero points are uint8")
+    device = _on_gpu("int4_linear", x, packed, scale, zero)
+    x, packed, scale, zero = x.contiguous(), packed.contiguous(), scale.contiguous(), zero.contiguous()
+    y = torch.empty(rows, width, dtype=x.dtype, device=device)
+    with _Device(device):
+        _lib.check(_lib.load().b200q_int4_linear(
+            x.data_ptr(), packed.data_ptr(), scale.data_ptr(), zero.data_ptr(), y.data_ptr(),
+            rows, depth, width, group, _code(x.dtype, "int4_linear"), _stream(device)))
+    return y
+
+
+@torch.library.custom_op("linnet::int4_linear", mutates_args=(), device_types="cuda")
+def _int4_linear_op(x: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor,
+                    zero: torch.Tensor) -> torch.Tensor:
+    return _int4_linear(x, packed, scale, zero)
+
+
+@_int4_linear_op.register_fake
+def _(x, packed, scale, zero):
+    return x.new_empty(x.shape[0], packed.shape[0])
+
+
+def int4_linear(x: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor,
+                zero: torch.Tensor) -> torch.Tensor:
+    """`F.linear(x, W)` for `x` [rows, In] (bf16 or f16) and the group-wise 4-bit weight
+    of `std.quant::linear_int4_groups`: `packed` [Out, Groups, Group/2] u8 (even value
+    low), `scale` and `zero` [Out, Groups].  Any row count: up to 16 rows stream the
+    weight once at HBM speed, more go through the tensor-memory GEMM."""
+    if torch.compiler.is_compiling():
+        return _int4_linear_op(x, packed, scale, zero)
+    return _int4_linear(x, packed, scale, zero)
+
+
+def int4_dequantize(packed: torch.Tensor, scale: torch.Tensor, zero: torch.Tensor) -> torch.Tensor:
+    """The [Out, In] weight in `scale`'s dtype, `(q - zero) * scale` rounded once: what
+    the generated `_int4_weight` computes (src/backend/torch_source.cpp:1537-1551)."""
+    width, groups, half = packed.shape
+    device = _on_gpu("int4_dequantize", packed, scale, zero)
+    packed, scale, zero = packed.contiguous(), scale.contiguous(), zero.contiguous()
+    out = torch.empty(width, groups * 2 * half, dtype=scale.dtype, device=device)
+    with _Device(device):
+        _lib.check(_lib.load().b200q_int4_dequantize(
+            packed.data_ptr(), scale.data_ptr(), zero.data_ptr(), out.data_ptr(), width,
+            groups * 2 * half, 2 * half, _code(scale.dtype, "int4_dequantize"), _stream(device)))
+    return out
+
+
+# ---- int8 ----------------------------------------------------------------------
+
+
+def _no_fp8(who: str, fp8: bool) -> None:
+    if fp8:
+        raise NotImplementedError(f"{who}: FP8 weights are outside this build (int8 only)")
+
+
+def _eight_bit(who: str, x: torch.Tensor, weight: torch.Tensor, scale: torch.Tensor, fp8: bool,
+               group: int, row_block: int) -> torch.Tensor:
+    _no_fp8(who, fp8)
+    if row_block != 1:
+        raise NotImplementedError(f"{who}: block scales (row_block {row_block}) are an FP8 format")
+    if weight.dtype != torch.int8:
+        raise ValueError(f"{who}: int8 weights expected, got {weight.dtype}")
+    rows, depth = x.shape
+    width = weight.shape[0]
+    if weight.shape[1] != depth:
+        raise ValueError(f"{who}: x has {depth} inputs, the weight {weight.shape[1]}")
+    device = _on_gpu(who, x, weight, scale)
+    x, weight = x.contiguous(), weight.contiguous()
+    scale = scale.float().contiguous()
+    y = torch.empty(rows, width, dtype=x.dtype, device=device)
+    with _Device(device):
+        _lib.check(_lib.load().b200q_int8_linear(
+            x.data_ptr(), weight.data_ptr(), scale.data_ptr(), y.data_ptr(), rows, depth, width,
+            group, _code(x.dtype, who), _stream(device)))
+    return y
+
+
+@torch.library.custom_op("linnet::gemv8", mutates_args=(), device_types="cuda")
+def _gemv8_op(x: torch.Tensor, weight: torch.Tensor, scale: torch.Tensor, fp8: bool, group: int,
+              row_block: int) -> torch.Tensor:
+    return _eight_bit("gemv8", x, weight, scale, fp8, group, row_block)
+
+
+@_gemv8_op.register_fake
+def _(x, weight, scale, fp8, group, row_block):
+    return x.new_empty(x.shape[0], weight.shape[0])
+
+
+@torch.library.custom_op("linnet::w8a16", mutates_args=(), device_types="cuda")
+def _w8a16_op(x: torch.Tensor, weight: torch.Tensor, scale: torch.Tensor, fp8: bool, group: int,
+              row_block: int) -> torch.Tensor:
+    return _eight_bit("w8a16", x, weight, scale, fp8, group, row_block)
+
+
+@_w8a16_op.register_fake
+def _(x, weight, scale, fp8, group, row_block):
+    return x.new_empty(x.shape[0], weight.shape[0])
+
+
+def gemv8(x: torch.Tensor, weight: torch.Tensor, scale: torch.Tensor, fp8: bool, group: int,
+          row_block: int) -> torch.Tensor:
+    """`F.linear(x, W)` for one row `x` [1, In] and int8 weights [Out, In] times `scale`:
+    one a row ([Out]) when `group` is 0, else [Out, In/group]."""
+    if torch.compiler.is_compiling():
+        return _gemv8_op(x, weight, scale, fp8, group, row_block)
+    return _eight_bit("gemv8", x, weight, scale, fp8, group, row_block)
+
+
+def w8a16(x: torch.Tensor, weight: torch.Tensor, scale: torch.Tensor, fp8: bool, group: int,
+          row_block: int) -> torch.Tensor:
+    """`F.linear(x, W)` for a few rows `x` [rows, In]; same weights as `gemv8`."""
+    if torch.compiler.is_compiling():
+        return _w8a16_op(x, weight, scale, fp8, group, row_block)
+    return _eight_bit("w8a16", x, weight, scale, fp8, group, row_block)
+
+
+def dequantize8(weight: torch.Tensor, scale: torch.Tensor, fp8: bool, group: int, row_block: int,
+                dtype: torch.dtype) -> torch.Tensor:
+    """The int8 weight of `gemv8` dequantized to `dtype` (f32 product, one rounding)."""
+    _no_fp8("dequantize8", fp8)
+    device = _on_gpu("dequantize8", weight, scale)
+    width, depth = weight.shape
+    weight, scale = weight.contiguous(), scale.float().contiguous()
+    out = torch.empty(width, depth, dtype=dtype, device=device)
+    with _Device(device):
+        _lib.check(_lib.load().b200q_int8_dequantize(
+            weight.data_ptr(), scale.data_ptr(), out.data_ptr(), width, depth, group,
+            _code(dtype, "dequantize8"), _stream(device)))
+    return out
+
+
+def _outside(name: str):
+    def missing(*args: object, **kwargs: object):
+        raise NotImplementedError(f"linnet.torch.kernels.{name} is outside this build "
+                                  "(int4 / int8 weight-only layers)")
+    missing.__name__ = name
+    return missing
+
+
+# Names the reference's `quantized.py` and generated source look up on this module
+# for formats that are not part of this build.
+fp8_rows = _outside("fp8_rows")
+fp8_groups = _outside("fp8_groups")
+int8_rows = _outside("int8_rows")
+int8_mm = _outside("int8_mm")

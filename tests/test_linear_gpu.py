@@ -1,0 +1,256 @@
+"""int4 / int8 linear kernels (through the C ABI, via the torch operators) against the
+CPU oracle of the reference's torch path.
+
+Tolerance: rtol 1e-2 / atol 1e-2 on bf16 outputs with f32 accumulation (the bar this
+build states), and additionally the reference's own kernel-test bound
+`atol = 1e-2 * max|expected|` (python/linnet/tests/test_quant_groups.py:165-195).
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import linear_oracle as lo
+from oracle import quant_oracle as qo
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 1e-2, 1e-2
+
+
+def close(got: torch.Tensor, want: torch.Tensor, what: str = "") -> None:
+    got, want = got.float().cpu(), want.float().cpu()
+    torch.testing.assert_close(got, want, rtol=RTOL, atol=ATOL, msg=lambda m: f"{what}: {m}")
+    bound = 1e-2 * want.abs().max().item()
+    assert (got - want).abs().max().item() <= bound + 1e-6, what
+
+
+def random_int4(out, depth, group, dtype, seed):
+    gen = torch.Generator().manual_seed(seed)
+    packed = torch.randint(0, 256, (out, depth // group, group // 2), generator=gen, dtype=torch.uint8)
+    scale = (torch.rand(out, depth // group, generator=gen) * 0.02 + 0.001).to(dtype)
+    zero = torch.randint(0, 16, (out, depth // group), generator=gen, dtype=torch.uint8)
+    return packed, scale, zero, gen
+
+
+def _bf16(bits):
+    return torch.from_numpy(bits.astype(np.int16)).view(torch.bfloat16)
+
+
+@pytest.mark.parametrize("rows", [1, 3, 16, 40])
+def test_int4_reference_fixture(golden_linear, rows):
+    """Outputs the reference itself produced for an Int4GroupLinear card."""
+    from linnet_b200 import kernels
+
+    g = golden_linear["lin4"]
+    x = _bf16(g[f"rows{rows}"]["x_bits"])
+    want = _bf16(g[f"rows{rows}"]["y_bits"])
+    got = kernels.int4_linear(x.cuda(), torch.from_numpy(g["packed"]).cuda(),
+                              _bf16(g["scale_bits"]).cuda(), torch.from_numpy(g["zero"]).cuda())
+    assert got.shape == want.shape and got.dtype == torch.bfloat16
+    close(got, want, f"fixture rows={rows}")
+
+
+@pytest.mark.parametrize(("rows", "group", "out", "dtype"), [
+    (8, 128, 72, torch.bfloat16),
+    (37, 32, 72, torch.float16),
+    (128, 64, 72, torch.bfloat16),
+    (24, 128, 8448, torch.bfloat16),
+])
+def test_int4_reference_kernel_cases(rows, group, out, dtype):
+    """The reference's kernel test, same seeds, shapes and bound
+    (python/linnet/tests/test_quant_groups.py:165-195)."""
+    from linnet_b200 import kernels
+
+    width = 512
+    generator = torch.Generator().manual_seed(rows)
+    packed = torch.randint(0, 256, (out, width // group, group // 2), generator=generator, dtype=torch.uint8)
+    scale = (torch.rand(out, width // group, generator=generator) * 0.02 + 0.001).to(dtype)
+    zero = torch.randint(6, 10, (out, width // group), generator=generator, dtype=torch.uint8)
+    x = torch.randn(rows, width, generator=generator).to(dtype)
+    levels = torch.stack([packed & 15, packed >> 4], dim=-1).reshape(out, width // group, group)
+    weight = (levels.float() - zero.float()[..., None]) * scale.float()[..., None]
+    expected = x.float() @ weight.reshape(out, width).T
+    got = kernels.int4_linear(x.cuda(), packed.cuda(), scale.cuda(), zero.cuda())
+    assert got.shape == (rows, out) and got.dtype == dtype
+    bound = 1e-2 * expected.abs().max().item()
+    torch.testing.assert_close(got.float().cpu(), expected, rtol=0, atol=bound)
+
+
+@pytest.mark.parametrize("rows", [1, 2, 4, 7, 8, 9, 15, 16, 17, 33])
+@pytest.mark.parametrize(("depth", "out", "group"), [
+    (512, 72, 128), (256, 17, 128), (1024, 16, 256), (384, 40, 64), (128, 8, 32), (256, 24, 16),
+    (192, 20, 64), (96, 5, 32), (14336, 64, 128), (4096, 1000, 512),
+])
+def test_int4_shapes(rows, depth, out, group):
+    from linnet_b200 import kernels
+
+    packed, scale, zero, gen = random_int4(out, depth, group, torch.bfloat16, rows * 131 + depth)
+    x = torch.randn(rows, depth, generator=gen).to(torch.bfloat16)
+    want = lo.int4_groups_linear(x, packed, scale, zero)
+    got = kernels.int4_linear(x.cuda(), packed.cuda(), scale.cuda(), zero.cuda())
+    close(got, want, f"rows={rows} depth={depth} out={out} group={group}")
+
+
+@pytest.mark.parametrize("rows", [1, 5, 16])
+def test_int4_f16(rows):
+    from linnet_b200 import kernels
+
+    packed, scale, zero, gen = random_int4(96, 1024, 128, torch.float16, 5 + rows)
+    x = torch.randn(rows, 1024, generator=gen).to(torch.float16)
+    want = lo.int4_groups_linear(x, packed, scale, zero)
+    got = kernels.int4_linear(x.cuda(), packed.cuda(), scale.cuda(), zero.cuda())
+    close(got, want, f"f16 rows={rows}")
+
+
+@pytest.fixture(scope="module")
+def gate_up_weight():
+    """Config: W ~ N(0, 0.02) [14336, 4096] quantized int4-g128 by the oracle quantizer,
+    scales stored as bf16 (seed 0)."""
+    gen = torch.Generator().manual_seed(0)
+    w = torch.randn(14336, 4096, generator=gen) * 0.02
+    packed, scale, zero = qo.quantize_int4_groups(w.numpy(), 128)
+    return (torch.from_numpy(packed), torch.from_numpy(scale).to(torch.bfloat16),
+            torch.from_numpy(zero), gen)
+
+
+@pytest.mark.parametrize("rows", [1, 4, 16])
+def test_int4_gate_up_shape(gate_up_weight, rows):
+    """The headline decode shape: K=4096, N=14336, g128, M in {1, 4, 16}."""
+    from linnet_b200 import kernels
+
+    packed, scale, zero, gen = gate_up_weight
+    x = torch.randn(rows, 4096, generator=gen).to(torch.bfloat16)
+    want = lo.int4_groups_linear(x, packed, scale, zero)
+    got = kernels.int4_linear(x.cuda(), packed.cuda(), scale.cuda(), zero.cuda())
+    close(got, want, f"gate/up rows={rows}")
+
+
+def test_int4_down_shape_and_linearity():
+    """K=14336, N=4096 (the row-split projection): oracle parity, and linearity in x,
+    which holds at any size: f(x1 + x2) = f(x1) + f(x2) up to rounding."""
+    from linnet_b200 import kernels
+
+    packed, scale, zero, gen = random_int4(4096, 14336, 128, torch.bfloat16, 99)
+    x1 = torch.randn(2, 14336, generator=gen).to(torch.bfloat16)
+    want = lo.int4_groups_linear(x1, packed, scale, zero)
+    dev = [t.cuda() for t in (packed, scale, zero)]
+    got = kernels.int4_linear(x1.cuda(), *dev)
+    close(got, want, "down")
+    x2 = (x1 * 0.5).to(torch.bfloat16)  # exact in bf16
+    both = kernels.int4_linear((x1 + x2).cuda(), *dev).float()
+    parts = got.float() + kernels.int4_linear(x2.cuda(), *dev).float()
+    torch.testing.assert_close(both, parts, rtol=2e-2, atol=2e-2 * parts.abs().max().item())
+
+
+def test_int4_dequantize_is_exact():
+    """`_int4_weight`: bit-for-bit the reference's arithmetic
+    (python/linnet/tests/test_quant_groups.py:151-162)."""
+    from linnet_b200 import int4
+
+    for group, dtype in ((128, torch.bfloat16), (32, torch.float16), (6, torch.bfloat16)):
+        packed, scale, zero, _ = random_int4(40, group * 6, group, dtype, group)
+        want = lo.int4_weight(packed, scale, zero, dtype)
+        got = int4._int4_weight(packed.cuda(), scale.cuda(), zero.cuda())
+        assert torch.equal(got.cpu().view(torch.int16), want.view(torch.int16)), group
+
+
+def test_generated_helpers_contract():
+    """`_int4_pack` yields the 3-tuple the reference's test asserts, `_int4_linear`
+    takes the generated call's arguments, bias and leading batch axes included."""
+    from linnet_b200 import int4
+
+    packed, scale, zero, gen = random_int4(64, 256, 128, torch.bfloat16, 3)
+    bias = torch.randn(64, generator=gen).to(torch.bfloat16)
+    x = torch.randn(2, 3, 256, generator=gen).to(torch.bfloat16)
+    p, s, z = packed.cuda(), scale.cuda(), zero.cuda()
+    prepared = int4._int4_pack(p, s, z)
+    assert isinstance(prepared, tuple) and len(prepared) == 3
+    got = int4._int4_linear(x.cuda(), prepared, bias.cuda(), p, s, z)
+    want = lo.int4_groups_linear(x, packed, scale, zero, bias)
+    assert got.shape == (2, 3, 64)
+    close(got, want, "generated helpers")
+
+
+# ---- int8 -------------------------------------------------------------------------
+
+
+@pytest.mark.parametrize("rows", [1, 5, 16])
+def test_int8_reference_fixture(golden_linear, rows):
+    from linnet_b200 import quantized
+
+    g = golden_linear["lin8"]
+    x = _bf16(g[f"rows{rows}"]["x_bits"]).cuda()
+    ops = quantized.int8_operands(torch.from_numpy(g["q_rows"]).cuda(),
+                                  torch.from_numpy(g["s_rows"]).reshape(-1).cuda(), 0)
+    close(quantized.int8_linear(x, ops, None), _bf16(g[f"rows{rows}"]["y_rows_bits"]), "rows")
+    gops = quantized.int8_group_operands(torch.from_numpy(g["q_groups"]).cuda(),
+                                         torch.from_numpy(g["s_groups"]).cuda())
+    close(quantized.int8_group_linear(x, gops, None), _bf16(g[f"rows{rows}"]["y_groups_bits"]), "groups")
+
+
+@pytest.mark.parametrize("rows", [1, 3, 8, 16, 17, 64])
+@pytest.mark.parametrize(("depth", "out", "group"), [
+    (4096, 4096, 0), (512, 72, 0), (256, 17, 128), (1024, 48, 64), (256, 24, 16), (96, 10, 32),
+    (100, 7, 0), (14336, 32, 0),
+])
+def test_int8_shapes(rows, depth, out, group):
+    from linnet_b200 import quantized
+
+    gen = torch.Generator().manual_seed(rows + depth + out)
+    w = torch.randn(out, depth, generator=gen) * 0.02
+    q, scale = qo.quantize_int8_groups(w.numpy(), group or depth, "f32")
+    q, scale = torch.from_numpy(q), torch.from_numpy(scale)
+    x = torch.randn(rows, depth, generator=gen).to(torch.bfloat16)
+    bias = torch.randn(out, generator=gen).to(torch.bfloat16)
+    if group == 0:
+        want = lo.int8_linear(x, q, scale.reshape(-1), bias)
+        ops = quantized.int8_operands(q.cuda(), scale.reshape(-1).cuda(), 1)
+        got = quantized.int8_linear(x.cuda(), ops, bias.cuda())
+    else:
+        want = lo.int8_group_linear(x, q, scale, bias)
+        ops = quantized.int8_group_operands(q.cuda(), scale.cuda())
+        got = quantized.int8_group_linear(x.cuda(), ops, bias.cuda())
+    close(got, want, f"int8 rows={rows} depth={depth} out={out} group={group}")
+
+
+def test_int8_config_one():
+    """int8 symmetric per-output-channel, M=1, K=N=4096, W ~ N(0, 0.02), seed 0."""
+    from linnet_b200 import kernels, quant
+
+    torch.manual_seed(0)
+    w = torch.randn(4096, 4096) * 0.02
+    x = torch.randn(1, 4096).to(torch.bfloat16)
+    q, scale = quant.quantize_int8_groups(w, 4096, "f32")
+    want_q, want_s = qo.quantize_int8_groups(w.numpy(), 4096, "f32")
+    assert np.array_equal(q.cpu().numpy(), want_q)
+    want = lo.int8_linear(x, torch.from_numpy(want_q), torch.from_numpy(want_s).reshape(-1))
+    got = kernels.gemv8(x.cuda(), q, scale.reshape(-1), False, 0, 1)
+    assert got.shape == (1, 4096)
+    close(got, want, "config 1")
+    deq = kernels.dequantize8(q, scale.reshape(-1), False, 0, 1, torch.bfloat16)
+    assert torch.equal(deq.cpu().view(torch.int16),
+                       lo.int8_weight(torch.from_numpy(want_q), torch.from_numpy(want_s), torch.bfloat16).view(torch.int16))
+
+
+def test_cuda_graph_capture():
+    """The operators record into a CUDA graph and replay (no sync, no allocation in the
+    C ABI; outputs come from PyTorch's graph pool)."""
+    from linnet_b200 import kernels
+
+    packed, scale, zero, gen = random_int4(256, 512, 128, torch.bfloat16, 11)
+    p, s, z = packed.cuda(), scale.cuda(), zero.cuda()
+    x = torch.randn(4, 512, generator=gen).to(torch.bfloat16)
+    static = x.cuda()
+    kernels.int4_linear(static, p, s, z)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y = kernels.int4_linear(static, p, s, z)
+    x2 = torch.randn(4, 512, generator=gen).to(torch.bfloat16)
+    static.copy_(x2.cuda())
+    graph.replay()
+    torch.cuda.synchronize()
+    close(y, lo.int4_groups_linear(x2, packed, scale, zero), "graph replay")
