@@ -62,10 +62,20 @@ __device__ __forceinline__ void reduce_and_store(const float (&total)[NT][MB][4]
     }
 }
 
+// Programmatic dependent launch: a kernel that calls pdl_wait() before it touches
+// anything an earlier kernel of the stream wrote may start while that kernel drains,
+// which hides launch latency and ramp-up behind the predecessor's tail.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // Launches `kernel` on a (tiles, ksplit) grid whose y extent forms one cluster.
+// `overlap`: launch with programmatic stream serialization (the kernel must call
+// pdl_wait() before reading activations or writing outputs).
 template <typename Kernel, typename Args>
 int32_t launch_clustered(const char* who, Kernel kernel, const Args& args, int tiles, int ksplit,
-                         int threads, size_t smem, cudaStream_t stream) {
+                         int threads, size_t smem, cudaStream_t stream, bool overlap = false) {
     if (smem > 48 * 1024) {
         if (smem > 227 * 1024) return fail("%s: %zu bytes of shared memory needed", who, smem);
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
@@ -75,13 +85,15 @@ int32_t launch_clustered(const char* who, Kernel kernel, const Args& args, int t
     config.blockDim = dim3(unsigned(threads), 1, 1);
     config.dynamicSmemBytes = smem;
     config.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = unsigned(ksplit);
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attr;
-    config.numAttrs = 1;
+    config.numAttrs = overlap ? 2 : 1;
     const cudaError_t err = cudaLaunchKernelEx(&config, kernel, args);
     if (err != cudaSuccess) {
         cudaGetLastError();

@@ -24,6 +24,7 @@
 //     partial sums meeting in (distributed) shared memory, so no global scratch
 //     and no atomics are used.
 #include "gemv_common.cuh"
+#include "int4_gemv_oct.cuh"
 
 namespace b200q {
 namespace {
@@ -354,6 +355,33 @@ int32_t dispatch_gemv(const GemvArgs& a, const Plan& p, cudaStream_t stream) {
     return launch_gemv<T, MODE, 2, 2, 4, 2>(a, p.ksplit, stream);
 }
 
+// The specialised g128 kernel when the shape allows it: the most warps per block
+// (of 4, 7, 2, 1) that divide K / 1024 with at most 8 blocks per cluster.
+template <typename T>
+bool run_oct(const GemvArgs& a, cudaStream_t stream, int32_t* status) {
+    OctArgs o{a.x, a.packed, a.scale, a.zero, a.y, a.M, a.K, a.N, 1, 0};
+    const bool few = a.M <= 8;
+    if (oct_plan(a.K, a.G, 4, a.scale, a.zero, &o.ksplit)) {
+        if (a.M <= 2) {
+            // One or two rows: every weight load of the kernel is issued up front
+            // (cp.async) and the launch overlaps the tail of the kernel before it.
+            o.overlap = 1;
+            *status = launch_oct<T, 1, 1, 4, 0>(o, stream);
+        } else {
+            *status = few ? launch_oct<T, 1, 1, 4, 2>(o, stream) : launch_oct<T, 2, 1, 4, 2>(o, stream);
+        }
+    } else if (oct_plan(a.K, a.G, 7, a.scale, a.zero, &o.ksplit)) {
+        *status = few ? launch_oct<T, 1, 1, 7, 2>(o, stream) : launch_oct<T, 2, 1, 7, 2>(o, stream);
+    } else if (oct_plan(a.K, a.G, 2, a.scale, a.zero, &o.ksplit)) {
+        *status = few ? launch_oct<T, 1, 1, 2, 2>(o, stream) : launch_oct<T, 2, 1, 2, 2>(o, stream);
+    } else if (oct_plan(a.K, a.G, 1, a.scale, a.zero, &o.ksplit)) {
+        *status = few ? launch_oct<T, 1, 1, 1, 2>(o, stream) : launch_oct<T, 2, 1, 1, 2>(o, stream);
+    } else {
+        return false;
+    }
+    return true;
+}
+
 template <typename T>
 int32_t run_gemv(GemvArgs a, int64_t rows, cudaStream_t stream) {
     const size_t elt = 2;
@@ -363,8 +391,10 @@ int32_t run_gemv(GemvArgs a, int64_t rows, cudaStream_t stream) {
         a.M = int(rows - m0 < 16 ? rows - m0 : 16);
         a.x = x + size_t(m0) * a.K * elt;
         a.y = y + size_t(m0) * a.N * elt;
-        int32_t status;
-        if (a.K % 128 == 0) {
+        int32_t status = B200Q_OK;
+        if (run_oct<T>(a, stream, &status)) {
+            // the specialised g128 kernel took it
+        } else if (a.K % 128 == 0) {
             const Plan p = choose_plan(a.M, a.K, a.N);
             status = a.G % 128 == 0 ? dispatch_gemv<T, kExactBlock>(a, p, stream)
                                     : dispatch_gemv<T, kExactWord>(a, p, stream);
@@ -385,7 +415,7 @@ int32_t run_gemv(GemvArgs a, int64_t rows, cudaStream_t stream) {
     case id: return launch_gemv<__nv_bfloat16, kExactBlock, MB, NT, W, D>(a, ksplit, stream); \
     case 100 + id: return launch_gemv<__nv_bfloat16, kPost, MB, NT, W, D>(a, ksplit, stream);
 int32_t tune_gemv(const GemvArgs& a, int variant, int ksplit, cudaStream_t stream) {
-    switch (variant) {
+    switch (variant & 0xFFF) {
         B200Q_VARIANT(0, 1, 1, 4, 3)
         B200Q_VARIANT(1, 1, 1, 4, 2)
         B200Q_VARIANT(2, 1, 1, 4, 4)
@@ -406,6 +436,26 @@ int32_t tune_gemv(const GemvArgs& a, int variant, int ksplit, cudaStream_t strea
         B200Q_VARIANT(25, 2, 4, 4, 1)
         B200Q_VARIANT(26, 2, 2, 4, 1)
         B200Q_VARIANT(27, 2, 1, 8, 4)
+    }
+    // 200 + ...: the specialised g128 kernel; bit 0x1000 of `variant` asks for
+    // programmatic dependent launch.
+    OctArgs o{a.x, a.packed, a.scale, a.zero, a.y, a.M, a.K, a.N, 1, (variant & 0x1000) ? 1 : 0};
+#define B200Q_OCT(id, MB, NT, W, D)                                                      \
+    case id:                                                                             \
+        if (!oct_plan(a.K, a.G, W, a.scale, a.zero, &o.ksplit)) return fail("oct: shape"); \
+        return launch_oct<__nv_bfloat16, MB, NT, W, D, false>(o, stream);                \
+    case 100 + id:                                                                       \
+        if (!oct_plan(a.K, a.G, W, a.scale, a.zero, &o.ksplit)) return fail("oct: shape"); \
+        return launch_oct<__nv_bfloat16, MB, NT, W, D, true>(o, stream);
+    switch (variant & 0xFFF) {
+        B200Q_OCT(200, 1, 1, 4, 2)
+        B200Q_OCT(201, 1, 1, 4, 0)
+        B200Q_OCT(203, 1, 2, 4, 2)
+        B200Q_OCT(210, 1, 1, 7, 2)
+        B200Q_OCT(211, 1, 1, 7, 0)
+        B200Q_OCT(220, 2, 1, 4, 2)
+        B200Q_OCT(221, 2, 2, 4, 2)
+        B200Q_OCT(222, 2, 1, 4, 0)
     }
     return fail("no such variant");
 }

@@ -1,0 +1,332 @@
+// The fast int4-g128 decode kernel: every warp owns one "oct" -- 8 consecutive
+// k-blocks (1024 inputs, 512 weight bytes per row) -- of NT 16-row tiles.
+//
+// It is the kernel of int4_gemv.cu specialised for group == 128 and K a multiple of
+// 1024 so that everything indexed by the k-block is a compile-time constant:
+//   * the oct's 8 scales (one 16-byte load) and 8 zero points (one 8-byte load) of a
+//     row arrive with the first weight loads; one PRMT each turns them into the
+//     (scale, scale) and (magic + zero, magic + zero) pairs of a k-block;
+//   * the 8 * NT k-block steps are fully unrolled around a D-deep register pipeline
+//     of 16-byte weight loads (L1-bypassing, straight into A-fragment position);
+//   * activations are not staged at all: each lane reads the 16 bytes of its
+//     activation row it needs for a pair of products straight from global memory
+//     (they stay in L1, which the weight loads bypass) and permutes them with four
+//     PRMTs to the (k, k+4) pairing of the A fragments; every B fragment is used
+//     exactly once per warp, so a shared-memory copy would only add traffic;
+//   * two accumulator sets alternate to halve the tensor-core dependency chains.
+// Dequantization is the reference's arithmetic exactly: (magic + q) - (magic + zero)
+// is the integer q - zero, and one multiply by the scale rounds once to the 16-bit
+// type.  Per k-block and 16-row tile that is 56 LOP3/SHF + 64 HSUB2/HMUL2 + 8 MMA.
+#pragma once
+
+#include "gemv_common.cuh"
+
+namespace b200q {
+
+struct OctArgs {
+    const void* x;          // [M, K]
+    const uint8_t* packed;  // [N, K/2]
+    const void* scale;      // [N, K/128]
+    const uint8_t* zero;    // [N, K/128]
+    void* y;                // [M, N]
+    int M, K, N;
+    int ksplit;             // blocks per cluster; K == 1024 * W * ksplit
+    int overlap;            // launched with programmatic stream serialization
+};
+
+// w >> S.  With B200Q_SHIFT_BY_MULHI it is computed as the high half of w * 2^(32-S),
+// an integer multiply that runs on the FMA pipe, to take load off the ALU pipe the
+// LOP3s and PRMTs of the dequantization already fill.
+// Waits until at most `pending` of this thread's cp.async groups are in flight
+// (`pending` is a constant once the caller's loop is unrolled).
+__device__ __forceinline__ void cp_async_wait(int pending) {
+    switch (pending) {
+        case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+        case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+        case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+        case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+        case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+        case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+        default: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+    }
+}
+
+template <int S>
+__device__ __forceinline__ uint32_t shr(uint32_t w) {
+#ifdef B200Q_SHIFT_BY_MULHI
+    uint32_t r;
+    asm("mul.hi.u32 %0, %1, %2;" : "=r"(r) : "r"(w), "r"(1u << (32 - S)));
+    return r;
+#else
+    return w >> S;
+#endif
+}
+
+// D > 0: a D-deep register pipeline of weight loads.  D == 0 ("deep", NT == 1): the
+// first k-block is loaded into registers and the other seven are requested at once
+// with cp.async into lane-private shared-memory slots (each lane later reads back
+// exactly the 16-byte pieces it asked for, so a wait_group is all the synchronisation
+// needed): the whole weight matrix is in flight from the first cycles of the kernel
+// and the arithmetic never waits on a load it has not long since issued.
+// FAST: zero point and scale are applied in f32 to each k-block's sums,
+//     y += scale * (sum_k x_k (magic + q_k) - (magic + zero) * sum_k x_k),
+// (sum_k x_k comes from a product with a fragment of ones) instead of dequantizing
+// every weight; cheaper, and closer to exact arithmetic, but not the reference's
+// rounding of each weight to the 16-bit type.
+template <typename T, int MB, int NT, int W, int D, bool FAST>
+__global__ void __launch_bounds__(W * 32, (NT == 1 ? 28 : 20) / W)  // warps wanted per multiprocessor
+int4_gemv_oct_kernel(const OctArgs a) {
+    static_assert(D > 0 || NT == 1, "the deep variant handles one tile per warp");
+    using H = Half16<T>;
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+    const int g = lane / 4, t = lane % 4;
+    const int M = a.M, K = a.K, N = a.N;
+    const int groups = K / 128;
+    const int tile_row = blockIdx.x * (16 * NT);
+    const int oct = blockIdx.y * W + warp;  // this warp's oct along K
+
+    // Shared memory: the block's reduction buffer, then (deep variant) each lane's
+    // private slots [7 k-blocks][2 rows] x 16 B, laid out [slot][lane] per warp.
+    float* red = reinterpret_cast<float*>(smem);
+    uint4* slots = reinterpret_cast<uint4*>(smem + size_t(W) * NT * 16 * MB * 8 * 4) +
+                   size_t(warp) * (14 * 32) + lane;
+
+    const uint8_t* rowp[NT][2];
+    uint4 s8[NT][2];
+    uint2 z8[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = min(tile_row + nt * 16 + h * 8 + g, N - 1);  // ragged tile: clamp
+            rowp[nt][h] = a.packed + size_t(r) * (K / 2) + size_t(oct) * 512 + t * 16;
+        }
+
+    // One pipeline step is one k-block of all NT tiles (2 * NT 16-byte loads a lane).
+    uint4 st[D > 0 ? D : 1][NT][2];
+    auto load_step = [&](int slot, int j) {  // compile-time arguments after unrolling
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            st[slot][nt][0] = ldg_stream(rowp[nt][0] + j * 64);
+            st[slot][nt][1] = ldg_stream(rowp[nt][1] + j * 64);
+        }
+    };
+
+    // 1. Weight loads first: they do not depend on the previous kernel.
+    if (D > 0) {
+#pragma unroll
+        for (int d = 0; d < D; ++d)
+            if (d < 8) load_step(d, d);
+    } else {
+        load_step(0, 0);
+#pragma unroll
+        for (int j = 1; j < 8; ++j) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t dst = uint32_t(__cvta_generic_to_shared(slots + ((j - 1) * 2 + h) * 32));
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(rowp[0][h] + j * 64) : "memory");
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = min(tile_row + nt * 16 + h * 8 + g, N - 1);
+            const size_t at = size_t(r) * groups + size_t(oct) * 8;
+            s8[nt][h] = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(a.scale) + at));
+            z8[nt][h] = __ldg(reinterpret_cast<const uint2*>(a.zero + at));
+        }
+    if (a.overlap) {
+        pdl_launch_dependents();
+        pdl_wait();  // activations may come from the kernel before this one
+    }
+
+    // 2. This lane's activations: row mb*8 + g, inputs oct*1024 + j*128 + t*32 + i*8 ...
+    const uint4* xp[MB];
+#pragma unroll
+    for (int mb = 0; mb < MB; ++mb) {
+        const int m = mb * 8 + g;
+        xp[mb] = m < M ? static_cast<const uint4*>(a.x) + (size_t(m) * K + size_t(oct) * 1024 + t * 32) / 8
+                       : nullptr;
+    }
+
+    // 3. The 8 * NT steps, fully unrolled.
+    float acc[NT][MB][2][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+            for (int s = 0; s < 2; ++s)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[nt][mb][s][i] = 0.0f;
+
+    const uint32_t kMask = 0x000F000Fu;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        uint4 q[NT][2];
+        if (D > 0) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                q[nt][0] = st[j % (D > 0 ? D : 1)][nt][0];
+                q[nt][1] = st[j % (D > 0 ? D : 1)][nt][1];
+            }
+            if (j + D < 8) load_step(j % (D > 0 ? D : 1), j + D);
+        } else if (j == 0) {
+            q[0][0] = st[0][0][0];
+            q[0][1] = st[0][0][1];
+        } else {
+            cp_async_wait(7 - j);
+            q[0][0] = slots[((j - 1) * 2 + 0) * 32];
+            q[0][1] = slots[((j - 1) * 2 + 1) * 32];
+        }
+        float kacc[NT][MB][4], xacc[MB][4];  // FAST: this k-block's sums
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                xacc[mb][e] = 0.0f;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) kacc[nt][mb][e] = 0.0f;
+            }
+        // (scale, scale) and (magic + zero, magic + zero) of rows g and g+8, k-block j.
+        uint32_t sc[NT][2], bias[NT][2];
+        // bytes [zero, high byte of magic, zero, high byte of magic]
+        const uint32_t zsel = 0x7070u | uint32_t(j & 3) | (uint32_t(j & 3) << 8);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint4 s = s8[nt][h];
+                const uint32_t sw = j < 2 ? s.x : j < 4 ? s.y : j < 6 ? s.z : s.w;
+                sc[nt][h] = __byte_perm(sw, 0, (j & 1) ? 0x3232 : 0x1010);
+                bias[nt][h] = __byte_perm(j < 4 ? z8[nt][h].x : z8[nt][h].y, H::kMagic, zsel);
+            }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint4 b[MB];  // (x0,x4) (x1,x5) (x2,x6) (x3,x7) of this lane's 8 inputs
+#pragma unroll
+            for (int mb = 0; mb < MB; ++mb) {
+                uint4 raw = make_uint4(0, 0, 0, 0);
+#ifndef B200Q_KO_X
+                if (xp[mb] != nullptr) raw = __ldg(xp[mb] + j * 16 + i);
+#else
+                raw = make_uint4(lane, j, i, mb);
+#endif
+                b[mb].x = __byte_perm(raw.x, raw.z, 0x5410);
+                b[mb].y = __byte_perm(raw.x, raw.z, 0x7632);
+                b[mb].z = __byte_perm(raw.y, raw.w, 0x5410);
+                b[mb].w = __byte_perm(raw.y, raw.w, 0x7632);
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint32_t w0 = i == 0 ? q[nt][0].x : i == 1 ? q[nt][0].y : i == 2 ? q[nt][0].z : q[nt][0].w;
+                const uint32_t w1 = i == 0 ? q[nt][1].x : i == 1 ? q[nt][1].y : i == 2 ? q[nt][1].z : q[nt][1].w;
+                uint32_t f0[4], f1[4];  // (k0,k4) (k1,k5) (k2,k6) (k3,k7) of rows g, g+8
+#ifdef B200Q_KO_DEQUANT
+                f0[0] = f0[1] = f0[2] = f0[3] = w0;
+                f1[0] = f1[1] = f1[2] = f1[3] = w1;
+                if (false) {
+#else
+                {
+#endif
+                f0[0] = lop3_and_or(w0, kMask, H::kMagic);
+                f0[1] = lop3_and_or(shr<4>(w0), kMask, H::kMagic);
+                f0[2] = lop3_and_or(shr<8>(w0), kMask, H::kMagic);
+                f0[3] = lop3_and_or(shr<12>(w0), kMask, H::kMagic);
+                f1[0] = lop3_and_or(w1, kMask, H::kMagic);
+                f1[1] = lop3_and_or(shr<4>(w1), kMask, H::kMagic);
+                f1[2] = lop3_and_or(shr<8>(w1), kMask, H::kMagic);
+                f1[3] = lop3_and_or(shr<12>(w1), kMask, H::kMagic);
+                if (!FAST) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        f0[e] = sub_mul<T>(f0[e], bias[nt][0], sc[nt][0]);
+                        f1[e] = sub_mul<T>(f1[e], bias[nt][1], sc[nt][1]);
+                    }
+                }
+                }
+                const uint32_t a_lo[4] = {f0[0], f1[0], f0[1], f1[1]};
+                const uint32_t a_hi[4] = {f0[2], f1[2], f0[3], f1[3]};
+#pragma unroll
+                for (int mb = 0; mb < MB; ++mb) {
+                    if (FAST) {
+                        H::mma(kacc[nt][mb], a_lo, b[mb].x, b[mb].y);
+                        H::mma(kacc[nt][mb], a_hi, b[mb].z, b[mb].w);
+                    } else {
+#ifdef B200Q_KO_MMA
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            acc[nt][mb][0][e] = __uint_as_float(__float_as_uint(acc[nt][mb][0][e]) ^ a_lo[e] ^ b[mb].x ^ b[mb].y);
+                            acc[nt][mb][1][e] = __uint_as_float(__float_as_uint(acc[nt][mb][1][e]) ^ a_hi[e] ^ b[mb].z ^ b[mb].w);
+                        }
+#else
+                        H::mma(acc[nt][mb][0], a_lo, b[mb].x, b[mb].y);
+                        H::mma(acc[nt][mb][1], a_hi, b[mb].z, b[mb].w);
+#endif
+                    }
+                }
+            }
+            if (FAST) {
+                const uint32_t ones[4] = {H::kOnes, H::kOnes, H::kOnes, H::kOnes};
+#pragma unroll
+                for (int mb = 0; mb < MB; ++mb) {
+                    H::mma(xacc[mb], ones, b[mb].x, b[mb].y);
+                    H::mma(xacc[mb], ones, b[mb].z, b[mb].w);
+                }
+            }
+        }
+        if (FAST) {
+            // y += scale * (sums - (magic + zero) * sum of activations), rows g and g+8.
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const float s0 = H::to_float(sc[nt][0] & 0xFFFFu), s1 = H::to_float(sc[nt][1] & 0xFFFFu);
+                const float z0 = H::to_float(bias[nt][0] & 0xFFFFu), z1 = H::to_float(bias[nt][1] & 0xFFFFu);
+#pragma unroll
+                for (int mb = 0; mb < MB; ++mb) {
+                    acc[nt][mb][0][0] = fmaf(s0, fmaf(-z0, xacc[mb][0], kacc[nt][mb][0]), acc[nt][mb][0][0]);
+                    acc[nt][mb][0][1] = fmaf(s0, fmaf(-z0, xacc[mb][1], kacc[nt][mb][1]), acc[nt][mb][0][1]);
+                    acc[nt][mb][0][2] = fmaf(s1, fmaf(-z1, xacc[mb][2], kacc[nt][mb][2]), acc[nt][mb][0][2]);
+                    acc[nt][mb][0][3] = fmaf(s1, fmaf(-z1, xacc[mb][3], kacc[nt][mb][3]), acc[nt][mb][0][3]);
+                }
+            }
+        }
+    }
+
+    // 4. Sum the two accumulator sets, the warps, the cluster; write y.
+    float total[NT][MB][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) total[nt][mb][i] = acc[nt][mb][0][i] + acc[nt][mb][1][i];
+    reduce_and_store<H, MB, NT, W>(total, red, a.ksplit, tile_row, M, N, static_cast<uint16_t*>(a.y));
+}
+
+// Whether the oct kernel takes this problem with W warps per block; sets ksplit.
+inline bool oct_plan(int K, int G, int W, const void* scale, const uint8_t* zero, int* ksplit) {
+    if (G != 128 || K % 1024 != 0) return false;
+    const int octs = K / 1024;
+    if (octs % W != 0 || octs / W > 8) return false;
+    if (!aligned(scale, 16) || !aligned(zero, 8)) return false;
+    *ksplit = octs / W;
+    return true;
+}
+
+template <typename T, int MB, int NT, int W, int D, bool FAST = false>
+int32_t launch_oct(const OctArgs& args, cudaStream_t stream) {
+    const int tiles = (args.N + 16 * NT - 1) / (16 * NT);
+    const size_t smem = size_t(W) * NT * 16 * MB * 8 * 4 + (D == 0 ? size_t(W) * 14 * 32 * 16 : 0);
+    auto kernel = int4_gemv_oct_kernel<T, MB, NT, W, D, FAST>;
+    if (D == 0)  // 7 blocks of 30 KB per multiprocessor need the largest carve-out
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+    return launch_clustered("int4_gemv", kernel, args, tiles, args.ksplit, W * 32, smem, stream,
+                            args.overlap != 0);
+}
+
+}  // namespace b200q

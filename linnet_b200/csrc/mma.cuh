@@ -17,6 +17,7 @@ struct Half16<__nv_bfloat16> {
     // 128 + q: the nibble sits in the low mantissa bits of 128.0 (ulp 1).
     static constexpr uint32_t kMagic = 0x43004300u;
     static constexpr float kBias = 128.0f;
+    static constexpr uint32_t kOnes = 0x3F803F80u;  // (1.0, 1.0)
     static constexpr int kDtype = B200Q_BF16;
     __device__ static __forceinline__ float to_float(uint32_t bits16) {
         return __uint_as_float(bits16 << 16);
@@ -43,6 +44,7 @@ struct Half16<__half> {
     using pair = __half2;
     static constexpr uint32_t kMagic = 0x64006400u;  // 1024 + q
     static constexpr float kBias = 1024.0f;
+    static constexpr uint32_t kOnes = 0x3C003C00u;  // (1.0, 1.0)
     static constexpr int kDtype = B200Q_F16;
     __device__ static __forceinline__ float to_float(uint32_t bits16) {
         return __half2float(__ushort_as_half(uint16_t(bits16)));
