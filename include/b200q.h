@@ -88,6 +88,12 @@ int32_t b200q_int4_gemm(const void* x, const uint8_t* packed, const void* scale,
                         const uint8_t* zero, void* y, int64_t rows, int64_t in,
                         int64_t out, int64_t group, int32_t dtype, void* stream);
 
+/* Synchronises the device and reports whether any b200q_int4_gemm launch on it gave
+ * up on one of its bounded waits (B200Q_ERROR, with the waiting role in the message);
+ * such a launch leaves its output incomplete but the context usable.  No reference
+ * counterpart: the reference's kernels spin without a bound. */
+int32_t b200q_int4_gemm_status(void);
+
 /* Replaces the generated `_int4_weight` / Triton `_int4_unpack`
  * (src/backend/torch_source.cpp:1519-1551): the [out, in] weight in `dtype`,
  * (q - zero) * scale computed in f32 and rounded once. */

@@ -27,6 +27,7 @@ PROTOTYPES: dict[str, list] = {
                         c_int64, c_int32, c_void_p],
     "b200q_int4_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                         c_int64, c_int32, c_void_p],
+    "b200q_int4_gemm_status": [],
     "b200q_int4_dequantize": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                               c_int32, c_void_p],
     "b200q_int8_linear": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,

@@ -1,9 +1,419 @@
-// placeholder until the tcgen05 kernel lands
-#include "common.cuh"
+// int4 group-quantized dequant-GEMM for prompt-sized row counts on Blackwell
+// tensor cores (tcgen05 + tensor memory).
+//
+//   Y[M, N] = X[M, K] . W[N, K]^T,  W[n, k] = (q[n, k] - zero[n, k/G]) * scale[n, k/G]
+//
+// Stands in for the reference's many-row route, which dequantizes the whole weight
+// with a Triton kernel and calls cuBLAS (`_int4_weight` + `F.linear`,
+// src/backend/torch_source.cpp:1519-1566); here the weight is dequantized tile by
+// tile inside the product and never written to HBM.
+//
+// One persistent block per multiprocessor, 14 warps with fixed roles:
+//   warps 0-3   epilogue: tensor memory -> registers (tcgen05.ld) -> bf16 -> Y
+//   warp  4     TMA producer: two 128 x 64 boxes of X per stage (SWIZZLE_128B)
+//   warp  5     MMA issuer: one thread issues tcgen05.mma (128 x 128 x 16, bf16 -> f32)
+//   warps 6-13  dequantizers: packed nibbles -> registers -> the exact bf16 weight
+//               ((q - zero) * scale, one rounding, as the reference) -> the 128-byte
+//               swizzled K-major layout the MMA reads from shared memory
+// A block tile is 256 rows of X by 128 rows of W: every dequantized 128 x 64 weight
+// tile feeds two accumulators (2 x 128 columns of tensor memory), which halves the
+// dequantization work per flop; the accumulators are double-buffered (4 x 128 = all
+// 512 columns) so the epilogue of one tile overlaps the main loop of the next.
+// Stages: 4 x (32 KB of X + 16 KB of W) of shared memory, mbarrier full/empty pairs.
+// Every wait on an mbarrier is bounded: on expiry the block raises an error flag in
+// global memory, stops issuing work, still releases its tensor memory and returns.
+#include <cuda.h>
+
+#include "mma.cuh"
+
 namespace b200q {
-bool int4_gemm_supports(int64_t, int64_t, int64_t, int64_t, int32_t, const void*, const void*) { return false; }
+namespace {
+
+constexpr int kBM = 128;       // rows of X per accumulator
+constexpr int kBN = 128;       // rows of W (columns of Y) per tile
+constexpr int kBK = 64;        // inputs per stage: one 128-byte swizzle atom of bf16
+constexpr int kStages = 4;
+constexpr int kATile = kBM * kBK * 2;               // 16 KB
+constexpr int kStageBytes = 2 * kATile + kBN * kBK * 2;  // 48 KB
+constexpr int kEpilogueWarps = 4, kTmaWarp = 4, kMmaWarp = 5, kFirstDequantWarp = 6;
+constexpr int kDequantWarps = 8;
+constexpr int kThreads = (kFirstDequantWarp + kDequantWarps) * 32;  // 448
+constexpr uint32_t kTmemColumns = 512;
+
+struct GemmArgs {
+    const uint8_t* packed;  // [N, K/2]
+    const uint16_t* scale;  // [N, K/G] bf16
+    const uint8_t* zero;    // [N, K/G]
+    uint16_t* y;            // [M, N] bf16
+    int M, K, N, G;
+    int m_tiles, n_tiles;   // tiles of 256 rows of X, of 128 rows of W
+};
+
+// Non-zero after a bounded wait expired in some launch on this device (the value
+// names the waiting role); read back by b200q_int4_gemm_status().
+__device__ int g_gemm_error = 0;
+
+// ---- PTX wrappers -------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return uint32_t(__cvta_generic_to_shared(p));
 }
-extern "C" int32_t b200q_int4_gemm(const void*, const uint8_t*, const void*, const uint8_t*, void*, int64_t,
-                                   int64_t, int64_t, int64_t, int32_t, void*) {
-    return b200q::unavailable("int4_gemm: not built");
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: false (and the error flag set) after about a second.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* error, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t start = global_timer_ns();
+    for (uint32_t spins = 0;; ++spins) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spins & 1023u) == 1023u) {
+            if (*reinterpret_cast<volatile int*>(error) != 0) return false;  // someone else gave up
+            if (global_timer_ns() - start > 1000000000ull) {
+                atomicCAS(error, 0, code);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1,
+                                            uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(dst)),
+        "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+        : "memory");
+}
+// D[tmem] (+)= A[smem] . B[smem]^T, 128 x 128 x 16, bf16 inputs, f32 accumulate.
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     smem_u32(bar))
+                 : "memory");
+}
+// K-major, 128-byte swizzle: rows of 128 bytes, 8-row atoms 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return uint64_t((addr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) |
+           (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+// kind::f16 instruction descriptor: f32 accumulator, bf16 A and B, both K-major, M = N = 128.
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(kBN >> 3) << 17) |
+                            (uint32_t(kBM >> 4) << 24);
+
+struct Pipeline {  // shared-memory barriers and the tensor-memory base address
+    uint64_t full_a[kStages];   // TMA bytes of X landed
+    uint64_t full_b[kStages];   // dequantized W tile written (8 warp arrivals)
+    uint64_t empty[kStages];    // MMAs that read the stage completed
+    uint64_t acc_full[2];       // all MMAs of a tile completed
+    uint64_t acc_empty[2];      // epilogue drained the accumulators (4 warp arrivals)
+    uint32_t tmem_base;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // The swizzled tiles need 1024-byte alignment.
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    Pipeline* pipe = reinterpret_cast<Pipeline*>(smem + kStages * kStageBytes);
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int ksteps = a.K / kBK;
+    const int tiles = a.m_tiles * a.n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&pipe->full_a[s], 1);
+            mbar_init(&pipe->full_b[s], kDequantWarps);
+            mbar_init(&pipe->empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&pipe->acc_full[b], 1);
+            mbar_init(&pipe->acc_empty[b], kEpilogueWarps);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kMmaWarp) {  // one warp allocates (and later frees) all of tensor memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(&pipe->tmem_base)),
+                     "r"(kTmemColumns)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = pipe->tmem_base;
+
+    if (warp == kTmaWarp) {
+        // ---- producer of X -------------------------------------------------------
+        if (lane == 0) {
+            uint32_t it = 0;  // stage uses so far
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % a.m_tiles) * (2 * kBM);
+                const bool two = m0 + kBM < a.M;
+                for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
+                    const int s = it % kStages;
+                    if (it >= kStages) ok = mbar_wait(&pipe->empty[s], ((it / kStages) - 1) & 1, &g_gemm_error, 1);
+                    if (!ok) break;
+                    uint8_t* dst = smem + s * kStageBytes;
+                    mbar_expect_tx(&pipe->full_a[s], two ? 2 * kATile : kATile);
+                    tma_load_2d(dst, &x_map, ks * kBK, m0, &pipe->full_a[s]);
+                    if (two) tma_load_2d(dst + kATile, &x_map, ks * kBK, m0 + kBM, &pipe->full_a[s]);
+                }
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ---- MMA issuer ----------------------------------------------------------
+        if (lane == 0) {
+            uint32_t it = 0, t = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++t) {
+                const int m0 = (tile % a.m_tiles) * (2 * kBM);
+                const bool two = m0 + kBM < a.M;
+                const uint32_t buf = t & 1;
+                if (t >= 2) ok = mbar_wait(&pipe->acc_empty[buf], ((t >> 1) - 1) & 1, &g_gemm_error, 2);
+                tc_fence_after();
+                for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
+                    const int s = it % kStages;
+                    const uint32_t parity = (it / kStages) & 1;
+                    ok = mbar_wait(&pipe->full_a[s], parity, &g_gemm_error, 3) &&
+                         mbar_wait(&pipe->full_b[s], parity, &g_gemm_error, 4);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t base = smem_u32(smem + s * kStageBytes);
+#pragma unroll
+                    for (int kk = 0; kk < kBK / 16; ++kk) {
+                        const uint64_t b_desc = smem_desc(base + 2 * kATile + kk * 32);
+                        const uint32_t acc = (ks > 0 || kk > 0) ? 1u : 0u;
+                        umma_bf16(tmem + buf * 256, smem_desc(base + kk * 32), b_desc, kIdesc, acc);
+                        if (two) umma_bf16(tmem + buf * 256 + 128, smem_desc(base + kATile + kk * 32), b_desc, kIdesc, acc);
+                    }
+                    umma_commit(&pipe->empty[s]);  // frees the stage when these MMAs retire
+                }
+                if (ok) umma_commit(&pipe->acc_full[buf]);
+            }
+        }
+    } else if (warp >= kFirstDequantWarp) {
+        // ---- dequantizers --------------------------------------------------------
+        const int d = threadIdx.x - kFirstDequantWarp * 32;  // 0..255
+        const int row = d >> 1, half = d & 1;                // W row of the tile, 32-input half
+        const int groups = a.K / a.G;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+            const int n = min((tile / a.m_tiles) * kBN + row, a.N - 1);  // ragged tile: clamp
+            const uint8_t* src = a.packed + size_t(n) * (a.K / 2) + half * 16;
+            const uint16_t* srow = a.scale + size_t(n) * groups;
+            const uint8_t* zrow = a.zero + size_t(n) * groups;
+            for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
+                const int s = it % kStages;
+                // Issue the loads before waiting for the stage to drain.
+                const uint4 q = __ldg(reinterpret_cast<const uint4*>(src + size_t(ks) * (kBK / 2)));
+                const int grp = (ks * kBK) / a.G;
+                const uint32_t sc = uint32_t(__ldg(srow + grp)) * 0x00010001u;
+                const uint32_t bias = 0x43004300u + uint32_t(__ldg(zrow + grp)) * 0x00010001u;
+                if (it >= kStages) ok = mbar_wait(&pipe->empty[s], ((it / kStages) - 1) & 1, &g_gemm_error, 5);
+                if (!ok) break;
+                uint8_t* tile_b = smem + s * kStageBytes + 2 * kATile + row * 128;
+                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    // (k0,k4) (k1,k5) (k2,k6) (k3,k7): magic + q, then exactly (q - zero) * scale
+                    uint32_t f[4];
+                    f[0] = lop3_and_or(w[i], 0x000F000Fu, 0x43004300u);
+                    f[1] = lop3_and_or(w[i] >> 4, 0x000F000Fu, 0x43004300u);
+                    f[2] = lop3_and_or(w[i] >> 8, 0x000F000Fu, 0x43004300u);
+                    f[3] = lop3_and_or(w[i] >> 12, 0x000F000Fu, 0x43004300u);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) f[e] = sub_mul<__nv_bfloat16>(f[e], bias, sc);
+                    uint4 out;  // natural order (k0,k1) (k2,k3) (k4,k5) (k6,k7)
+                    out.x = __byte_perm(f[0], f[1], 0x5410);
+                    out.y = __byte_perm(f[2], f[3], 0x5410);
+                    out.z = __byte_perm(f[0], f[1], 0x7632);
+                    out.w = __byte_perm(f[2], f[3], 0x7632);
+                    const int chunk = half * 4 + i;  // 16-byte chunk of the 128-byte row
+                    *reinterpret_cast<uint4*>(tile_b + ((chunk ^ (row & 7)) * 16)) = out;
+                }
+                fence_proxy_async();  // generic-proxy stores -> visible to the tensor core
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&pipe->full_b[s]);
+            }
+        }
+    } else {
+        // ---- epilogue (warps 0-3; warp w owns tensor-memory lanes 32w .. 32w+31) ---
+        uint32_t t = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++t) {
+            const int m0 = (tile % a.m_tiles) * (2 * kBM);
+            const int n0 = (tile / a.m_tiles) * kBN;
+            const uint32_t buf = t & 1;
+            ok = mbar_wait(&pipe->acc_full[buf], (t >> 1) & 1, &g_gemm_error, 6);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int acc = 0; acc < 2; ++acc) {
+                const int m = m0 + acc * kBM + warp * 32 + lane;
+                if (m0 + acc * kBM >= a.M) break;  // second accumulator unused (warp-uniform)
+#pragma unroll 1
+                for (int c0 = 0; c0 < kBN; c0 += 32) {
+                    uint32_t v[32];
+                    const uint32_t taddr = tmem + (uint32_t(warp * 32) << 16) + buf * 256 + acc * 128 + c0;
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+                          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+                          "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
+                          "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
+                          "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                        : "r"(taddr));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (m < a.M) {
+                        uint16_t* dst = a.y + size_t(m) * a.N + n0 + c0;
+                        if (n0 + c0 + 32 <= a.N && (a.N % 8) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                uint4 o;
+                                o.x = Half16<__nv_bfloat16>::pack(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+                                o.y = Half16<__nv_bfloat16>::pack(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+                                o.z = Half16<__nv_bfloat16>::pack(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+                                o.w = Half16<__nv_bfloat16>::pack(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+                                reinterpret_cast<uint4*>(dst)[j] = o;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (n0 + c0 + j < a.N)
+                                    dst[j] = Half16<__nv_bfloat16>::from_float(__uint_as_float(v[j]));
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&pipe->acc_empty[buf]);
+        }
+    }
+
+    // Every role falls through to here, also after an expired wait.
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns)
+                     : "memory");
+    }
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no libcuda link).
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(p);
+    }
+    return fn;
+}
+
+}  // namespace
+
+bool int4_gemm_supports(int64_t rows, int64_t in, int64_t out, int64_t group, int32_t dtype,
+                        const void* x, const void* y) {
+    return dtype == B200Q_BF16 && rows > 0 && in % kBK == 0 && group % kBK == 0 && in >= kBK &&
+           (in * 2) % 16 == 0 && aligned(x, 16) && aligned(y, 2) && out > 0;
+}
+
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" int32_t b200q_int4_gemm(const void* x, const uint8_t* packed, const void* scale,
+                                   const uint8_t* zero, void* y, int64_t rows, int64_t in, int64_t out,
+                                   int64_t group, int32_t dtype, void* stream) {
+    const int32_t ok = check_int4_args("int4_gemm", x, packed, scale, zero, y, rows, in, out, group, dtype);
+    if (ok != B200Q_OK || rows == 0) return ok;
+    B200Q_REQUIRE(int4_gemm_supports(rows, in, out, group, dtype, x, y),
+                  "int4_gemm: needs bf16, inputs and group multiples of %d (got in=%lld group=%lld)", kBK,
+                  (long long)in, (long long)group);
+    B200Q_REQUIRE(rows < (int64_t(1) << 30), "int4_gemm: too many rows");
+    EncodeTiled encode = encode_tiled();
+    if (encode == nullptr) return unavailable("int4_gemm: the driver has no cuTensorMapEncodeTiled");
+
+    CUtensorMap x_map;
+    const cuuint64_t dims[2] = {cuuint64_t(in), cuuint64_t(rows)};
+    const cuuint64_t strides[1] = {cuuint64_t(in) * 2};
+    const cuuint32_t box[2] = {cuuint32_t(kBK), cuuint32_t(kBM)};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult made = encode(&x_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims,
+                                 strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    B200Q_REQUIRE(made == CUDA_SUCCESS, "int4_gemm: cuTensorMapEncodeTiled failed (%d)", int(made));
+
+    GemmArgs a{packed, static_cast<const uint16_t*>(scale), zero, static_cast<uint16_t*>(y),
+               int(rows), int(in), int(out), int(group),
+               int((rows + 2 * kBM - 1) / (2 * kBM)), int((out + kBN - 1) / kBN)};
+    const size_t smem = size_t(kStages) * kStageBytes + 1024 + 256;
+    cudaFuncSetAttribute(int4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    const int tiles = a.m_tiles * a.n_tiles;
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    int4_gemm_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(x_map, a);
+    return launched("int4_gemm");
+}
+
+extern "C" int32_t b200q_int4_gemm_status(void) {
+    int flag = 0;
+    const cudaError_t err = cudaMemcpyFromSymbol(&flag, g_gemm_error, sizeof(int));
+    if (err != cudaSuccess) return fail("int4_gemm_status: %s", cudaGetErrorString(err));
+    if (flag != 0) return fail("int4_gemm: a bounded wait expired (role %d)", flag);
+    return B200Q_OK;
 }
