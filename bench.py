@@ -323,7 +323,7 @@ def main() -> None:
         def reduce_max(v: float) -> float:
             return v
 
-    workload = args.workload or "gemv"
+    workload = args.workload or ("gemv" if world == 1 else "decode")
     if workload == "decode":
         from linnet_b200 import decoder
 

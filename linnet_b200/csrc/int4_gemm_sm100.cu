@@ -8,11 +8,11 @@
 // src/backend/torch_source.cpp:1519-1566); here the weight is dequantized tile by
 // tile inside the product and never written to HBM.
 //
-// One persistent block per multiprocessor, 14 warps with fixed roles:
+// One persistent block per multiprocessor, 22 warps with fixed roles:
 //   warps 0-3   epilogue: tensor memory -> registers (tcgen05.ld) -> bf16 -> Y
 //   warp  4     TMA producer: two 128 x 64 boxes of X per stage (SWIZZLE_128B)
 //   warp  5     MMA issuer: one thread issues tcgen05.mma (128 x 128 x 16, bf16 -> f32)
-//   warps 6-13  dequantizers: packed nibbles -> registers -> the exact bf16 weight
+//   warps 6-21  dequantizers (two groups of 8 taking stages in turn): packed nibbles -> registers -> the exact bf16 weight
 //               ((q - zero) * scale, one rounding, as the reference) -> the 128-byte
 //               swizzled K-major layout the MMA reads from shared memory
 // A block tile is 256 rows of X by 128 rows of W: every dequantized 128 x 64 weight
@@ -36,8 +36,9 @@ constexpr int kStages = 4;
 constexpr int kATile = kBM * kBK * 2;               // 16 KB
 constexpr int kStageBytes = 2 * kATile + kBN * kBK * 2;  // 48 KB
 constexpr int kEpilogueWarps = 4, kTmaWarp = 4, kMmaWarp = 5, kFirstDequantWarp = 6;
-constexpr int kDequantWarps = 8;
-constexpr int kThreads = (kFirstDequantWarp + kDequantWarps) * 32;  // 448
+constexpr int kDequantWarps = 8;   // warps that fill one stage
+constexpr int kDequantGroups = 2;  // groups of such warps, taking stages in turn
+constexpr int kThreads = (kFirstDequantWarp + kDequantWarps * kDequantGroups) * 32;  // 704
 constexpr uint32_t kTmemColumns = 512;
 
 struct GemmArgs {
@@ -235,7 +236,8 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
         }
     } else if (warp >= kFirstDequantWarp) {
         // ---- dequantizers --------------------------------------------------------
-        const int d = threadIdx.x - kFirstDequantWarp * 32;  // 0..255
+        const int d = (threadIdx.x - kFirstDequantWarp * 32) % (kDequantWarps * 32);  // 0..255
+        const int group_id = (threadIdx.x - kFirstDequantWarp * 32) / (kDequantWarps * 32);
         const int row = d >> 1, half = d & 1;                // W row of the tile, 32-input half
         const int groups = a.K / a.G;
         uint32_t it = 0;
@@ -246,6 +248,7 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
             const uint16_t* srow = a.scale + size_t(n) * groups;
             const uint8_t* zrow = a.zero + size_t(n) * groups;
             for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
+                if (int(it % kDequantGroups) != group_id) continue;  // the other group's stage
                 const int s = it % kStages;
                 // Issue the loads before waiting for the stage to drain.
                 const uint4 q = __ldg(reinterpret_cast<const uint4*>(src + size_t(ks) * (kBK / 2)));

@@ -1,0 +1,151 @@
+"""The tensor-parallel decoder: on the CPU the sharding and the collectives are checked
+with the oracle as the linear operator (gloo, world size 2); on a GPU the same model
+runs on the CUDA operators and must agree with the CPU oracle model."""
+
+from __future__ import annotations
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from linnet_b200 import decoder as dec
+from tests import decoder_util as du
+
+
+def dense_reference(cfg, whole, batch, steps):
+    """The same model with dequantized f32 weights and textbook attention."""
+    from oracle import linear_oracle as lo
+
+    def W(t):
+        return lo.int4_weight(*t, torch.float32)
+
+    gen = torch.Generator().manual_seed(3)
+    hd = cfg.head_dim
+    ks = [torch.zeros(batch, cfg.kv_heads, cfg.max_seq, hd) for _ in range(cfg.layers)]
+    vs = [torch.zeros(batch, cfg.kv_heads, cfg.max_seq, hd) for _ in range(cfg.layers)]
+    out = None
+    for t in range(steps):
+        tokens = torch.randint(0, cfg.vocab, (batch,), generator=gen)
+        pos = torch.full((batch,), t, dtype=torch.long)
+        x = whole["embed"][tokens].float()
+        for i, L in enumerate(whole["layers"]):
+            def norm(v, w):
+                return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.eps) * w.float()
+            h = norm(x, L["norm1"])
+            q = (h @ W(L["q"]).T).reshape(batch, cfg.heads, hd)
+            k = (h @ W(L["k"]).T).reshape(batch, cfg.kv_heads, hd)
+            v = (h @ W(L["v"]).T).reshape(batch, cfg.kv_heads, hd)
+            q, k = dec.rotary(q, pos, cfg.rope_theta), dec.rotary(k, pos, cfg.rope_theta)
+            ks[i][:, :, t], vs[i][:, :, t] = k, v
+            rep = cfg.heads // cfg.kv_heads
+            kk = ks[i][:, :, :t + 1].repeat_interleave(rep, dim=1)
+            vv = vs[i][:, :, :t + 1].repeat_interleave(rep, dim=1)
+            att = torch.softmax(torch.einsum("bhd,bhsd->bhs", q, kk) / hd ** 0.5, dim=-1)
+            o = torch.einsum("bhs,bhsd->bhd", att, vv).reshape(batch, -1)
+            x = x + o @ W(L["o"]).T
+            h = norm(x, L["norm2"])
+            x = x + (torch.nn.functional.silu(h @ W(L["gate"]).T) * (h @ W(L["up"]).T)) @ W(L["down"]).T
+        out = norm(x, whole["final_norm"]) @ W(whole["head"]).T
+    return out
+
+
+def test_single_rank_matches_dense_reference():
+    cfg = dec.DecoderConfig.tiny()
+    whole = du.whole_model(cfg)
+    model = du.rank_model(cfg, whole, 0, 1, du.oracle_linear)
+    got = du.run_steps(model, cfg, batch=3, steps=3).float()
+    want = dense_reference(cfg, whole, 3, 3)
+    assert got.shape == (3, cfg.vocab)
+    torch.testing.assert_close(got, want, rtol=5e-2, atol=5e-2 * want.abs().max().item())
+
+
+def test_shard_shapes_and_checks():
+    cfg = dec.DecoderConfig.tiny()
+    whole = du.whole_model(cfg)
+    m = du.rank_model(cfg, whole, 1, 2, du.oracle_linear)
+    w = m.layers[0]
+    assert w.qkv[0].shape == ((cfg.heads + 2 * cfg.kv_heads) * cfg.head_dim // 2, cfg.hidden // 128, 64)
+    assert w.o[0].shape == (cfg.hidden, cfg.heads * cfg.head_dim // 2 // 128, 64)   # K groups halved
+    assert w.down[1].shape == (cfg.hidden, cfg.mlp // 2 // 128)
+    assert m.head[0].shape[0] == cfg.vocab // 2
+    with pytest.raises(ValueError, match="do not divide"):
+        dec.check_tp(cfg, 3)
+    with pytest.raises(ValueError, match="whole groups"):
+        dec.check_tp(dec.DecoderConfig(layers=1, hidden=256, heads=4, kv_heads=4, head_dim=64, mlp=512,
+                                       vocab=512, max_seq=8), 4)
+    full = dec.DecoderConfig.llama31_8b()
+    for tp in (1, 2, 4, 8):
+        dec.check_tp(full, tp)
+    assert abs(full.int4_elements() - 7.5046e9) < 1e6
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _tp_worker(rank: int, world: int, port: int, out_dir: str) -> None:
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(0)
+        cfg = dec.DecoderConfig.tiny()
+        whole = du.whole_model(cfg)
+        model = du.rank_model(cfg, whole, rank, world, du.oracle_linear)
+        logits = du.run_steps(model, cfg, batch=2, steps=3)
+        torch.save(logits, os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_reproduce_the_whole_model(tmp_path):
+    """Each rank holds half of every projection; one all-reduce per row-split layer and
+    one all-gather of the logits reproduce the single-rank result on every rank."""
+    world = 2
+    mp.spawn(_tp_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    cfg = dec.DecoderConfig.tiny()
+    whole = du.whole_model(cfg)
+    single = du.run_steps(du.rank_model(cfg, whole, 0, 1, du.oracle_linear), cfg, batch=2, steps=3).float()
+    for rank in range(world):
+        got = torch.load(tmp_path / f"rank{rank}.pt").float()
+        assert got.shape == single.shape
+        # partial sums are rounded to bf16 before they are added, so not bit-identical
+        torch.testing.assert_close(got, single, rtol=3e-2, atol=3e-2 * single.abs().max().item())
+
+
+@pytest.mark.gpu
+def test_gpu_decoder_matches_cpu_oracle_decoder():
+    from linnet_b200 import kernels
+
+    cfg = dec.DecoderConfig.tiny()
+    whole = du.whole_model(cfg)
+    cpu = du.run_steps(du.rank_model(cfg, whole, 0, 1, du.oracle_linear), cfg, batch=4, steps=3).float()
+    gpu_model = du.rank_model(cfg, whole, 0, 1, kernels.int4_linear, device="cuda")
+    gpu = du.run_steps(gpu_model, cfg, batch=4, steps=3, device="cuda").float().cpu()
+    torch.testing.assert_close(gpu, cpu, rtol=3e-2, atol=3e-2 * cpu.abs().max().item())
+
+
+@pytest.mark.gpu
+def test_gpu_decoder_graph_replay():
+    from linnet_b200 import kernels, quant
+
+    cfg = dec.DecoderConfig.tiny()
+    dev = torch.device("cuda", 0)
+    model = dec.build_random(cfg, dev, rank=0, tp=1, seed=1, linear=kernels.int4_linear,
+                             quantize=quant.quantize_int4_groups)
+    model.allocate_cache(2, torch.Generator(device=dev).manual_seed(2))
+    tokens = torch.tensor([3, 5], device=dev)
+    positions = torch.full((2,), cfg.max_seq - 1, device=dev, dtype=torch.long)
+    eager = model.step(tokens, positions).clone()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = model.step(tokens, positions)
+    graph.replay()
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out, eager, rtol=0, atol=0)
