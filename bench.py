@@ -251,7 +251,80 @@ def run_gemv(args, rank: int, world: int, device: torch.device, barrier, reduce_
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_reference_gemv(args.rows, sets=4, reps=5, warm=2)
+    if rank == 0 and not args.no_other_configs:
+        del sets
+        torch.cuda.empty_cache()
+        line["other_configs"] = other_configs(device)
     return line
+
+
+def _time_us(fn, reps: int, warm: int = 3) -> float:
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(reps):
+        fn()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) * 1e3 / reps
+
+
+def other_configs(device: torch.device) -> dict:
+    """Short measurements of the other workloads (not the headline): the int8
+    per-channel GEMV, the prefill dequant-GEMM at M=2048 and the bulk quantize/pack
+    kernels on one 70B-shaped tensor.  Inputs are larger than L2 or rotated."""
+    from linnet_b200 import kernels, quant
+
+    bf16_peak = 1683.2
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        bf16_peak = float(json.loads(path.read_text())["bf16_tflops"])
+    hbm, _ = peaks()
+    out: dict = {}
+    gen = torch.Generator(device=device).manual_seed(3)
+    # int8 symmetric per-output-channel GEMV, M=1, K=N=4096 (16 weight sets = 268 MB)
+    sets8 = []
+    for _ in range(16):
+        w = torch.empty(4096, 4096, device=device).normal_(0, 0.02, generator=gen)
+        q, s = quant.quantize_int8_groups(w, 4096, "f32")
+        sets8.append((q, s.reshape(-1).contiguous()))
+    x1 = torch.randn(1, 4096, device=device, generator=gen).to(torch.bfloat16)
+    state = {"i": 0}
+
+    def gemv8() -> None:
+        q, s = sets8[state["i"] % 16]
+        state["i"] += 1
+        kernels.gemv8(x1, q, s, False, 0, 1)
+
+    us = _time_us(gemv8, 320)
+    nbytes = 4096 * 4096 + 4096 * 4 + 4096 * 2 + 4096 * 2
+    out["int8_gemv_M1_K4096_N4096"] = {"us": us, "GB/s": nbytes / us / 1e3, "frac_hbm": nbytes / us / 1e3 / hbm,
+                                       "note": "eager launches incl. host launch gaps"}
+    del sets8
+    # prefill dequant-GEMM, M = 2048
+    x = torch.randn(2048, 14336, device=device, generator=gen).to(torch.bfloat16)
+    for K, N in ((4096, 6144), (4096, 28672), (14336, 4096)):
+        w = torch.empty(N, K, device=device, dtype=torch.bfloat16).normal_(0, 0.02, generator=gen)
+        packed, _s, zero, scale = quant.quantize_int4_groups(w, GROUP, scale_dtype="bf16")
+        del w
+        xk = x[:, :K].contiguous()
+        us = _time_us(lambda: kernels.int4_linear(xk, packed, scale, zero), 10)
+        tf = 2.0 * 2048 * N * K / us / 1e6
+        out[f"int4_gemm_M2048_K{K}_N{N}"] = {"us": us, "TFLOP/s": tf, "frac_bf16_peak": tf / bf16_peak}
+    del x, packed, scale, zero
+    torch.cuda.empty_cache()
+    # bulk quantize/pack, one Llama-3-70B-shaped tensor (gate/up: 28672 x 8192, bf16 N(0, 0.015))
+    w = torch.empty(28672, 8192, device=device, dtype=torch.bfloat16).normal_(0, 0.015, generator=gen)
+    n = w.numel()
+    us = _time_us(lambda: quant.quantize_int4_groups(w, GROUP, scale_dtype="bf16"), 10)
+    b4 = n * 2 + n // 2 + (n // GROUP) * (4 + 2 + 1)
+    out["quantize_int4_g128_28672x8192"] = {"us": us, "GB/s": b4 / us / 1e3, "frac_hbm": b4 / us / 1e3 / hbm}
+    us = _time_us(lambda: quant.quantize_int8_groups(w, 8192, "f32"), 10)
+    b8 = n * 2 + n + 28672 * 4
+    out["quantize_int8_channel_28672x8192"] = {"us": us, "GB/s": b8 / us / 1e3, "frac_hbm": b8 / us / 1e3 / hbm}
+    return out
 
 
 def run_reference(args, rank: int, world: int) -> dict | None:
@@ -287,6 +360,7 @@ def main() -> None:
     parser.add_argument("--rows", type=int, default=1)
     parser.add_argument("--batch", type=int, default=1)
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-other-configs", action="store_true")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
 

@@ -82,8 +82,8 @@ int32_t b200q_int4_gemv(const void* x, const uint8_t* packed, const void* scale,
                         const uint8_t* zero, void* y, int64_t rows, int64_t in,
                         int64_t out, int64_t group, int32_t dtype, void* stream);
 
-/* The prefill kernel alone: TMA + tcgen05/TMEM dequant-GEMM (bf16, group a
- * multiple of 64, in a multiple of 64, out a multiple of 16). */
+/* The prefill kernel alone: TMA + tcgen05/TMEM dequant-GEMM (bf16; `in` and `group`
+ * multiples of 64; any rows and out). */
 int32_t b200q_int4_gemm(const void* x, const uint8_t* packed, const void* scale,
                         const uint8_t* zero, void* y, int64_t rows, int64_t in,
                         int64_t out, int64_t group, int32_t dtype, void* stream);
@@ -116,6 +116,45 @@ int32_t b200q_int8_linear(const void* x, const int8_t* w, const float* scale,
 int32_t b200q_int8_dequantize(const int8_t* w, const float* scale, void* weight,
                               int64_t out, int64_t in, int64_t group, int32_t dtype,
                               void* stream);
+
+/* ---- decode-step glue ------------------------------------------------------
+ * The small operations between the quantized linears of a decode step.  In the
+ * reference they are stdlib ops lowered to PyTorch calls inside the captured
+ * decode graph (examples/01-llama/src/lib.linnet and attention.linnet, replayed by
+ * python/linnet/src/linnet/torch/compiled.py:430-503): rms_norm, rope, the
+ * index_put_ cache write, scaled_dot_product_attention, silu * mul.  All tensors
+ * are bf16 unless stated. */
+
+/* x[rows, hidden] += delta (skipped when delta is NULL), then
+ * y = x * rsqrt(mean(x^2) + eps) * weight, computed in f32. */
+int32_t b200q_add_rmsnorm(void* x, const void* delta, const void* weight, void* y,
+                          int64_t rows, int64_t hidden, float eps, void* stream);
+
+/* qkv [batch, (nq + 2 nkv) * head_dim]: rotary embedding (halves rotated) of the
+ * query and key heads at positions[batch] (int64); queries go to q_out
+ * [batch, nq, head_dim], keys and values to cache_{k,v}[batch, nkv, max_seq,
+ * head_dim] at their position. */
+int32_t b200q_rope_cache(const void* qkv, const int64_t* positions, void* q_out,
+                         void* cache_k, void* cache_v, int64_t batch, int64_t nq,
+                         int64_t nkv, int64_t head_dim, int64_t max_seq, float theta,
+                         void* stream);
+
+/* Single-query attention of q [batch, nq, head_dim] over cache positions
+ * 0..positions[b], grouped-query (nq / nkv in 1, 2, 4, 8; head_dim 64 or 128), the
+ * keys split `splits` ways.  `scratch` is caller-owned device memory of
+ * b200q_decode_attention_scratch_bytes(...) bytes holding the splits' partial
+ * results; out is [batch, nq * head_dim]. */
+int64_t b200q_decode_attention_scratch_bytes(int64_t batch, int64_t nq, int64_t head_dim,
+                                             int64_t splits);
+int32_t b200q_decode_attention(const void* q, const void* cache_k, const void* cache_v,
+                               const int64_t* positions, void* out, void* scratch,
+                               int64_t batch, int64_t nq, int64_t nkv, int64_t head_dim,
+                               int64_t max_seq, int64_t splits, void* stream);
+
+/* out[rows, inner] = silu(gate_up[:, :inner]) * gate_up[:, inner:], silu rounded to
+ * bf16 before the product as the two PyTorch ops round. */
+int32_t b200q_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t inner,
+                       void* stream);
 
 #ifdef __cplusplus
 }

@@ -5,7 +5,7 @@ or a call fails, this raises."""
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_int32, c_int64, c_void_p
+from ctypes import c_char_p, c_float, c_int32, c_int64, c_void_p
 from pathlib import Path
 
 LIBRARY = Path(__file__).resolve().parent / "libb200q.so"
@@ -34,6 +34,13 @@ PROTOTYPES: dict[str, list] = {
                           c_int32, c_void_p],
     "b200q_int8_dequantize": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int32,
                               c_void_p],
+    "b200q_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float, c_void_p],
+    "b200q_rope_cache": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                         c_int64, c_int64, c_float, c_void_p],
+    "b200q_decode_attention_scratch_bytes": [c_int64, c_int64, c_int64, c_int64],
+    "b200q_decode_attention": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                               c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p],
+    "b200q_silu_mul": [c_void_p, c_void_p, c_int64, c_int64, c_void_p],
 }
 
 
@@ -56,7 +63,7 @@ def load() -> ctypes.CDLL:
         for name, argtypes in PROTOTYPES.items():
             fn = getattr(lib, name)
             fn.argtypes = argtypes
-            fn.restype = c_int32
+            fn.restype = c_int64 if name.endswith("_bytes") else c_int32
         lib.b200q_last_error.argtypes = []
         lib.b200q_last_error.restype = c_char_p
         if lib.b200q_abi_version() != 1:

@@ -1,0 +1,337 @@
+// The small kernels between the quantized linears of a decode step: residual add +
+// RMSNorm, rotary embedding + KV-cache write, single-query attention over the cache
+// (split over the keys, then merged) and SwiGLU's silu(gate) * up.
+//
+// In the reference these are stdlib ops lowered to PyTorch calls inside the captured
+// decode graph (rms_norm, rope, index_put_ cache write, scaled_dot_product_attention,
+// silu * mul: examples/01-llama/src/{lib,attention}.linnet run by
+// python/linnet/src/linnet/torch/compiled.py:430-503); run that way a batch-1 step on a
+// B200 spends three quarters of its time in ~50 tiny elementwise launches per layer, so
+// the decode benchmark fuses them into six launches per layer.  Arithmetic follows the
+// PyTorch ops (f32 math on bf16 values, one rounding where PyTorch rounds).
+#include "common.cuh"
+
+namespace b200q {
+namespace {
+
+__device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
+__device__ __forceinline__ uint32_t bf16_pack(float lo, float hi) {
+    __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&p);
+}
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// ---- x (+= delta); y = rms_norm(x) * w --------------------------------------------
+// One block per row; hidden is a multiple of 8.  x is updated in place when delta != null.
+__global__ void __launch_bounds__(256)
+add_rmsnorm_kernel(uint16_t* __restrict__ x, const uint16_t* __restrict__ delta,
+                   const uint16_t* __restrict__ w, uint16_t* __restrict__ y, int hidden, float eps) {
+    __shared__ float partial[8];
+    const int row = blockIdx.x, chunks = hidden / 8;
+    uint4* xr = reinterpret_cast<uint4*>(x + size_t(row) * hidden);
+    const uint4* dr = delta ? reinterpret_cast<const uint4*>(delta + size_t(row) * hidden) : nullptr;
+    float sum = 0.0f;
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+        uint4 v = xr[c];
+        if (dr) {
+            const uint4 d = dr[c];
+            v.x = bf16_pack(bf16_lo(v.x) + bf16_lo(d.x), bf16_hi(v.x) + bf16_hi(d.x));
+            v.y = bf16_pack(bf16_lo(v.y) + bf16_lo(d.y), bf16_hi(v.y) + bf16_hi(d.y));
+            v.z = bf16_pack(bf16_lo(v.z) + bf16_lo(d.z), bf16_hi(v.z) + bf16_hi(d.z));
+            v.w = bf16_pack(bf16_lo(v.w) + bf16_lo(d.w), bf16_hi(v.w) + bf16_hi(d.w));
+            xr[c] = v;
+        }
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sum += bf16_lo(u[i]) * bf16_lo(u[i]) + bf16_hi(u[i]) * bf16_hi(u[i]);
+    }
+    for (int d = 16; d >= 1; d >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, d);
+    if (threadIdx.x % 32 == 0) partial[threadIdx.x / 32] = sum;
+    __syncthreads();
+    float total = 0.0f;
+    for (int i = 0; i < int(blockDim.x) / 32; ++i) total += partial[i];
+    const float rstd = rsqrtf(total / float(hidden) + eps);
+    const uint4* wr = reinterpret_cast<const uint4*>(w);
+    uint4* yr = reinterpret_cast<uint4*>(y + size_t(row) * hidden);
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+        const uint4 v = xr[c], g = wr[c];
+        uint4 o;
+        o.x = bf16_pack(bf16_lo(v.x) * rstd * bf16_lo(g.x), bf16_hi(v.x) * rstd * bf16_hi(g.x));
+        o.y = bf16_pack(bf16_lo(v.y) * rstd * bf16_lo(g.y), bf16_hi(v.y) * rstd * bf16_hi(g.y));
+        o.z = bf16_pack(bf16_lo(v.z) * rstd * bf16_lo(g.z), bf16_hi(v.z) * rstd * bf16_hi(g.z));
+        o.w = bf16_pack(bf16_lo(v.w) * rstd * bf16_lo(g.w), bf16_hi(v.w) * rstd * bf16_hi(g.w));
+        yr[c] = o;
+    }
+}
+
+// ---- rotary embedding of q and k, cache write of k and v -----------------------------
+// qkv [B, (nq + 2 nkv) * hd]; q_out [B, nq, hd]; cache_{k,v} [B, nkv, S, hd]; halves rotated.
+__global__ void rope_cache_kernel(const uint16_t* __restrict__ qkv, const int64_t* __restrict__ positions,
+                                  uint16_t* __restrict__ q_out, uint16_t* __restrict__ cache_k,
+                                  uint16_t* __restrict__ cache_v, int nq, int nkv, int hd, int S,
+                                  float theta) {
+    const int b = blockIdx.y, head = blockIdx.x;  // head < nq: q; < nq + nkv: k; else v
+    const int half = hd / 2;
+    const int64_t pos = positions[b];
+    const uint16_t* src = qkv + (size_t(b) * (nq + 2 * nkv) + head) * hd;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        if (head < nq + nkv) {
+            const float freq = powf(theta, -float(i) / float(half));
+            float s, c;
+            sincosf(float(pos) * freq, &s, &c);
+            const float a = bf16_lo(src[i]), bb = bf16_lo(src[i + half]);
+            const uint16_t lo = uint16_t(bf16_pack(a * c - bb * s, 0.0f) & 0xFFFF);
+            const uint16_t hi = uint16_t(bf16_pack(bb * c + a * s, 0.0f) & 0xFFFF);
+            uint16_t* dst = head < nq ? q_out + (size_t(b) * nq + head) * hd
+                                      : cache_k + ((size_t(b) * nkv + (head - nq)) * S + pos) * hd;
+            dst[i] = lo;
+            dst[i + half] = hi;
+        } else {
+            uint16_t* dst = cache_v + ((size_t(b) * nkv + (head - nq - nkv)) * S + pos) * hd;
+            dst[i] = src[i];
+            dst[i + half] = src[i + half];
+        }
+    }
+}
+
+// ---- single-query attention, split over the keys --------------------------------------
+// Block (split, kv head, batch row): 4 warps; a group of HD/16 lanes owns one key at a time
+// (16 elements a lane) and keeps its own running softmax for the REP query heads that
+// share the KV head; groups, warps and finally splits are merged with the usual
+// (max, sum, weighted accumulator) rule.  partial: [B, nq, splits, HD + 2] f32.
+template <int HD, int REP>
+__global__ void __launch_bounds__(128)
+attention_partial_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ cache_k,
+                         const uint16_t* __restrict__ cache_v, const int64_t* __restrict__ positions,
+                         float* __restrict__ partial, int nq, int nkv, int S, int splits, float scale) {
+    constexpr int LPK = HD / 16;     // lanes per key
+    constexpr int KPW = 32 / LPK;    // keys per warp step
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+    const int sub = lane / LPK, part = lane % LPK;  // key slot of the warp step, slice of the head
+    const int keys = int(positions[b]) + 1;          // attend to positions 0 .. pos
+    const int per_split = (keys + splits - 1) / splits;
+    const int k0 = split * per_split, k1 = min(k0 + per_split, keys);
+
+    float qv[REP][16];
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+        const uint4* qp = reinterpret_cast<const uint4*>(q + (size_t(b) * nq + kvh * REP + r) * HD + part * 16);
+        const uint4 lo = qp[0], hi = qp[1];
+        const uint32_t u[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            qv[r][2 * i] = bf16_lo(u[i]) * scale;
+            qv[r][2 * i + 1] = bf16_hi(u[i]) * scale;
+        }
+    }
+    float m[REP], l[REP], acc[REP][16];
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+        m[r] = -INFINITY;
+        l[r] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[r][i] = 0.0f;
+    }
+    const size_t base = (size_t(b) * nkv + kvh) * S * HD + part * 16;
+    for (int s0 = k0 + warp * KPW; s0 < k1; s0 += 4 * KPW) {
+        const int s = s0 + sub;
+        const bool live = s < k1;
+        uint4 ka = make_uint4(0, 0, 0, 0), kb = ka, va = ka, vb = ka;
+        if (live) {
+            const uint4* kp = reinterpret_cast<const uint4*>(cache_k + base + size_t(s) * HD);
+            const uint4* vp = reinterpret_cast<const uint4*>(cache_v + base + size_t(s) * HD);
+            ka = ldg_stream(kp); kb = ldg_stream(kp + 1);
+            va = ldg_stream(vp); vb = ldg_stream(vp + 1);
+        }
+        const uint32_t ku[8] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w};
+        const uint32_t vu[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+        for (int r = 0; r < REP; ++r) {
+            float dot = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                dot += qv[r][2 * i] * bf16_lo(ku[i]) + qv[r][2 * i + 1] * bf16_hi(ku[i]);
+#pragma unroll
+            for (int d = LPK / 2; d >= 1; d >>= 1) dot += __shfl_xor_sync(0xFFFFFFFFu, dot, d);
+            if (live) {
+                const float m_new = fmaxf(m[r], dot);
+                const float corr = __expf(m[r] - m_new), p = __expf(dot - m_new);
+                m[r] = m_new;
+                l[r] = l[r] * corr + p;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    acc[r][2 * i] = acc[r][2 * i] * corr + p * bf16_lo(vu[i]);
+                    acc[r][2 * i + 1] = acc[r][2 * i + 1] * corr + p * bf16_hi(vu[i]);
+                }
+            }
+        }
+    }
+    // Merge the key slots of the warp (lanes with the same `part`).
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+#pragma unroll
+        for (int d = LPK; d < 32; d <<= 1) {
+            const float m_o = __shfl_xor_sync(0xFFFFFFFFu, m[r], d);
+            const float l_o = __shfl_xor_sync(0xFFFFFFFFu, l[r], d);
+            const float m_new = fmaxf(m[r], m_o);
+            const float c_s = m[r] == -INFINITY ? 0.0f : __expf(m[r] - m_new);
+            const float c_o = m_o == -INFINITY ? 0.0f : __expf(m_o - m_new);
+            l[r] = l[r] * c_s + l_o * c_o;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float a_o = __shfl_xor_sync(0xFFFFFFFFu, acc[r][i], d);
+                acc[r][i] = acc[r][i] * c_s + a_o * c_o;
+            }
+            m[r] = m_new;
+        }
+    }
+    // Merge the four warps through shared memory.
+    __shared__ float sm_m[4][REP], sm_l[4][REP], sm_acc[4][REP][HD];
+    if (sub == 0) {
+#pragma unroll
+        for (int r = 0; r < REP; ++r) {
+            if (part == 0) {
+                sm_m[warp][r] = m[r];
+                sm_l[warp][r] = l[r];
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) sm_acc[warp][r][part * 16 + i] = acc[r][i];
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < REP * HD; e += blockDim.x) {
+        const int r = e / HD, dcol = e % HD;
+        float m_all = sm_m[0][r];
+        for (int w = 1; w < 4; ++w) m_all = fmaxf(m_all, sm_m[w][r]);
+        float l_all = 0.0f, a_all = 0.0f;
+        for (int w = 0; w < 4; ++w) {
+            const float c = sm_m[w][r] == -INFINITY ? 0.0f : __expf(sm_m[w][r] - m_all);
+            l_all += sm_l[w][r] * c;
+            a_all += sm_acc[w][r][dcol] * c;
+        }
+        float* out = partial + ((size_t(b) * nq + kvh * REP + r) * splits + split) * (HD + 2);
+        out[dcol] = a_all;
+        if (dcol == 0) {
+            out[HD] = m_all;
+            out[HD + 1] = l_all;
+        }
+    }
+}
+
+template <int HD>
+__global__ void attention_merge_kernel(const float* __restrict__ partial, uint16_t* __restrict__ out,
+                                       int splits) {
+    const size_t head = blockIdx.x;  // b * nq + query head
+    const float* p = partial + head * splits * (HD + 2);
+    float m_all = -INFINITY;
+    for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, p[s * (HD + 2) + HD]);
+    for (int dcol = threadIdx.x; dcol < HD; dcol += blockDim.x) {
+        float l_all = 0.0f, a_all = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = p[s * (HD + 2) + HD];
+            const float c = ms == -INFINITY ? 0.0f : __expf(ms - m_all);
+            l_all += p[s * (HD + 2) + HD + 1] * c;
+            a_all += p[s * (HD + 2) + dcol] * c;
+        }
+        out[head * HD + dcol] = uint16_t(bf16_pack(a_all / l_all, 0.0f) & 0xFFFF);
+    }
+}
+
+// ---- silu(gate) * up ---------------------------------------------------------------------
+// gate_up [B, 2 I] -> out [B, I]; silu is rounded to bf16 before the product, as the two
+// PyTorch ops do.
+__global__ void silu_mul_kernel(const uint16_t* __restrict__ gate_up, uint16_t* __restrict__ out,
+                                int inner, int64_t total) {
+    for (int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
+         e += int64_t(gridDim.x) * blockDim.x) {
+        const int64_t row = e / inner, col = e % inner;
+        const float g = bf16_lo(gate_up[row * 2 * inner + col]);
+        const float u = bf16_lo(gate_up[row * 2 * inner + inner + col]);
+        const float s = bf16_round(g / (1.0f + expf(-g)));
+        out[e] = uint16_t(bf16_pack(s * u, 0.0f) & 0xFFFF);
+    }
+}
+
+}  // namespace
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" int32_t b200q_add_rmsnorm(void* x, const void* delta, const void* weight, void* y,
+                                     int64_t rows, int64_t hidden, float eps, void* stream) {
+    B200Q_REQUIRE(rows >= 0 && hidden > 0 && hidden % 8 == 0, "add_rmsnorm: hidden must be a multiple of 8");
+    if (rows == 0) return B200Q_OK;
+    B200Q_REQUIRE(x && weight && y && aligned(x, 16) && aligned(weight, 16) && aligned(y, 16) &&
+                      (!delta || aligned(delta, 16)),
+                  "add_rmsnorm: tensors must be 16-byte aligned");
+    add_rmsnorm_kernel<<<unsigned(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<uint16_t*>(x), static_cast<const uint16_t*>(delta), static_cast<const uint16_t*>(weight),
+        static_cast<uint16_t*>(y), int(hidden), eps);
+    return launched("add_rmsnorm");
+}
+
+extern "C" int32_t b200q_rope_cache(const void* qkv, const int64_t* positions, void* q_out, void* cache_k,
+                                    void* cache_v, int64_t batch, int64_t nq, int64_t nkv, int64_t head_dim,
+                                    int64_t max_seq, float theta, void* stream) {
+    B200Q_REQUIRE(batch >= 0 && nq > 0 && nkv > 0 && head_dim % 2 == 0, "rope_cache: bad shape");
+    if (batch == 0) return B200Q_OK;
+    rope_cache_kernel<<<dim3(unsigned(nq + 2 * nkv), unsigned(batch)), 64, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t*>(qkv), positions, static_cast<uint16_t*>(q_out),
+        static_cast<uint16_t*>(cache_k), static_cast<uint16_t*>(cache_v), int(nq), int(nkv), int(head_dim),
+        int(max_seq), theta);
+    return launched("rope_cache");
+}
+
+extern "C" int64_t b200q_decode_attention_scratch_bytes(int64_t batch, int64_t nq, int64_t head_dim,
+                                                        int64_t splits) {
+    return batch * nq * splits * (head_dim + 2) * 4;
+}
+
+extern "C" int32_t b200q_decode_attention(const void* q, const void* cache_k, const void* cache_v,
+                                          const int64_t* positions, void* out, void* scratch,
+                                          int64_t batch, int64_t nq, int64_t nkv, int64_t head_dim,
+                                          int64_t max_seq, int64_t splits, void* stream) {
+    B200Q_REQUIRE(batch >= 0 && nq > 0 && nkv > 0 && nq % nkv == 0 && splits >= 1 && splits <= 65535,
+                  "decode_attention: bad shape");
+    if (batch == 0) return B200Q_OK;
+    const int rep = int(nq / nkv);
+    B200Q_REQUIRE((head_dim == 128 || head_dim == 64) && (rep == 1 || rep == 2 || rep == 4 || rep == 8),
+                  "decode_attention: head_dim is 64 or 128 and heads / kv_heads is 1, 2, 4 or 8");
+    B200Q_REQUIRE(q && cache_k && cache_v && positions && out && scratch && aligned(q, 16) &&
+                      aligned(cache_k, 16) && aligned(cache_v, 16) && aligned(scratch, 16),
+                  "decode_attention: tensors must be 16-byte aligned");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const dim3 grid{unsigned(splits), unsigned(nkv), unsigned(batch)};
+    const float scale = 1.0f / sqrtf(float(head_dim));
+#define B200Q_ATTN(HD, REP)                                                                           \
+    attention_partial_kernel<HD, REP><<<grid, 128, 0, s>>>(                                           \
+        static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(cache_k),                       \
+        static_cast<const uint16_t*>(cache_v), positions, static_cast<float*>(scratch), int(nq),      \
+        int(nkv), int(max_seq), int(splits), scale)
+    if (head_dim == 128) {
+        if (rep == 1) B200Q_ATTN(128, 1); else if (rep == 2) B200Q_ATTN(128, 2);
+        else if (rep == 4) B200Q_ATTN(128, 4); else B200Q_ATTN(128, 8);
+        attention_merge_kernel<128><<<unsigned(batch * nq), 128, 0, s>>>(
+            static_cast<const float*>(scratch), static_cast<uint16_t*>(out), int(splits));
+    } else {
+        if (rep == 1) B200Q_ATTN(64, 1); else if (rep == 2) B200Q_ATTN(64, 2);
+        else if (rep == 4) B200Q_ATTN(64, 4); else B200Q_ATTN(64, 8);
+        attention_merge_kernel<64><<<unsigned(batch * nq), 64, 0, s>>>(
+            static_cast<const float*>(scratch), static_cast<uint16_t*>(out), int(splits));
+    }
+#undef B200Q_ATTN
+    return launched("decode_attention");
+}
+
+extern "C" int32_t b200q_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t inner, void* stream) {
+    B200Q_REQUIRE(rows >= 0 && inner > 0, "silu_mul: bad shape");
+    const int64_t total = rows * inner;
+    if (total == 0) return B200Q_OK;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > int64_t(sm_count()) * 16) blocks = int64_t(sm_count()) * 16;
+    silu_mul_kernel<<<unsigned(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t*>(gate_up), static_cast<uint16_t*>(out), int(inner), total);
+    return launched("silu_mul");
+}

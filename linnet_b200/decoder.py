@@ -15,9 +15,12 @@ the packed layout makes it a concatenation along the output axis.
 
 The linear operator is injected (`linear=`): the product passes the CUDA operator, the
 CPU tests pass the oracle, so the sharding and the collectives are exercised on `gloo`
-ranks without a GPU.  Everything between the linears (RMSNorm, rotary embedding, cache
-write, attention, SwiGLU) is plain PyTorch, recorded with the linears into one CUDA graph
-per batch size, which is how the reference's serving engine replays a decode step
+ranks without a GPU.  Between the linears (RMSNorm, rotary embedding, cache write,
+attention, SwiGLU) `step` has two routes with the same arithmetic: plain PyTorch ops (any
+device; what the reference's generated source does, and what the CPU tests run) and, on a
+GPU, the fused kernels of `linnet_b200.glue` (six launches a layer instead of about fifty).
+Either way a step is recorded into one CUDA graph per batch size, which is how the
+reference's serving engine replays a decode step
 (python/linnet/src/linnet/torch/compiled.py:430-503).
 """
 
@@ -129,8 +132,10 @@ class Int4Decoder:
 
     def __init__(self, cfg: DecoderConfig, layers: list[LayerWeights], embed: torch.Tensor,
                  final_norm: torch.Tensor, head: Int4, *, linear: Linear, rank: int = 0, tp: int = 1,
-                 group: "dist.ProcessGroup | None" = None) -> None:
+                 group: "dist.ProcessGroup | None" = None, fused: bool | None = None) -> None:
         check_tp(cfg, tp)
+        # Fused glue kernels by default wherever the model lives on a GPU.
+        self.fused = embed.is_cuda if fused is None else fused
         self.cfg, self.layers, self.embed, self.final_norm, self.head = cfg, layers, embed, final_norm, head
         self.linear, self.rank, self.tp, self.group = linear, rank, tp, group
         self.cache_k: list[torch.Tensor] = []
@@ -169,6 +174,30 @@ class Int4Decoder:
 
     # -- one decode step -----------------------------------------------------------
     def step(self, tokens: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        if self.fused:
+            return self._step_fused(tokens, positions)
+        return self._step_torch(tokens, positions)
+
+    def _step_fused(self, tokens: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        from . import glue
+
+        cfg, tp = self.cfg, self.tp
+        nq, nkv = cfg.heads // tp, cfg.kv_heads // tp
+        x = self.embed[tokens]           # the residual stream, updated in place
+        delta = None                     # what the previous sub-layer adds to it
+        for i, w in enumerate(self.layers):
+            h = glue.add_rmsnorm(x, delta, w.norm1, cfg.eps)
+            qkv = self.linear(h, *w.qkv)
+            q = glue.rope_cache(qkv, positions, self.cache_k[i], self.cache_v[i], nq, nkv, cfg.rope_theta)
+            attn = glue.decode_attention(q, self.cache_k[i], self.cache_v[i], positions)
+            delta = self._all_reduce(self.linear(attn, *w.o))
+            h = glue.add_rmsnorm(x, delta, w.norm2, cfg.eps)
+            act = glue.silu_mul(self.linear(h, *w.gate_up))
+            delta = self._all_reduce(self.linear(act, *w.down))
+        h = glue.add_rmsnorm(x, delta, self.final_norm, cfg.eps)
+        return self._all_gather(self.linear(h, *self.head))
+
+    def _step_torch(self, tokens: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         cfg, tp = self.cfg, self.tp
         nq, nkv, hd = cfg.heads // tp, cfg.kv_heads // tp, cfg.head_dim
         batch = tokens.shape[0]

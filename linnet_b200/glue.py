@@ -1,0 +1,78 @@
+"""PyTorch-facing wrappers of the decode-step glue kernels (`csrc/decoder_glue.cu`):
+residual add + RMSNorm, rotary embedding + KV-cache write, single-query attention over
+the cache, and SwiGLU's `silu(gate) * up`.  bf16 CUDA tensors only; launches go to the
+current stream and record into CUDA graphs."""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _bf16(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if not t.is_cuda or t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise RuntimeError("glue kernels take contiguous bf16 CUDA tensors")
+
+
+def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """`x += delta` in place (when given), returns `rms_norm(x) * weight`."""
+    _bf16(x, weight, *([] if delta is None else [delta]))
+    rows, hidden = x.shape
+    y = torch.empty_like(x)
+    _lib.check(_lib.load().b200q_add_rmsnorm(x.data_ptr(), None if delta is None else delta.data_ptr(),
+                                             weight.data_ptr(), y.data_ptr(), rows, hidden, eps, _stream(x)))
+    return y
+
+
+def rope_cache(qkv: torch.Tensor, positions: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor,
+               nq: int, nkv: int, theta: float) -> torch.Tensor:
+    """Rotates q and k of `qkv` [B, (nq + 2 nkv) * D], writes k and v into the caches
+    [B, nkv, S, D] at `positions` and returns q [B, nq, D]."""
+    _bf16(qkv, cache_k, cache_v)
+    batch = qkv.shape[0]
+    _, _, max_seq, hd = cache_k.shape
+    q = torch.empty(batch, nq, hd, device=qkv.device, dtype=qkv.dtype)
+    _lib.check(_lib.load().b200q_rope_cache(qkv.data_ptr(), positions.data_ptr(), q.data_ptr(),
+                                            cache_k.data_ptr(), cache_v.data_ptr(), batch, nq, nkv, hd,
+                                            max_seq, theta, _stream(qkv)))
+    return q
+
+
+def attention_splits(batch: int, nkv: int, max_seq: int, sms: int = 148) -> int:
+    """Key splits so that about two blocks per multiprocessor are in flight."""
+    want = max(1, (2 * sms) // max(1, batch * nkv))
+    return max(1, min(want, max_seq // 64, 64))
+
+
+def decode_attention(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor,
+                     positions: torch.Tensor, splits: int | None = None) -> torch.Tensor:
+    """Attention of one query per row, q [B, nq, D], over cache positions 0..positions[b];
+    returns [B, nq * D]."""
+    _bf16(q, cache_k, cache_v)
+    batch, nq, hd = q.shape
+    _, nkv, max_seq, _ = cache_k.shape
+    if splits is None:
+        splits = attention_splits(batch, nkv, max_seq)
+    lib = _lib.load()
+    scratch = torch.empty(lib.b200q_decode_attention_scratch_bytes(batch, nq, hd, splits), dtype=torch.uint8,
+                          device=q.device)
+    out = torch.empty(batch, nq * hd, device=q.device, dtype=q.dtype)
+    _lib.check(lib.b200q_decode_attention(q.data_ptr(), cache_k.data_ptr(), cache_v.data_ptr(),
+                                          positions.data_ptr(), out.data_ptr(), scratch.data_ptr(), batch, nq,
+                                          nkv, hd, max_seq, splits, _stream(q)))
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """`silu(gate_up[:, :I]) * gate_up[:, I:]` for gate_up [B, 2 I]."""
+    _bf16(gate_up)
+    rows, width = gate_up.shape
+    out = torch.empty(rows, width // 2, device=gate_up.device, dtype=gate_up.dtype)
+    _lib.check(_lib.load().b200q_silu_mul(gate_up.data_ptr(), out.data_ptr(), rows, width // 2, _stream(gate_up)))
+    return out

@@ -131,6 +131,63 @@ def test_gpu_decoder_matches_cpu_oracle_decoder():
 
 
 @pytest.mark.gpu
+def test_fused_glue_equals_torch_glue():
+    """The fused kernels between the linears against the PyTorch ops they replace."""
+    from linnet_b200 import glue, kernels
+
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator().manual_seed(5)
+    for hidden, rows in ((4096, 1), (256, 5), (1024, 64)):
+        x = torch.randn(rows, hidden, generator=gen).to(torch.bfloat16).to(dev)
+        d = torch.randn(rows, hidden, generator=gen).to(torch.bfloat16).to(dev)
+        w = (1 + 0.1 * torch.randn(hidden, generator=gen)).to(torch.bfloat16).to(dev)
+        want_x = x + d
+        want = torch.nn.functional.rms_norm(want_x, (hidden,), w, 1e-5)
+        got = glue.add_rmsnorm(x, d, w, 1e-5)
+        assert torch.equal(x, want_x)
+        torch.testing.assert_close(got.float(), want.float(), rtol=1e-2, atol=1e-2)
+        gu = torch.randn(rows, 2 * hidden, generator=gen).to(torch.bfloat16).to(dev)
+        want = torch.nn.functional.silu(gu[:, :hidden]) * gu[:, hidden:]
+        torch.testing.assert_close(glue.silu_mul(gu).float(), want.float(), rtol=1e-2, atol=1e-2)
+    for nq, nkv, hd, S, batch in ((32, 8, 128, 2048, 1), (4, 2, 64, 32, 3), (8, 8, 128, 300, 2), (16, 2, 64, 128, 5)):
+        qkv = torch.randn(batch, (nq + 2 * nkv) * hd, generator=gen).to(torch.bfloat16).to(dev)
+        ck = torch.randn(batch, nkv, S, hd, generator=gen).to(torch.bfloat16).to(dev)
+        cv = torch.randn(batch, nkv, S, hd, generator=gen).to(torch.bfloat16).to(dev)
+        pos = torch.randint(0, S, (batch,), generator=gen).to(dev)
+        pos[0] = S - 1
+        ck2, cv2 = ck.clone(), cv.clone()
+        q, k, v = qkv.split([nq * hd, nkv * hd, nkv * hd], dim=-1)
+        q_ref = dec.rotary(q.reshape(batch, nq, hd), pos, 500000.0)
+        rows_i = torch.arange(batch, device=dev)
+        ck2[rows_i, :, pos] = dec.rotary(k.reshape(batch, nkv, hd), pos, 500000.0)
+        cv2[rows_i, :, pos] = v.reshape(batch, nkv, hd)
+        q_got = glue.rope_cache(qkv, pos, ck, cv, nq, nkv, 500000.0)
+        torch.testing.assert_close(q_got.float(), q_ref.float(), rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(ck.float(), ck2.float(), rtol=2e-2, atol=2e-2)
+        assert torch.equal(cv, cv2)
+        mask = (torch.arange(S, device=dev)[None, :] <= pos[:, None])[:, None, None, :]
+        want = torch.nn.functional.scaled_dot_product_attention(
+            q_ref[:, :, None, :], ck2, cv2, attn_mask=mask, enable_gqa=True).reshape(batch, nq * hd)
+        for splits in (None, 1, 3):
+            got = glue.decode_attention(q_ref, ck2, cv2, pos, splits)
+            torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.gpu
+def test_fused_and_torch_steps_agree():
+    from linnet_b200 import kernels
+
+    cfg = dec.DecoderConfig.tiny()
+    whole = du.whole_model(cfg)
+    outs = []
+    for fused in (True, False):
+        model = du.rank_model(cfg, whole, 0, 1, kernels.int4_linear, device="cuda")
+        model.fused = fused
+        outs.append(du.run_steps(model, cfg, batch=4, steps=3, device="cuda").float())
+    torch.testing.assert_close(outs[0], outs[1], rtol=3e-2, atol=3e-2 * outs[1].abs().max().item())
+
+
+@pytest.mark.gpu
 def test_gpu_decoder_graph_replay():
     from linnet_b200 import kernels, quant
 
