@@ -381,6 +381,7 @@ def main() -> None:
     if world > 1:
         import torch.distributed as dist
 
+        os.environ.pop("NCCL_DEBUG", None)  # its banner would share stdout with the JSON line
         dist.init_process_group("nccl", device_id=device)
 
         def barrier() -> None:
