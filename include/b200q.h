@@ -151,6 +151,26 @@ int32_t b200q_decode_attention(const void* q, const void* cache_k, const void* c
                                int64_t batch, int64_t nq, int64_t nkv, int64_t head_dim,
                                int64_t max_seq, int64_t splits, void* stream);
 
+/* b200q_decode_attention for hosts that cannot give it scratch memory (a runtime with a
+ * fixed arena, a plug-in without access to the allocator, a caller inside a stream
+ * capture): the partial results go to a 4 MiB array built into the library, which every
+ * GPU that loads the library holds until the process exits.  It has no counterpart in
+ * the reference.  Same arguments and result as b200q_decode_attention without `scratch`.
+ *   - Fails with B200Q_ERROR when b200q_decode_attention_scratch_bytes(batch, nq,
+ *     head_dim, splits) exceeds b200q_decode_attention_static_scratch_limit().
+ *   - The first call on each device looks the array's address up (one runtime query, no
+ *     allocation); make that first call before you begin capturing a stream.
+ *   - All calls share the one array and it keeps the previous call's contents (nothing in
+ *     it needs clearing: every partial result read was written by the same call), so two
+ *     calls whose kernels overlap on the GPU -- different streams, or graphs replayed
+ *     side by side -- race; keep them ordered.
+ *   - Allocates nothing, frees nothing. */
+int64_t b200q_decode_attention_static_scratch_limit(void);
+int32_t b200q_decode_attention_static(const void* q, const void* cache_k, const void* cache_v,
+                                      const int64_t* positions, void* out, int64_t batch,
+                                      int64_t nq, int64_t nkv, int64_t head_dim, int64_t max_seq,
+                                      int64_t splits, void* stream);
+
 /* out[rows, inner] = silu(gate_up[:, :inner]) * gate_up[:, inner:], silu rounded to
  * bf16 before the product as the two PyTorch ops round. */
 int32_t b200q_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t inner,

@@ -40,6 +40,9 @@ PROTOTYPES: dict[str, list] = {
     "b200q_decode_attention_scratch_bytes": [c_int64, c_int64, c_int64, c_int64],
     "b200q_decode_attention": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p],
+    "b200q_decode_attention_static_scratch_limit": [],
+    "b200q_decode_attention_static": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                      c_int64, c_int64, c_int64, c_int64, c_void_p],
     "b200q_silu_mul": [c_void_p, c_void_p, c_int64, c_int64, c_void_p],
 }
 
@@ -63,7 +66,7 @@ def load() -> ctypes.CDLL:
         for name, argtypes in PROTOTYPES.items():
             fn = getattr(lib, name)
             fn.argtypes = argtypes
-            fn.restype = c_int64 if name.endswith("_bytes") else c_int32
+            fn.restype = c_int64 if name.endswith(("_bytes", "_limit")) else c_int32
         lib.b200q_last_error.argtypes = []
         lib.b200q_last_error.restype = c_char_p
         if lib.b200q_abi_version() != 1:

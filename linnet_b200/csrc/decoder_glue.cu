@@ -289,19 +289,21 @@ extern "C" int64_t b200q_decode_attention_scratch_bytes(int64_t batch, int64_t n
     return batch * nq * splits * (head_dim + 2) * 4;
 }
 
-extern "C" int32_t b200q_decode_attention(const void* q, const void* cache_k, const void* cache_v,
-                                          const int64_t* positions, void* out, void* scratch,
-                                          int64_t batch, int64_t nq, int64_t nkv, int64_t head_dim,
-                                          int64_t max_seq, int64_t splits, void* stream) {
+namespace b200q {
+namespace {
+
+int32_t launch_attention(const char* who, const void* q, const void* cache_k, const void* cache_v,
+                         const int64_t* positions, void* out, void* scratch, int64_t batch, int64_t nq,
+                         int64_t nkv, int64_t head_dim, int64_t max_seq, int64_t splits, void* stream) {
     B200Q_REQUIRE(batch >= 0 && nq > 0 && nkv > 0 && nq % nkv == 0 && splits >= 1 && splits <= 65535,
-                  "decode_attention: bad shape");
+                  "%s: bad shape", who);
     if (batch == 0) return B200Q_OK;
     const int rep = int(nq / nkv);
     B200Q_REQUIRE((head_dim == 128 || head_dim == 64) && (rep == 1 || rep == 2 || rep == 4 || rep == 8),
-                  "decode_attention: head_dim is 64 or 128 and heads / kv_heads is 1, 2, 4 or 8");
+                  "%s: head_dim is 64 or 128 and heads / kv_heads is 1, 2, 4 or 8", who);
     B200Q_REQUIRE(q && cache_k && cache_v && positions && out && scratch && aligned(q, 16) &&
                       aligned(cache_k, 16) && aligned(cache_v, 16) && aligned(scratch, 16),
-                  "decode_attention: tensors must be 16-byte aligned");
+                  "%s: tensors must be 16-byte aligned", who);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const dim3 grid{unsigned(splits), unsigned(nkv), unsigned(batch)};
     const float scale = 1.0f / sqrtf(float(head_dim));
@@ -322,7 +324,70 @@ extern "C" int32_t b200q_decode_attention(const void* q, const void* cache_k, co
             static_cast<const float*>(scratch), static_cast<uint16_t*>(out), int(splits));
     }
 #undef B200Q_ATTN
-    return launched("decode_attention");
+    return launched(who);
+}
+
+}  // namespace
+}  // namespace b200q
+
+extern "C" int32_t b200q_decode_attention(const void* q, const void* cache_k, const void* cache_v,
+                                          const int64_t* positions, void* out, void* scratch,
+                                          int64_t batch, int64_t nq, int64_t nkv, int64_t head_dim,
+                                          int64_t max_seq, int64_t splits, void* stream) {
+    return launch_attention("decode_attention", q, cache_k, cache_v, positions, out, scratch, batch, nq,
+                            nkv, head_dim, max_seq, splits, stream);
+}
+
+// ---- the same attention for callers that cannot allocate device memory ----------------
+// Some hosts of this library have no way to hand it scratch memory: a runtime that owns a
+// fixed arena sized before the model is known, a plug-in loaded into a server whose
+// allocator is off limits to it, code running while a stream is being captured (no
+// cudaMalloc there).  For them the splits' partial results live in a fixed array inside
+// the library image instead: 4 MiB that every GPU which loads the library keeps until
+// the process exits.
+constexpr int64_t kStaticScratchBytes = int64_t(4) << 20;
+static __device__ __align__(256) unsigned char g_attention_scratch[kStaticScratchBytes];
+
+namespace b200q {
+namespace {
+
+// In host code `g_attention_scratch` is only a handle for the runtime, not a device
+// address; the address is asked for once per device, with that device current.
+void* static_scratch_address() {
+    static void* cached[64] = {nullptr};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return nullptr;
+    if (cached[device] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_attention_scratch) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        cached[device] = p;
+    }
+    return cached[device];
+}
+
+}  // namespace
+}  // namespace b200q
+
+extern "C" int64_t b200q_decode_attention_static_scratch_limit(void) { return kStaticScratchBytes; }
+
+extern "C" int32_t b200q_decode_attention_static(const void* q, const void* cache_k, const void* cache_v,
+                                                 const int64_t* positions, void* out, int64_t batch,
+                                                 int64_t nq, int64_t nkv, int64_t head_dim, int64_t max_seq,
+                                                 int64_t splits, void* stream) {
+    B200Q_REQUIRE(batch >= 0 && nq > 0 && head_dim > 0 && splits >= 1, "decode_attention_static: bad shape");
+    const int64_t need = b200q_decode_attention_scratch_bytes(batch, nq, head_dim, splits);
+    B200Q_REQUIRE(need <= kStaticScratchBytes,
+                  "decode_attention_static: batch %lld x %lld heads x %lld splits needs %lld bytes of scratch, "
+                  "the built-in array holds %lld; use fewer splits or b200q_decode_attention with your own scratch",
+                  (long long)batch, (long long)nq, (long long)splits, (long long)need,
+                  (long long)kStaticScratchBytes);
+    void* scratch = static_scratch_address();
+    B200Q_REQUIRE(scratch != nullptr, "decode_attention_static: cudaGetSymbolAddress failed on this device");
+    return launch_attention("decode_attention_static", q, cache_k, cache_v, positions, out, scratch, batch, nq,
+                            nkv, head_dim, max_seq, splits, stream);
 }
 
 extern "C" int32_t b200q_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t inner, void* stream) {
