@@ -247,14 +247,24 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
             const uint8_t* src = a.packed + size_t(n) * (a.K / 2) + half * 16;
             const uint16_t* srow = a.scale + size_t(n) * groups;
             const uint8_t* zrow = a.zero + size_t(n) * groups;
+            // This thread's loads for its next stage are issued one stage ahead, so the
+            // L2 latency of the packed weights hides behind the previous stage's arithmetic.
+            auto fetch = [&](int ks, uint4& q, uint32_t& sc, uint32_t& bias) {
+                q = __ldg(reinterpret_cast<const uint4*>(src + size_t(ks) * (kBK / 2)));
+                const int grp = (ks * kBK) / a.G;
+                sc = uint32_t(__ldg(srow + grp)) * 0x00010001u;
+                bias = 0x43004300u + uint32_t(__ldg(zrow + grp)) * 0x00010001u;
+            };
+            const int first = int((group_id + kDequantGroups - it % kDequantGroups) % kDequantGroups);
+            uint4 q_next = make_uint4(0, 0, 0, 0);
+            uint32_t sc_next = 0, bias_next = 0;
+            if (first < ksteps) fetch(first, q_next, sc_next, bias_next);
             for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
                 if (int(it % kDequantGroups) != group_id) continue;  // the other group's stage
                 const int s = it % kStages;
-                // Issue the loads before waiting for the stage to drain.
-                const uint4 q = __ldg(reinterpret_cast<const uint4*>(src + size_t(ks) * (kBK / 2)));
-                const int grp = (ks * kBK) / a.G;
-                const uint32_t sc = uint32_t(__ldg(srow + grp)) * 0x00010001u;
-                const uint32_t bias = 0x43004300u + uint32_t(__ldg(zrow + grp)) * 0x00010001u;
+                const uint4 q = q_next;
+                const uint32_t sc = sc_next, bias = bias_next;
+                if (ks + kDequantGroups < ksteps) fetch(ks + kDequantGroups, q_next, sc_next, bias_next);
                 if (it >= kStages) ok = mbar_wait(&pipe->empty[s], ((it / kStages) - 1) & 1, &g_gemm_error, 5);
                 if (!ok) break;
                 uint8_t* tile_b = smem + s * kStageBytes + 2 * kATile + row * 128;

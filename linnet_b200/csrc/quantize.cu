@@ -82,9 +82,21 @@ __device__ __forceinline__ float int4_zero(float lo, float step) {
     float z = rintf(__fdiv_rn(-lo, step));
     return fminf(fmaxf(z, 0.0f), 15.0f);
 }
+// round(v / s) exactly as NumPy computes it (a correctly rounded f32 division, then
+// round-half-even), at a fraction of the division's cost: v * (1/s) is within 1.2e-7
+// relative of the true quotient, so for |quotient| < 256 it is within 4.6e-5 of the
+// rounded quotient NumPy sees; unless it lies within 1e-4 of a half-integer both round to
+// the same integer.  The rare near-tie, huge or non-finite quotients take the division.
+__device__ __forceinline__ float rint_div(float v, float s, float inv_s) {
+    const float t = __fmul_rn(v, inv_s);
+    float n = rintf(t);
+    const float to_half = fabsf(fabsf(__fsub_rn(t, n)) - 0.5f);
+    if (!(fabsf(t) < 256.0f) || to_half < 1e-4f) n = rintf(__fdiv_rn(v, s));
+    return n;
+}
 // quant.py:96: q = clip(round(g / scale) + zero, 0, 15).
-__device__ __forceinline__ uint32_t int4_level(float v, float step, float zero) {
-    float q = __fadd_rn(rintf(__fdiv_rn(v, step)), zero);
+__device__ __forceinline__ uint32_t int4_level(float v, float step, float inv_step, float zero) {
+    float q = __fadd_rn(rint_div(v, step, inv_step), zero);
     return uint32_t(fminf(fmaxf(q, 0.0f), 15.0f));
 }
 // weights.py:74-79: bf16 bits, round to nearest even by the integer trick.
@@ -101,8 +113,8 @@ __device__ __forceinline__ float int8_scale(float absmax, int scale_dtype) {
     return s;
 }
 // quant.py:119: q = clip(round(g / scale), -127, 127).
-__device__ __forceinline__ int int8_level(float v, float scale) {
-    float q = rintf(__fdiv_rn(v, scale));
+__device__ __forceinline__ int int8_level(float v, float scale, float inv_scale) {
+    float q = rint_div(v, scale, inv_scale);
     return int(fminf(fmaxf(q, -127.0f), 127.0f));
 }
 
@@ -119,17 +131,19 @@ __device__ __forceinline__ void store_scale(void* dst, int dtype, int64_t i, flo
 
 __device__ __forceinline__ uint32_t pack8_int4(const Chunk& c, float step, float zero) {
     uint32_t word = 0;
+    const float inv = __frcp_rn(step);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) word |= int4_level(c.v[j], step, zero) << (4 * j);
+    for (int j = 0; j < 8; ++j) word |= int4_level(c.v[j], step, inv, zero) << (4 * j);
     return word;  // little endian: byte j/2 holds element j (even) low, j+1 high
 }
 
 __device__ __forceinline__ uint2 pack8_int8(const Chunk& c, float scale) {
     uint32_t lo = 0, hi = 0;
+    const float inv = __frcp_rn(scale);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-        lo |= (uint32_t(int8_level(c.v[j], scale)) & 0xFFu) << (8 * j);
-        hi |= (uint32_t(int8_level(c.v[4 + j], scale)) & 0xFFu) << (8 * j);
+        lo |= (uint32_t(int8_level(c.v[j], scale, inv)) & 0xFFu) << (8 * j);
+        hi |= (uint32_t(int8_level(c.v[4 + j], scale, inv)) & 0xFFu) << (8 * j);
     }
     return make_uint2(lo, hi);
 }
@@ -145,7 +159,7 @@ struct Outputs {
 // ---- team kernel ------------------------------------------------------------
 // T lanes per group, one 8-element chunk per lane, U chunks in flight per lane.
 template <int MODE, int T, typename In, int U>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)  // at most 64 registers: 32 warps per multiprocessor
 quantize_team_kernel(const In* __restrict__ w, int64_t chunks, Outputs o) {
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     const int64_t first = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -304,8 +318,9 @@ quantize_group_kernel(const In* __restrict__ w, int64_t groups, int64_t G, Outpu
                 }
             } else {
                 for (int64_t b = lane; b < G / 2; b += THREADS) {
-                    const uint32_t even = int4_level(widen_one(src + 2 * b), step, zero);
-                    const uint32_t odd = int4_level(widen_one(src + 2 * b + 1), step, zero);
+                    const float inv = __frcp_rn(step);
+                    const uint32_t even = int4_level(widen_one(src + 2 * b), step, inv, zero);
+                    const uint32_t odd = int4_level(widen_one(src + 2 * b + 1), step, inv, zero);
                     dst[b] = uint8_t(even | (odd << 4));
                 }
             }
@@ -328,7 +343,7 @@ quantize_group_kernel(const In* __restrict__ w, int64_t groups, int64_t G, Outpu
                 }
             } else {
                 for (int64_t e = lane; e < G; e += THREADS)
-                    dst[e] = uint8_t(int8_level(widen_one(src + e), scale));
+                    dst[e] = uint8_t(int8_level(widen_one(src + e), scale, __frcp_rn(scale)));
             }
         }
     }
