@@ -37,6 +37,12 @@ int32_t launched(const char* what) {
     return fail("%s: launch failed: %s", what, cudaGetErrorString(err));
 }
 
+int32_t launch_status(const char* what, cudaError_t err) {
+    if (err == cudaSuccess) return launched(what);
+    cudaGetLastError();
+    return fail("%s: launch failed: %s", what, cudaGetErrorString(err));
+}
+
 int sm_count() {
     // Indexed by device ordinal; written once per device (benign if two host
     // threads race: both write the same value).

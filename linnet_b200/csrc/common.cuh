@@ -22,6 +22,8 @@ int32_t unavailable(const char* format, ...);
 // After a launch: turns a launch error into a status + message.  Never
 // synchronises (an asynchronous fault shows at the caller's next sync).
 int32_t launched(const char* what);
+// The same for a launch call that returned `err`.
+int32_t launch_status(const char* what, cudaError_t err);
 
 inline bool aligned(const void* p, size_t bytes) {
     return (reinterpret_cast<uintptr_t>(p) % bytes) == 0;
@@ -39,6 +41,32 @@ int sm_count();
     do {                                         \
         if (!(cond)) return ::b200q::fail(__VA_ARGS__); \
     } while (0)
+
+// ---- programmatic dependent launch ------------------------------------------
+// A kernel launched with launch_overlapped() may start while the kernel before it in
+// the stream is still draining; it must call pdl_wait() before it reads anything an
+// earlier kernel wrote and before it writes anything an earlier kernel may still read.
+// Chains of such kernels hide most of the launch latency between them.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename... Params, typename... Args>
+cudaError_t launch_overlapped(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, Params(args)...);
+}
 
 // ---- device helpers -------------------------------------------------------
 

@@ -28,6 +28,8 @@ __global__ void __launch_bounds__(256)
 add_rmsnorm_kernel(uint16_t* __restrict__ x, const uint16_t* __restrict__ delta,
                    const uint16_t* __restrict__ w, uint16_t* __restrict__ y, int hidden, float eps) {
     __shared__ float partial[8];
+    pdl_wait();
+    pdl_launch_dependents();
     const int row = blockIdx.x, chunks = hidden / 8;
     uint4* xr = reinterpret_cast<uint4*>(x + size_t(row) * hidden);
     const uint4* dr = delta ? reinterpret_cast<const uint4*>(delta + size_t(row) * hidden) : nullptr;
@@ -71,6 +73,8 @@ __global__ void rope_cache_kernel(const uint16_t* __restrict__ qkv, const int64_
                                   uint16_t* __restrict__ q_out, uint16_t* __restrict__ cache_k,
                                   uint16_t* __restrict__ cache_v, int nq, int nkv, int hd, int S,
                                   float theta) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int b = blockIdx.y, head = blockIdx.x;  // head < nq: q; < nq + nkv: k; else v
     const int half = hd / 2;
     const int64_t pos = positions[b];
@@ -107,6 +111,8 @@ attention_partial_kernel(const uint16_t* __restrict__ q, const uint16_t* __restr
                          float* __restrict__ partial, int nq, int nkv, int S, int splits, float scale) {
     constexpr int LPK = HD / 16;     // lanes per key
     constexpr int KPW = 32 / LPK;    // keys per warp step
+    pdl_wait();
+    pdl_launch_dependents();
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
     const int sub = lane / LPK, part = lane % LPK;  // key slot of the warp step, slice of the head
@@ -223,6 +229,8 @@ attention_partial_kernel(const uint16_t* __restrict__ q, const uint16_t* __restr
 template <int HD>
 __global__ void attention_merge_kernel(const float* __restrict__ partial, uint16_t* __restrict__ out,
                                        int splits) {
+    pdl_wait();
+    pdl_launch_dependents();
     const size_t head = blockIdx.x;  // b * nq + query head
     const float* p = partial + head * splits * (HD + 2);
     float m_all = -INFINITY;
@@ -244,6 +252,8 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial, uint16
 // PyTorch ops do.
 __global__ void silu_mul_kernel(const uint16_t* __restrict__ gate_up, uint16_t* __restrict__ out,
                                 int inner, int64_t total) {
+    pdl_wait();
+    pdl_launch_dependents();
     for (int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
          e += int64_t(gridDim.x) * blockDim.x) {
         const int64_t row = e / inner, col = e % inner;
@@ -266,10 +276,10 @@ extern "C" int32_t b200q_add_rmsnorm(void* x, const void* delta, const void* wei
     B200Q_REQUIRE(x && weight && y && aligned(x, 16) && aligned(weight, 16) && aligned(y, 16) &&
                       (!delta || aligned(delta, 16)),
                   "add_rmsnorm: tensors must be 16-byte aligned");
-    add_rmsnorm_kernel<<<unsigned(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    return launch_status("add_rmsnorm", launch_overlapped(
+        add_rmsnorm_kernel, dim3(unsigned(rows)), dim3(256), 0, static_cast<cudaStream_t>(stream),
         static_cast<uint16_t*>(x), static_cast<const uint16_t*>(delta), static_cast<const uint16_t*>(weight),
-        static_cast<uint16_t*>(y), int(hidden), eps);
-    return launched("add_rmsnorm");
+        static_cast<uint16_t*>(y), int(hidden), eps));
 }
 
 extern "C" int32_t b200q_rope_cache(const void* qkv, const int64_t* positions, void* q_out, void* cache_k,
@@ -277,11 +287,11 @@ extern "C" int32_t b200q_rope_cache(const void* qkv, const int64_t* positions, v
                                     int64_t max_seq, float theta, void* stream) {
     B200Q_REQUIRE(batch >= 0 && nq > 0 && nkv > 0 && head_dim % 2 == 0, "rope_cache: bad shape");
     if (batch == 0) return B200Q_OK;
-    rope_cache_kernel<<<dim3(unsigned(nq + 2 * nkv), unsigned(batch)), 64, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint16_t*>(qkv), positions, static_cast<uint16_t*>(q_out),
-        static_cast<uint16_t*>(cache_k), static_cast<uint16_t*>(cache_v), int(nq), int(nkv), int(head_dim),
-        int(max_seq), theta);
-    return launched("rope_cache");
+    return launch_status("rope_cache", launch_overlapped(
+        rope_cache_kernel, dim3(unsigned(nq + 2 * nkv), unsigned(batch)), dim3(64), 0,
+        static_cast<cudaStream_t>(stream), static_cast<const uint16_t*>(qkv), positions,
+        static_cast<uint16_t*>(q_out), static_cast<uint16_t*>(cache_k), static_cast<uint16_t*>(cache_v), int(nq),
+        int(nkv), int(head_dim), int(max_seq), theta));
 }
 
 extern "C" int64_t b200q_decode_attention_scratch_bytes(int64_t batch, int64_t nq, int64_t head_dim,
@@ -308,20 +318,20 @@ int32_t launch_attention(const char* who, const void* q, const void* cache_k, co
     const dim3 grid{unsigned(splits), unsigned(nkv), unsigned(batch)};
     const float scale = 1.0f / sqrtf(float(head_dim));
 #define B200Q_ATTN(HD, REP)                                                                           \
-    attention_partial_kernel<HD, REP><<<grid, 128, 0, s>>>(                                           \
-        static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(cache_k),                       \
-        static_cast<const uint16_t*>(cache_v), positions, static_cast<float*>(scratch), int(nq),      \
-        int(nkv), int(max_seq), int(splits), scale)
+    launch_overlapped(attention_partial_kernel<HD, REP>, grid, dim3(128), 0, s,                       \
+                      static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(cache_k),         \
+                      static_cast<const uint16_t*>(cache_v), positions, static_cast<float*>(scratch), \
+                      int(nq), int(nkv), int(max_seq), int(splits), scale)
     if (head_dim == 128) {
         if (rep == 1) B200Q_ATTN(128, 1); else if (rep == 2) B200Q_ATTN(128, 2);
         else if (rep == 4) B200Q_ATTN(128, 4); else B200Q_ATTN(128, 8);
-        attention_merge_kernel<128><<<unsigned(batch * nq), 128, 0, s>>>(
-            static_cast<const float*>(scratch), static_cast<uint16_t*>(out), int(splits));
+        launch_overlapped(attention_merge_kernel<128>, dim3(unsigned(batch * nq)), dim3(128), 0, s,
+                          static_cast<const float*>(scratch), static_cast<uint16_t*>(out), int(splits));
     } else {
         if (rep == 1) B200Q_ATTN(64, 1); else if (rep == 2) B200Q_ATTN(64, 2);
         else if (rep == 4) B200Q_ATTN(64, 4); else B200Q_ATTN(64, 8);
-        attention_merge_kernel<64><<<unsigned(batch * nq), 64, 0, s>>>(
-            static_cast<const float*>(scratch), static_cast<uint16_t*>(out), int(splits));
+        launch_overlapped(attention_merge_kernel<64>, dim3(unsigned(batch * nq)), dim3(64), 0, s,
+                          static_cast<const float*>(scratch), static_cast<uint16_t*>(out), int(splits));
     }
 #undef B200Q_ATTN
     return launched(who);
@@ -396,7 +406,7 @@ extern "C" int32_t b200q_silu_mul(const void* gate_up, void* out, int64_t rows, 
     if (total == 0) return B200Q_OK;
     int64_t blocks = (total + 255) / 256;
     if (blocks > int64_t(sm_count()) * 16) blocks = int64_t(sm_count()) * 16;
-    silu_mul_kernel<<<unsigned(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint16_t*>(gate_up), static_cast<uint16_t*>(out), int(inner), total);
-    return launched("silu_mul");
+    return launch_status("silu_mul", launch_overlapped(
+        silu_mul_kernel, dim3(unsigned(blocks)), dim3(256), 0, static_cast<cudaStream_t>(stream),
+        static_cast<const uint16_t*>(gate_up), static_cast<uint16_t*>(out), int(inner), total));
 }

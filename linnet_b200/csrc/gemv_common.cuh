@@ -62,14 +62,6 @@ __device__ __forceinline__ void reduce_and_store(const float (&total)[NT][MB][4]
     }
 }
 
-// Programmatic dependent launch: a kernel that calls pdl_wait() before it touches
-// anything an earlier kernel of the stream wrote may start while that kernel drains,
-// which hides launch latency and ramp-up behind the predecessor's tail.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-}
-
 // Launches `kernel` on a (tiles, ksplit) grid whose y extent forms one cluster.
 // `overlap`: launch with programmatic stream serialization (the kernel must call
 // pdl_wait() before reading activations or writing outputs).

@@ -123,6 +123,9 @@ int4_gemv_kernel(const GemvArgs a) {
     for (int d = 0; d < D; ++d)
         if (d < nw) load_stage(st[d], wb0 + d);
 
+    pdl_launch_dependents();
+    pdl_wait();  // activations may come from the kernel before this one
+
     // 2. Each warp stages the activations of its own K range (no block barrier):
     //    16-byte pieces, permuted to the (k, k+4) pairing of the A fragments.
     {
@@ -346,7 +349,7 @@ int32_t launch_gemv(const GemvArgs& args, int ksplit, cudaStream_t stream) {
     const size_t smem = size_t(W) * cap * 16 * a.M * 16 + (MODE == kPost ? size_t(W) * cap * 16 * 4 : 0) +
                         size_t(W) * NT * 16 * MB * 8 * 4;
     return launch_clustered("int4_gemv", int4_gemv_kernel<T, MODE, MB, NT, W, D>, a, tiles, ksplit,
-                            W * 32, smem, stream);
+                            W * 32, smem, stream, true);
 }
 
 template <typename T, int MODE>
@@ -359,13 +362,13 @@ int32_t dispatch_gemv(const GemvArgs& a, const Plan& p, cudaStream_t stream) {
 // (of 4, 7, 2, 1) that divide K / 1024 with at most 8 blocks per cluster.
 template <typename T>
 bool run_oct(const GemvArgs& a, cudaStream_t stream, int32_t* status) {
-    OctArgs o{a.x, a.packed, a.scale, a.zero, a.y, a.M, a.K, a.N, 1, 0};
+    // Every variant is launched with programmatic stream serialization: its weight
+    // prefetch overlaps the tail of the kernel before it.
+    OctArgs o{a.x, a.packed, a.scale, a.zero, a.y, a.M, a.K, a.N, 1, 1};
     const bool few = a.M <= 8;
     if (oct_plan(a.K, a.G, 4, a.scale, a.zero, &o.ksplit)) {
         if (a.M <= 2) {
-            // One or two rows: every weight load of the kernel is issued up front
-            // (cp.async) and the launch overlaps the tail of the kernel before it.
-            o.overlap = 1;
+            // One or two rows: every weight load of the kernel is issued up front (cp.async).
             *status = launch_oct<T, 1, 1, 4, 0>(o, stream);
         } else {
             *status = few ? launch_oct<T, 1, 1, 4, 2>(o, stream) : launch_oct<T, 2, 1, 4, 2>(o, stream);

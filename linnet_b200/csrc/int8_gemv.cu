@@ -111,6 +111,8 @@ int8_gemv_kernel(const Gemv8Args a) {
     for (int d = 0; d < D; ++d)
         if (wb0 + d < wb1) load_stage(st[d], wb0 + d);
 
+    pdl_launch_dependents();
+    pdl_wait();  // activations may come from the kernel before this one
     {
         const uint4* xg = static_cast<const uint4*>(a.x);
         const int per_row = nkb * 8;  // 16-byte pieces per activation row
@@ -243,7 +245,7 @@ int32_t launch_gemv8(const Gemv8Args& args, int ksplit, cudaStream_t stream) {
     const int tiles = (a.N + 16 * NT - 1) / (16 * NT);
     const size_t smem = size_t(a.kb_per_cta) * 8 * a.M * 16 + size_t(W) * NT * 16 * MB * 8 * 4;
     return launch_clustered("int8_gemv", int8_gemv_kernel<T, MODE, MB, NT, W, D>, a, tiles, ksplit,
-                            W * 32, smem, stream);
+                            W * 32, smem, stream, true);
 }
 
 template <typename T, int MODE>
