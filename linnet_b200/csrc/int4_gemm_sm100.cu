@@ -24,22 +24,42 @@
 // global memory, stops issuing work, still releases its tensor memory and returns.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "mma.cuh"
 
 namespace b200q {
 namespace {
 
 constexpr int kBM = 128;       // rows of X per accumulator
-constexpr int kBN = 128;       // rows of W (columns of Y) per tile
 constexpr int kBK = 64;        // inputs per stage: one 128-byte swizzle atom of bf16
-constexpr int kStages = 4;
 constexpr int kATile = kBM * kBK * 2;               // 16 KB
-constexpr int kStageBytes = 2 * kATile + kBN * kBK * 2;  // 48 KB
 constexpr int kEpilogueWarps = 4, kTmaWarp = 4, kMmaWarp = 5, kFirstDequantWarp = 6;
-constexpr int kDequantWarps = 8;   // warps that fill one stage
-constexpr int kDequantGroups = 2;  // groups of such warps, taking stages in turn
-constexpr int kThreads = (kFirstDequantWarp + kDequantWarps * kDequantGroups) * 32;  // 704
+constexpr int kAllDequantWarps = 16;
+constexpr int kThreads = (kFirstDequantWarp + kAllDequantWarps) * 32;  // 704
 constexpr uint32_t kTmemColumns = 512;
+
+// The tile's width BN (rows of W = columns of Y) decides how often X is re-read from L2:
+// every X element is loaded once per BN output columns.  At BN = 128 the X tiles alone
+// need ~6 TB/s of L2 bandwidth at the tensor cores' speed and the kernel is L2-bound
+// (measured ~0.8 PFLOP/s); BN = 256 halves that.
+//   BN = 128: 4 stages of 48 KB, accumulators double-buffered (2 x 2 x 128 columns), the
+//             dequantizers work as two groups of 8 warps taking stages in turn;
+//   BN = 256: 3 stages of 64 KB, 2 x 256 columns used once per tile (the epilogue of a
+//             tile does not overlap the next tile's products), all 16 dequantizer warps
+//             fill every stage.
+template <int BN>
+struct Shape {
+    static constexpr int kStages = BN == 128 ? 4 : 3;
+    static constexpr int kStageBytes = 2 * kATile + BN * kBK * 2;
+    static constexpr int kAccBufs = BN == 128 ? 2 : 1;
+    static constexpr int kDequantGroups = BN == 128 ? 2 : 1;
+    static constexpr int kDequantWarps = kAllDequantWarps / kDequantGroups;  // warps per stage
+    static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(BN >> 3) << 17) |
+                                       (uint32_t(kBM >> 4) << 24);
+    static constexpr size_t kSmem = size_t(kStages) * kStageBytes + 1024 + 256;
+};
+constexpr int kMaxStages = 4;
 
 struct GemmArgs {
     const uint8_t* packed;  // [N, K/2]
@@ -137,21 +157,26 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
     return uint64_t((addr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) |
            (uint64_t(1) << 46) | (uint64_t(2) << 61);
 }
-// kind::f16 instruction descriptor: f32 accumulator, bf16 A and B, both K-major, M = N = 128.
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(kBN >> 3) << 17) |
-                            (uint32_t(kBM >> 4) << 24);
+// (The kind::f16 instruction descriptor is Shape<BN>::kIdesc: f32 accumulator, bf16 A and
+// B, both K-major, M = 128, N = BN.)
 
 struct Pipeline {  // shared-memory barriers and the tensor-memory base address
-    uint64_t full_a[kStages];   // TMA bytes of X landed
-    uint64_t full_b[kStages];   // dequantized W tile written (8 warp arrivals)
-    uint64_t empty[kStages];    // MMAs that read the stage completed
+    uint64_t full_a[kMaxStages];   // TMA bytes of X landed
+    uint64_t full_b[kMaxStages];   // dequantized W tile written (one arrival per dequantizer warp)
+    uint64_t empty[kMaxStages];    // MMAs that read the stage completed
     uint64_t acc_full[2];       // all MMAs of a tile completed
     uint64_t acc_empty[2];      // epilogue drained the accumulators (4 warp arrivals)
     uint32_t tmem_base;
 };
 
+template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
+    using S = Shape<BN>;
+    constexpr int kStages = S::kStages, kStageBytes = S::kStageBytes, kAccBufs = S::kAccBufs;
+    constexpr int kDequantGroups = S::kDequantGroups, kDequantWarps = S::kDequantWarps;
+    constexpr uint32_t kIdesc = S::kIdesc;
+    constexpr int kBN = BN;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // The swizzled tiles need 1024-byte alignment.
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -211,8 +236,9 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
             for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++t) {
                 const int m0 = (tile % a.m_tiles) * (2 * kBM);
                 const bool two = m0 + kBM < a.M;
-                const uint32_t buf = t & 1;
-                if (t >= 2) ok = mbar_wait(&pipe->acc_empty[buf], ((t >> 1) - 1) & 1, &g_gemm_error, 2);
+                const uint32_t buf = t % kAccBufs;
+                if (t >= uint32_t(kAccBufs))
+                    ok = mbar_wait(&pipe->acc_empty[buf], ((t / kAccBufs) - 1) & 1, &g_gemm_error, 2);
                 tc_fence_after();
                 for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
                     const int s = it % kStages;
@@ -226,8 +252,8 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
                     for (int kk = 0; kk < kBK / 16; ++kk) {
                         const uint64_t b_desc = smem_desc(base + 2 * kATile + kk * 32);
                         const uint32_t acc = (ks > 0 || kk > 0) ? 1u : 0u;
-                        umma_bf16(tmem + buf * 256, smem_desc(base + kk * 32), b_desc, kIdesc, acc);
-                        if (two) umma_bf16(tmem + buf * 256 + 128, smem_desc(base + kATile + kk * 32), b_desc, kIdesc, acc);
+                        umma_bf16(tmem + buf * (2 * kBN), smem_desc(base + kk * 32), b_desc, kIdesc, acc);
+                        if (two) umma_bf16(tmem + buf * (2 * kBN) + kBN, smem_desc(base + kATile + kk * 32), b_desc, kIdesc, acc);
                     }
                     umma_commit(&pipe->empty[s]);  // frees the stage when these MMAs retire
                 }
@@ -236,7 +262,7 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
         }
     } else if (warp >= kFirstDequantWarp) {
         // ---- dequantizers --------------------------------------------------------
-        const int d = (threadIdx.x - kFirstDequantWarp * 32) % (kDequantWarps * 32);  // 0..255
+        const int d = (threadIdx.x - kFirstDequantWarp * 32) % (kDequantWarps * 32);  // (row, half) of a stage
         const int group_id = (threadIdx.x - kFirstDequantWarp * 32) / (kDequantWarps * 32);
         const int row = d >> 1, half = d & 1;                // W row of the tile, 32-input half
         const int groups = a.K / a.G;
@@ -299,8 +325,8 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
         for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++t) {
             const int m0 = (tile % a.m_tiles) * (2 * kBM);
             const int n0 = (tile / a.m_tiles) * kBN;
-            const uint32_t buf = t & 1;
-            ok = mbar_wait(&pipe->acc_full[buf], (t >> 1) & 1, &g_gemm_error, 6);
+            const uint32_t buf = t % kAccBufs;
+            ok = mbar_wait(&pipe->acc_full[buf], (t / kAccBufs) & 1, &g_gemm_error, 6);
             if (!ok) break;
             tc_fence_after();
 #pragma unroll 1
@@ -310,7 +336,7 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
 #pragma unroll 1
                 for (int c0 = 0; c0 < kBN; c0 += 32) {
                     uint32_t v[32];
-                    const uint32_t taddr = tmem + (uint32_t(warp * 32) << 16) + buf * 256 + acc * 128 + c0;
+                    const uint32_t taddr = tmem + (uint32_t(warp * 32) << 16) + buf * (2 * kBN) + acc * kBN + c0;
                     asm volatile(
                         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                         "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
@@ -359,6 +385,8 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
     }
 }
 
+int g_force_bn = 0;  // measurement hook: B200Q_GEMM_BN=128|256 in the environment
+
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no libcuda link).
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -398,6 +426,12 @@ extern "C" int32_t b200q_int4_gemm(const void* x, const uint8_t* packed, const v
                   "int4_gemm: needs bf16, inputs and group multiples of %d (got in=%lld group=%lld)", kBK,
                   (long long)in, (long long)group);
     B200Q_REQUIRE(rows < (int64_t(1) << 30), "int4_gemm: too many rows");
+    static const bool env_read = [] {
+        const char* v = getenv("B200Q_GEMM_BN");
+        if (v != nullptr) g_force_bn = atoi(v);
+        return true;
+    }();
+    (void)env_read;
     EncodeTiled encode = encode_tiled();
     if (encode == nullptr) return unavailable("int4_gemm: the driver has no cuTensorMapEncodeTiled");
 
@@ -412,14 +446,25 @@ extern "C" int32_t b200q_int4_gemm(const void* x, const uint8_t* packed, const v
                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     B200Q_REQUIRE(made == CUDA_SUCCESS, "int4_gemm: cuTensorMapEncodeTiled failed (%d)", int(made));
 
+    // Tile width: 256 unless the narrower tile's better fit to the SM count outweighs its
+    // L2-bound main loop (a 256-wide tile takes about 1.25x the time of a 128-wide one).
+    const int sms = sm_count();
+    const int m_tiles = int((rows + 2 * kBM - 1) / (2 * kBM));
+    const int64_t tiles128 = int64_t(m_tiles) * ((out + 127) / 128), tiles256 = int64_t(m_tiles) * ((out + 255) / 256);
+    const double cost128 = double((tiles128 + sms - 1) / sms), cost256 = 1.25 * double((tiles256 + sms - 1) / sms);
+    const bool wide = g_force_bn == 256 || (g_force_bn != 128 && cost256 <= cost128);
     GemmArgs a{packed, static_cast<const uint16_t*>(scale), zero, static_cast<uint16_t*>(y),
-               int(rows), int(in), int(out), int(group),
-               int((rows + 2 * kBM - 1) / (2 * kBM)), int((out + kBN - 1) / kBN)};
-    const size_t smem = size_t(kStages) * kStageBytes + 1024 + 256;
-    cudaFuncSetAttribute(int4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+               int(rows), int(in), int(out), int(group), m_tiles, int(wide ? (out + 255) / 256 : (out + 127) / 128)};
     const int tiles = a.m_tiles * a.n_tiles;
-    const int grid = tiles < sm_count() ? tiles : sm_count();
-    int4_gemm_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(x_map, a);
+    const int grid = tiles < sms ? tiles : sms;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (wide) {
+        cudaFuncSetAttribute(int4_gemm_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(Shape<256>::kSmem));
+        int4_gemm_kernel<256><<<grid, kThreads, Shape<256>::kSmem, s>>>(x_map, a);
+    } else {
+        cudaFuncSetAttribute(int4_gemm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(Shape<128>::kSmem));
+        int4_gemm_kernel<128><<<grid, kThreads, Shape<128>::kSmem, s>>>(x_map, a);
+    }
     return launched("int4_gemm");
 }
 
