@@ -5,13 +5,15 @@
 
 Prints ONE JSON line.  Workloads:
 
-* `gemv` (default on one GPU) -- the W4A16 g128 decode product the headline metric is
+* `gemv` (default) -- the W4A16 g128 decode product the headline metric is
   quoted on: K=4096, N=14336 (Llama-3-8B gate/up), x bf16 [M, K], M=1 for `value`
   (M=4 and 16 are reported under `per_rows`).  One step is 64 launches cycling through
   8 distinct weight sets (246 MB, larger than the 126 MB L2, so every launch streams its
   weights from HBM), recorded once into a CUDA graph and replayed.
-* `decode` (default on several GPUs) -- a Llama-3.1-8B-shaped int4 decoder step,
-  tensor-parallel over the ranks (see linnet_b200/decoder.py).
+  With N ranks every rank runs this on its own GPU and weight sets (`value` is the sum).
+  The line also carries `decode`: tokens/s of a Llama-3.1-8B-shaped int4 decoder step,
+  tensor-parallel over the N ranks (linnet_b200/decoder.py), at batch 1, 8 and 64.
+* `--workload decode` -- only the decoder, tokens/s as `value`.
 
 `--impl reference` times the reference's own CPU route for the same workload (its
 torch path: weight dequantized once, then bf16 `F.linear`) on the host cores.
@@ -363,6 +365,7 @@ def main() -> None:
     parser.add_argument("--batch", type=int, default=1)
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-other-configs", action="store_true")
+    parser.add_argument("--no-decode", action="store_true")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -400,13 +403,26 @@ def main() -> None:
         def reduce_max(v: float) -> float:
             return v
 
-    workload = args.workload or ("gemv" if world == 1 else "decode")
-    if workload == "decode":
-        from linnet_b200 import decoder
+    from linnet_b200 import decoder
 
+    if args.workload == "decode":
         line = decoder.bench(args, rank, world, device, barrier, reduce_max, Clocks)
     else:
+        # The headline line is the same at every N: the GEMV of BASELINE's configs[1], each
+        # rank streaming its own weight sets (the product shards by output rows with no
+        # exchange, so more GPUs are more independent rows: weak scaling).  The second half
+        # of the metric, decoder tokens/s tensor-parallel over the N ranks, rides along
+        # under "decode".
         line = run_gemv(args, rank, world, device, barrier, reduce_max)
+        if not args.no_decode:
+            torch.cuda.empty_cache()
+            dargs = argparse.Namespace(**vars(args))
+            dargs.steps = max(10, args.steps // 4)
+            dec = decoder.bench(dargs, rank, world, device, barrier, reduce_max, Clocks)
+            line["decode"] = {"metric": "8B-shape int4 decode tok/s", "tensor_parallel": world,
+                              "tok_s": dec["value"], "ms_per_step": dec["ms_per_step"],
+                              "per_batch": dec["per_batch"], "e2e": dec["e2e"], "steps": dargs.steps,
+                              "roofline": dec["roofline"], "config": dec["config"]}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

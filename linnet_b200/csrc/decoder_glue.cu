@@ -100,128 +100,132 @@ __global__ void rope_cache_kernel(const uint16_t* __restrict__ qkv, const int64_
 }
 
 // ---- single-query attention, split over the keys --------------------------------------
-// Block (split, kv head, batch row): 4 warps; a group of HD/16 lanes owns one key at a time
-// (16 elements a lane) and keeps its own running softmax for the REP query heads that
-// share the KV head; groups, warps and finally splits are merged with the usual
-// (max, sum, weighted accumulator) rule.  partial: [B, nq, splits, HD + 2] f32.
+// Block (split, kv head, batch row): one warp per query head of the KV head's group (REP
+// warps).  The block streams its keys and values through shared memory in chunks of 64
+// positions with cp.async, two chunks in flight, so every K/V byte is read from HBM once
+// for all REP heads and many bytes are in flight per multiprocessor; a group of HD/16
+// lanes owns one position at a time (two 16-byte pieces per lane, laid out so a quarter
+// warp reads 128 contiguous bytes) and keeps its own running softmax; the groups of a
+// warp and finally the splits are merged with the usual (max, sum, weighted accumulator)
+// rule.  partial: [B, nq, splits, HD + 2] f32.
+constexpr int kAttnChunk = 64;
+
 template <int HD, int REP>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(32 * REP)
 attention_partial_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ cache_k,
                          const uint16_t* __restrict__ cache_v, const int64_t* __restrict__ positions,
                          float* __restrict__ partial, int nq, int nkv, int S, int splits, float scale) {
-    constexpr int LPK = HD / 16;     // lanes per key
-    constexpr int KPW = 32 / LPK;    // keys per warp step
+    constexpr int LPK = HD / 16;             // lanes per position
+    constexpr int KPW = 32 / LPK;            // positions per warp step
+    constexpr int kRowBytes = HD * 2;
+    constexpr int kStage = kAttnChunk * kRowBytes;  // bytes of K (or V) per chunk
+    extern __shared__ __align__(16) uint8_t attn_smem[];  // [2 stages][K chunk | V chunk]
     pdl_wait();
     pdl_launch_dependents();
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
-    const int sub = lane / LPK, part = lane % LPK;  // key slot of the warp step, slice of the head
-    const int keys = int(positions[b]) + 1;          // attend to positions 0 .. pos
+    const int sub = lane / LPK, part = lane % LPK;
+    const int keys = int(positions[b]) + 1;  // attend to positions 0 .. pos
     const int per_split = (keys + splits - 1) / splits;
     const int k0 = split * per_split, k1 = min(k0 + per_split, keys);
+    const int chunks = k1 > k0 ? (k1 - k0 + kAttnChunk - 1) / kAttnChunk : 0;
+    const size_t base = (size_t(b) * nkv + kvh) * S * HD;
 
-    float qv[REP][16];
-#pragma unroll
-    for (int r = 0; r < REP; ++r) {
-        const uint4* qp = reinterpret_cast<const uint4*>(q + (size_t(b) * nq + kvh * REP + r) * HD + part * 16);
-        const uint4 lo = qp[0], hi = qp[1];
+    auto issue = [&](int c) {  // chunk c of this split -> stage c % 2
+        uint8_t* dst = attn_smem + (c % 2) * 2 * kStage;
+        const int first = k0 + c * kAttnChunk;
+        for (int piece = threadIdx.x; piece < 2 * kStage / 16; piece += 32 * REP) {
+            const int which = piece / (kStage / 16), within = piece % (kStage / 16);
+            const int key = min(first + within / (kRowBytes / 16), k1 - 1);  // the tail repeats the last key
+            const uint16_t* src = (which ? cache_v : cache_k) + base + size_t(key) * HD + (within % (kRowBytes / 16)) * 8;
+            const uint32_t d = uint32_t(__cvta_generic_to_shared(dst + size_t(piece) * 16));
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (chunks > 0) issue(0);
+    if (chunks > 1) issue(1);
+
+    // This warp's query head, scaled; the lane's 16 elements are [part*8, +8) of each half.
+    float qv[16];
+    {
+        const uint16_t* qp = q + (size_t(b) * nq + kvh * REP + warp) * HD;
+        const uint4 lo = *reinterpret_cast<const uint4*>(qp + part * 8);
+        const uint4 hi = *reinterpret_cast<const uint4*>(qp + HD / 2 + part * 8);
         const uint32_t u[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            qv[r][2 * i] = bf16_lo(u[i]) * scale;
-            qv[r][2 * i + 1] = bf16_hi(u[i]) * scale;
+            qv[2 * i] = bf16_lo(u[i]) * scale;
+            qv[2 * i + 1] = bf16_hi(u[i]) * scale;
         }
     }
-    float m[REP], l[REP], acc[REP][16];
+    float m = -INFINITY, l = 0.0f, acc[16];
 #pragma unroll
-    for (int r = 0; r < REP; ++r) {
-        m[r] = -INFINITY;
-        l[r] = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) acc[r][i] = 0.0f;
-    }
-    const size_t base = (size_t(b) * nkv + kvh) * S * HD + part * 16;
-    for (int s0 = k0 + warp * KPW; s0 < k1; s0 += 4 * KPW) {
-        const int s = s0 + sub;
-        const bool live = s < k1;
-        uint4 ka = make_uint4(0, 0, 0, 0), kb = ka, va = ka, vb = ka;
-        if (live) {
-            const uint4* kp = reinterpret_cast<const uint4*>(cache_k + base + size_t(s) * HD);
-            const uint4* vp = reinterpret_cast<const uint4*>(cache_v + base + size_t(s) * HD);
-            ka = ldg_stream(kp); kb = ldg_stream(kp + 1);
-            va = ldg_stream(vp); vb = ldg_stream(vp + 1);
-        }
-        const uint32_t ku[8] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w};
-        const uint32_t vu[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
-#pragma unroll
-        for (int r = 0; r < REP; ++r) {
+    for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
+
+    for (int c = 0; c < chunks; ++c) {
+        if (c + 1 < chunks) asm volatile("cp.async.wait_group 1;" ::: "memory");
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        const uint8_t* ks = attn_smem + (c % 2) * 2 * kStage;
+        const uint8_t* vs = ks + kStage;
+        const int first = k0 + c * kAttnChunk;
+#pragma unroll 2
+        for (int s0 = 0; s0 < kAttnChunk; s0 += KPW) {
+            const int slot = s0 + sub;
+            const bool live = first + slot < k1;
+            const uint4 ka = *reinterpret_cast<const uint4*>(ks + slot * kRowBytes + part * 16);
+            const uint4 kb = *reinterpret_cast<const uint4*>(ks + slot * kRowBytes + HD + part * 16);
+            const uint32_t ku[8] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w};
             float dot = 0.0f;
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-                dot += qv[r][2 * i] * bf16_lo(ku[i]) + qv[r][2 * i + 1] * bf16_hi(ku[i]);
+            for (int i = 0; i < 8; ++i) dot += qv[2 * i] * bf16_lo(ku[i]) + qv[2 * i + 1] * bf16_hi(ku[i]);
 #pragma unroll
             for (int d = LPK / 2; d >= 1; d >>= 1) dot += __shfl_xor_sync(0xFFFFFFFFu, dot, d);
             if (live) {
-                const float m_new = fmaxf(m[r], dot);
-                const float corr = __expf(m[r] - m_new), p = __expf(dot - m_new);
-                m[r] = m_new;
-                l[r] = l[r] * corr + p;
+                const uint4 va = *reinterpret_cast<const uint4*>(vs + slot * kRowBytes + part * 16);
+                const uint4 vb = *reinterpret_cast<const uint4*>(vs + slot * kRowBytes + HD + part * 16);
+                const uint32_t vu[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+                const float m_new = fmaxf(m, dot);
+                const float corr = __expf(m - m_new), p = __expf(dot - m_new);
+                m = m_new;
+                l = l * corr + p;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    acc[r][2 * i] = acc[r][2 * i] * corr + p * bf16_lo(vu[i]);
-                    acc[r][2 * i + 1] = acc[r][2 * i + 1] * corr + p * bf16_hi(vu[i]);
+                    acc[2 * i] = acc[2 * i] * corr + p * bf16_lo(vu[i]);
+                    acc[2 * i + 1] = acc[2 * i + 1] * corr + p * bf16_hi(vu[i]);
                 }
             }
         }
+        __syncthreads();  // everyone is done with this stage before it is refilled
+        if (c + 2 < chunks) issue(c + 2);
     }
-    // Merge the key slots of the warp (lanes with the same `part`).
+    // Merge the position slots of the warp (lanes with the same `part`).
 #pragma unroll
-    for (int r = 0; r < REP; ++r) {
+    for (int d = LPK; d < 32; d <<= 1) {
+        const float m_o = __shfl_xor_sync(0xFFFFFFFFu, m, d);
+        const float l_o = __shfl_xor_sync(0xFFFFFFFFu, l, d);
+        const float m_new = fmaxf(m, m_o);
+        const float c_s = m == -INFINITY ? 0.0f : __expf(m - m_new);
+        const float c_o = m_o == -INFINITY ? 0.0f : __expf(m_o - m_new);
+        l = l * c_s + l_o * c_o;
 #pragma unroll
-        for (int d = LPK; d < 32; d <<= 1) {
-            const float m_o = __shfl_xor_sync(0xFFFFFFFFu, m[r], d);
-            const float l_o = __shfl_xor_sync(0xFFFFFFFFu, l[r], d);
-            const float m_new = fmaxf(m[r], m_o);
-            const float c_s = m[r] == -INFINITY ? 0.0f : __expf(m[r] - m_new);
-            const float c_o = m_o == -INFINITY ? 0.0f : __expf(m_o - m_new);
-            l[r] = l[r] * c_s + l_o * c_o;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float a_o = __shfl_xor_sync(0xFFFFFFFFu, acc[r][i], d);
-                acc[r][i] = acc[r][i] * c_s + a_o * c_o;
-            }
-            m[r] = m_new;
+        for (int i = 0; i < 16; ++i) {
+            const float a_o = __shfl_xor_sync(0xFFFFFFFFu, acc[i], d);
+            acc[i] = acc[i] * c_s + a_o * c_o;
         }
+        m = m_new;
     }
-    // Merge the four warps through shared memory.
-    __shared__ float sm_m[4][REP], sm_l[4][REP], sm_acc[4][REP][HD];
     if (sub == 0) {
+        float* out = partial + ((size_t(b) * nq + kvh * REP + warp) * splits + split) * (HD + 2);
 #pragma unroll
-        for (int r = 0; r < REP; ++r) {
-            if (part == 0) {
-                sm_m[warp][r] = m[r];
-                sm_l[warp][r] = l[r];
-            }
-#pragma unroll
-            for (int i = 0; i < 16; ++i) sm_acc[warp][r][part * 16 + i] = acc[r][i];
+        for (int i = 0; i < 8; ++i) {
+            out[part * 8 + i] = acc[i];
+            out[HD / 2 + part * 8 + i] = acc[8 + i];
         }
-    }
-    __syncthreads();
-    for (int e = threadIdx.x; e < REP * HD; e += blockDim.x) {
-        const int r = e / HD, dcol = e % HD;
-        float m_all = sm_m[0][r];
-        for (int w = 1; w < 4; ++w) m_all = fmaxf(m_all, sm_m[w][r]);
-        float l_all = 0.0f, a_all = 0.0f;
-        for (int w = 0; w < 4; ++w) {
-            const float c = sm_m[w][r] == -INFINITY ? 0.0f : __expf(sm_m[w][r] - m_all);
-            l_all += sm_l[w][r] * c;
-            a_all += sm_acc[w][r][dcol] * c;
-        }
-        float* out = partial + ((size_t(b) * nq + kvh * REP + r) * splits + split) * (HD + 2);
-        out[dcol] = a_all;
-        if (dcol == 0) {
-            out[HD] = m_all;
-            out[HD + 1] = l_all;
+        if (part == 0) {
+            out[HD] = m;
+            out[HD + 1] = l;
         }
     }
 }
@@ -234,9 +238,11 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial, uint16
     const size_t head = blockIdx.x;  // b * nq + query head
     const float* p = partial + head * splits * (HD + 2);
     float m_all = -INFINITY;
+#pragma unroll 8
     for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, p[s * (HD + 2) + HD]);
     for (int dcol = threadIdx.x; dcol < HD; dcol += blockDim.x) {
         float l_all = 0.0f, a_all = 0.0f;
+#pragma unroll 8
         for (int s = 0; s < splits; ++s) {
             const float ms = p[s * (HD + 2) + HD];
             const float c = ms == -INFINITY ? 0.0f : __expf(ms - m_all);
@@ -317,11 +323,14 @@ int32_t launch_attention(const char* who, const void* q, const void* cache_k, co
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const dim3 grid{unsigned(splits), unsigned(nkv), unsigned(batch)};
     const float scale = 1.0f / sqrtf(float(head_dim));
-#define B200Q_ATTN(HD, REP)                                                                           \
-    launch_overlapped(attention_partial_kernel<HD, REP>, grid, dim3(128), 0, s,                       \
+#define B200Q_ATTN(HD, REP) do {                                                                      \
+    cudaFuncSetAttribute(attention_partial_kernel<HD, REP>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                         4 * kAttnChunk * HD * 2);                                                    \
+    launch_overlapped(attention_partial_kernel<HD, REP>, grid, dim3(32 * REP),                        \
+                      size_t(4) * kAttnChunk * HD * 2, s,                                             \
                       static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(cache_k),         \
                       static_cast<const uint16_t*>(cache_v), positions, static_cast<float*>(scratch), \
-                      int(nq), int(nkv), int(max_seq), int(splits), scale)
+                      int(nq), int(nkv), int(max_seq), int(splits), scale); } while (0)
     if (head_dim == 128) {
         if (rep == 1) B200Q_ATTN(128, 1); else if (rep == 2) B200Q_ATTN(128, 2);
         else if (rep == 4) B200Q_ATTN(128, 4); else B200Q_ATTN(128, 8);

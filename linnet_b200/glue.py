@@ -45,9 +45,13 @@ def rope_cache(qkv: torch.Tensor, positions: torch.Tensor, cache_k: torch.Tensor
 
 
 def attention_splits(batch: int, nkv: int, max_seq: int, sms: int = 148) -> int:
-    """Key splits so that about two blocks per multiprocessor are in flight."""
-    want = max(1, (2 * sms) // max(1, batch * nkv))
-    return max(1, min(want, max_seq // 64, 64))
+    """Key splits (a power of two, at least 64 positions each) so that about eight blocks
+    per multiprocessor exist: enough for an even spread over the GPU."""
+    want = max(1, (8 * sms) // max(1, batch * nkv))
+    splits = 1
+    while splits * 2 <= want and max_seq // (splits * 2) >= 64:
+        splits *= 2
+    return splits
 
 
 def decode_attention(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor,
