@@ -366,6 +366,10 @@ def main() -> None:
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-other-configs", action="store_true")
     parser.add_argument("--no-decode", action="store_true")
+    parser.add_argument("--single-batch", action="store_true",
+                        help="decode: time only --batch, not 1 / 8 / 64 as well (for profiling)")
+    parser.add_argument("--reduce", default="peer", choices=["peer", "nccl"],
+                        help="tensor-parallel decode: one peer-memory kernel per reduction, or NCCL")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -422,7 +426,10 @@ def main() -> None:
             line["decode"] = {"metric": "8B-shape int4 decode tok/s", "tensor_parallel": world,
                               "tok_s": dec["value"], "ms_per_step": dec["ms_per_step"],
                               "per_batch": dec["per_batch"], "e2e": dec["e2e"], "steps": dargs.steps,
-                              "roofline": dec["roofline"], "config": dec["config"]}
+                              "roofline": dec["roofline"], "config": dec["config"],
+                              "reduce_route": dec["reduce_route"],
+                              **({"per_batch_nccl_route": dec["per_batch_nccl_route"]}
+                                 if "per_batch_nccl_route" in dec else {})}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -91,4 +91,13 @@ __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) {
     return __uint_as_float(bits16 << 16);
 }
 
+// Two bf16 values packed in 32 bits <-> f32.
+__device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
+__device__ __forceinline__ uint32_t bf16_pack(float lo, float hi) {
+    __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&p);
+}
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
 }  // namespace b200q

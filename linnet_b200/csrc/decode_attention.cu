@@ -1,0 +1,348 @@
+// Single-query (decode) attention over the KV cache, split over the keys and merged.
+//
+// In the reference this is `scaled_dot_product_attention` with a [B, 1, 1, S] mask and
+// `enable_gqa` inside the captured decode graph (examples/01-llama/src/attention.linnet run
+// by python/linnet/src/linnet/torch/compiled.py:430-503).  A decode step reads every
+// cached key and value once, so the kernel is bound by HBM: 2 * 2 * S * HD bytes per KV
+// head and row, shared by the REP = heads / kv_heads query heads of the group.
+//
+// Block (split, kv head, batch row), four warps.  The block streams its keys and values
+// through shared memory in chunks of 64 positions with 16-byte cp.async copies, three
+// chunks deep; each warp owns 16 positions of a chunk and runs them through the tensor
+// cores for all REP heads at once:
+//   scores [heads x 16 positions] = Q [heads(padded to 16) x HD] . K^T   (mma m16n8k16, K
+//       fragments by ldmatrix from the position-major tile),
+//   running softmax in f32 on the accumulator fragments (base 2, scale folded in),
+//   out [heads x HD] += P [heads x 16 positions] . V                      (V fragments by
+//       ldmatrix.trans; P reuses the score registers, rounded to bf16).
+// Rows of 2*HD bytes would put the eight rows of an ldmatrix on the same banks, so the
+// 16-byte pieces of a row are stored at piece ^ (position % 8).  The four warps' running
+// (max, sum, accumulator) are merged through shared memory into partial
+// [B, nq, splits, HD + 2] f32 (max in natural-log units), and a second small kernel merges
+// the splits.
+#include "common.cuh"
+
+namespace b200q {
+namespace {
+
+constexpr int kAttnChunk = 64;   // positions per shared-memory stage
+constexpr int kAttnStages = 3;
+constexpr int kAttnWarps = 4;    // 16 positions of a chunk each
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+// d += a . b with rows 8..15 of a all zero (a1 = a3 = 0): only d0, d1 carry data.
+__device__ __forceinline__ void mma_top(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+
+template <int HD, int REP>
+__global__ void __launch_bounds__(32 * kAttnWarps)
+attention_partial_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ cache_k,
+                         const uint16_t* __restrict__ cache_v, const int64_t* __restrict__ positions,
+                         float* __restrict__ partial, int nq, int nkv, int S, int splits, float scale_log2) {
+    static_assert(REP <= 8 && (HD == 64 || HD == 128), "heads of a group sit in rows 0..7 of the MMA");
+    constexpr int kRowBytes = HD * 2;
+    constexpr int kPieces = kRowBytes / 16;          // 16-byte pieces per row
+    constexpr int kStage = kAttnChunk * kRowBytes;   // bytes of K (or V) per chunk
+    constexpr int kThreads = 32 * kAttnWarps;
+    constexpr float kLn2 = 0.6931471805599453f;
+    extern __shared__ __align__(128) uint8_t attn_smem[];  // [stages][K chunk | V chunk]
+    pdl_wait();
+    pdl_launch_dependents();
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+    const int g = lane / 4, t = lane % 4;
+    const int keys = int(positions[b]) + 1;  // attend to positions 0 .. pos
+    const int per_split = (keys + splits - 1) / splits;
+    const int k0 = split * per_split, k1 = min(k0 + per_split, keys);
+    const int chunks = k1 > k0 ? (k1 - k0 + kAttnChunk - 1) / kAttnChunk : 0;
+    const size_t base = (size_t(b) * nkv + kvh) * S * HD;
+    const uint32_t smem0 = uint32_t(__cvta_generic_to_shared(attn_smem));
+
+    auto issue = [&](int c) {  // chunk c of this split -> stage c % kAttnStages (an empty group past the end)
+        if (c < chunks) {
+            const uint32_t dst = smem0 + (c % kAttnStages) * 2 * kStage;
+            const int first = k0 + c * kAttnChunk;
+            for (int piece = threadIdx.x; piece < 2 * kStage / 16; piece += kThreads) {
+                const int which = piece / (kStage / 16), within = piece % (kStage / 16);
+                const int row = within / kPieces, col = within % kPieces;
+                const int key = min(first + row, k1 - 1);  // the tail repeats the last key
+                const uint16_t* src = (which ? cache_v : cache_k) + base + size_t(key) * HD + col * 8;
+                const uint32_t d = dst + which * kStage + row * kRowBytes + ((col ^ (row & 7)) * 16);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    issue(0);
+    issue(1);
+
+    // Q as the A operand: row g = head g of the group (zero rows past REP), two registers per 16 dims.
+    uint32_t qa[HD / 16][2];
+    {
+        const uint16_t* qp = q + (size_t(b) * nq + kvh * REP + (g < REP ? g : 0)) * HD;
+#pragma unroll
+        for (int s = 0; s < HD / 16; ++s) {
+            const uint32_t lo = *reinterpret_cast<const uint32_t*>(qp + 16 * s + 2 * t);
+            const uint32_t hi = *reinterpret_cast<const uint32_t*>(qp + 16 * s + 8 + 2 * t);
+            qa[s][0] = g < REP ? lo : 0u;
+            qa[s][1] = g < REP ? hi : 0u;
+        }
+    }
+    float m = -INFINITY, l = 0.0f;  // running max (log2 units) and this lane's share of the sum, head g
+    float acc[HD / 8][4];
+#pragma unroll
+    for (int d = 0; d < HD / 8; ++d) acc[d][0] = acc[d][1] = acc[d][2] = acc[d][3] = 0.0f;
+
+    const int r0 = warp * 16;                       // this warp's rows of a chunk
+    const int lm_row = lane & 7, lm_mat = lane >> 3;  // ldmatrix: this lane addresses row lm_row of matrix lm_mat
+    for (int c = 0; c < chunks; ++c) {
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();  // chunk c has landed for everyone; everyone is done with chunk c - 1
+        issue(c + 2);     // into the stage chunk c - 1 used
+        const int first = k0 + c * kAttnChunk;
+        if (first + r0 >= k1) continue;  // warp-uniform: none of this warp's 16 positions exist
+        const uint32_t ks = smem0 + (c % kAttnStages) * 2 * kStage, vs = ks + kStage;
+
+        float sc[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f;
+            const int row = r0 + 8 * j + lm_row;
+#pragma unroll
+            for (int p = 0; p < HD / 32; ++p) {  // two 16-dim steps per ldmatrix
+                uint32_t kb[4];
+                ldmatrix_x4(kb, ks + row * kRowBytes + (((4 * p + lm_mat) ^ (row & 7)) * 16));
+                mma_top(sc[j], qa[2 * p][0], qa[2 * p][1], kb[0], kb[1]);
+                mma_top(sc[j], qa[2 * p + 1][0], qa[2 * p + 1][1], kb[2], kb[3]);
+            }
+        }
+        // scores of head g at positions first + r0 + 8 j + 2 t + {0, 1}
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const bool live = first + r0 + 8 * j + 2 * t + e < k1;
+                sc[j][e] = live ? sc[j][e] * scale_log2 : -INFINITY;
+                mx = fmaxf(mx, sc[j][e]);
+            }
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+        const float m_new = fmaxf(m, mx);  // finite: the warp's first position exists
+        const float corr = exp2f(m - m_new);
+        m = m_new;
+        float pr[2][2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) pr[j][e] = exp2f(sc[j][e] - m_new);
+        l = l * corr + (pr[0][0] + pr[0][1]) + (pr[1][0] + pr[1][1]);
+        const uint32_t pa0 = bf16_pack(pr[0][0], pr[0][1]), pa2 = bf16_pack(pr[1][0], pr[1][1]);
+#pragma unroll
+        for (int d = 0; d < HD / 8; ++d) {
+            acc[d][0] *= corr;
+            acc[d][1] *= corr;
+        }
+        {
+            const int row = r0 + (lm_mat & 1) * 8 + lm_row;
+#pragma unroll
+            for (int dp = 0; dp < HD / 16; ++dp) {  // two 8-dim blocks per ldmatrix
+                uint32_t vb[4];
+                ldmatrix_x4_trans(vb, vs + row * kRowBytes + (((2 * dp + (lm_mat >> 1)) ^ (row & 7)) * 16));
+                mma_top(acc[2 * dp], pa0, pa2, vb[0], vb[1]);
+                mma_top(acc[2 * dp + 1], pa0, pa2, vb[2], vb[3]);
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    l += __shfl_xor_sync(0xFFFFFFFFu, l, 1);
+    l += __shfl_xor_sync(0xFFFFFFFFu, l, 2);
+    __syncthreads();  // the stages are free: reuse them for the warps' results
+
+    float* merge = reinterpret_cast<float*>(attn_smem);  // [warp][head][HD + 2]
+    if (g < REP) {
+        float* mine = merge + (warp * REP + g) * (HD + 2);
+#pragma unroll
+        for (int d = 0; d < HD / 8; ++d) {
+            mine[8 * d + 2 * t] = acc[d][0];
+            mine[8 * d + 2 * t + 1] = acc[d][1];
+        }
+        if (t == 0) {
+            mine[HD] = m;
+            mine[HD + 1] = l;
+        }
+    }
+    __syncthreads();
+    for (int item = threadIdx.x; item < REP * (HD + 1); item += kThreads) {
+        const int head = item / (HD + 1), col = item % (HD + 1);  // col HD: the (max, sum) pair
+        float m_all = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) m_all = fmaxf(m_all, merge[(w * REP + head) * (HD + 2) + HD]);
+        float total = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) {
+            const float* theirs = merge + (w * REP + head) * (HD + 2);
+            const float weight = theirs[HD] == -INFINITY ? 0.0f : exp2f(theirs[HD] - m_all);
+            total += weight * theirs[col == HD ? HD + 1 : col];
+        }
+        float* out = partial + ((size_t(b) * nq + kvh * REP + head) * splits + split) * (HD + 2);
+        if (col == HD) {
+            out[HD] = m_all * kLn2;
+            out[HD + 1] = total;
+        } else {
+            out[col] = total;
+        }
+    }
+}
+
+template <int HD>
+__global__ void attention_merge_kernel(const float* __restrict__ partial, uint16_t* __restrict__ out,
+                                       int splits) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t head = blockIdx.x;  // b * nq + query head
+    const float* p = partial + head * splits * (HD + 2);
+    float m_all = -INFINITY;
+#pragma unroll 8
+    for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, p[s * (HD + 2) + HD]);
+    for (int dcol = threadIdx.x; dcol < HD; dcol += blockDim.x) {
+        float l_all = 0.0f, a_all = 0.0f;
+#pragma unroll 8
+        for (int s = 0; s < splits; ++s) {
+            const float ms = p[s * (HD + 2) + HD];
+            const float c = ms == -INFINITY ? 0.0f : __expf(ms - m_all);
+            l_all += p[s * (HD + 2) + HD + 1] * c;
+            a_all += p[s * (HD + 2) + dcol] * c;
+        }
+        out[head * HD + dcol] = uint16_t(bf16_pack(a_all / l_all, 0.0f) & 0xFFFF);
+    }
+}
+
+}  // namespace
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" int64_t b200q_decode_attention_scratch_bytes(int64_t batch, int64_t nq, int64_t head_dim,
+                                                        int64_t splits) {
+    return batch * nq * splits * (head_dim + 2) * 4;
+}
+
+namespace b200q {
+namespace {
+
+int32_t launch_attention(const char* who, const void* q, const void* cache_k, const void* cache_v,
+                         const int64_t* positions, void* out, void* scratch, int64_t batch, int64_t nq,
+                         int64_t nkv, int64_t head_dim, int64_t max_seq, int64_t splits, void* stream) {
+    B200Q_REQUIRE(batch >= 0 && nq > 0 && nkv > 0 && nq % nkv == 0 && splits >= 1 && splits <= 65535,
+                  "%s: bad shape", who);
+    if (batch == 0) return B200Q_OK;
+    const int rep = int(nq / nkv);
+    B200Q_REQUIRE((head_dim == 128 || head_dim == 64) && (rep == 1 || rep == 2 || rep == 4 || rep == 8),
+                  "%s: head_dim is 64 or 128 and heads / kv_heads is 1, 2, 4 or 8", who);
+    B200Q_REQUIRE(q && cache_k && cache_v && positions && out && scratch && aligned(q, 16) &&
+                      aligned(cache_k, 16) && aligned(cache_v, 16) && aligned(scratch, 16),
+                  "%s: tensors must be 16-byte aligned", who);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const dim3 grid{unsigned(splits), unsigned(nkv), unsigned(batch)};
+    const float scale_log2 = 1.4426950408889634f / sqrtf(float(head_dim));  // softmax in base 2
+#define B200Q_ATTN(HD, REP) do {                                                                      \
+    constexpr int kSmem = kAttnStages * 2 * kAttnChunk * HD * 2;                                      \
+    cudaFuncSetAttribute(attention_partial_kernel<HD, REP>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                         kSmem);                                                                      \
+    launch_overlapped(attention_partial_kernel<HD, REP>, grid, dim3(32 * kAttnWarps), size_t(kSmem), s, \
+                      static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(cache_k),         \
+                      static_cast<const uint16_t*>(cache_v), positions, static_cast<float*>(scratch), \
+                      int(nq), int(nkv), int(max_seq), int(splits), scale_log2); } while (0)
+    if (head_dim == 128) {
+        if (rep == 1) B200Q_ATTN(128, 1); else if (rep == 2) B200Q_ATTN(128, 2);
+        else if (rep == 4) B200Q_ATTN(128, 4); else B200Q_ATTN(128, 8);
+        launch_overlapped(attention_merge_kernel<128>, dim3(unsigned(batch * nq)), dim3(128), 0, s,
+                          static_cast<const float*>(scratch), static_cast<uint16_t*>(out), int(splits));
+    } else {
+        if (rep == 1) B200Q_ATTN(64, 1); else if (rep == 2) B200Q_ATTN(64, 2);
+        else if (rep == 4) B200Q_ATTN(64, 4); else B200Q_ATTN(64, 8);
+        launch_overlapped(attention_merge_kernel<64>, dim3(unsigned(batch * nq)), dim3(64), 0, s,
+                          static_cast<const float*>(scratch), static_cast<uint16_t*>(out), int(splits));
+    }
+#undef B200Q_ATTN
+    return launched(who);
+}
+
+}  // namespace
+}  // namespace b200q
+
+extern "C" int32_t b200q_decode_attention(const void* q, const void* cache_k, const void* cache_v,
+                                          const int64_t* positions, void* out, void* scratch,
+                                          int64_t batch, int64_t nq, int64_t nkv, int64_t head_dim,
+                                          int64_t max_seq, int64_t splits, void* stream) {
+    return launch_attention("decode_attention", q, cache_k, cache_v, positions, out, scratch, batch, nq,
+                            nkv, head_dim, max_seq, splits, stream);
+}
+
+// ---- the same attention for callers that cannot allocate device memory ----------------
+// Some hosts of this library have no way to hand it scratch memory: a runtime that owns a
+// fixed arena sized before the model is known, a plug-in loaded into a server whose
+// allocator is off limits to it, code running while a stream is being captured (no
+// cudaMalloc there).  For them the splits' partial results live in a fixed array inside
+// the library image instead: 4 MiB that every GPU which loads the library keeps until
+// the process exits.
+constexpr int64_t kStaticScratchBytes = int64_t(4) << 20;
+static __device__ __align__(256) unsigned char g_attention_scratch[kStaticScratchBytes];
+
+namespace b200q {
+namespace {
+
+// In host code `g_attention_scratch` is only a handle for the runtime, not a device
+// address; the address is asked for once per device, with that device current.
+void* static_scratch_address() {
+    static void* cached[64] = {nullptr};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return nullptr;
+    if (cached[device] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_attention_scratch) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        cached[device] = p;
+    }
+    return cached[device];
+}
+
+}  // namespace
+}  // namespace b200q
+
+extern "C" int64_t b200q_decode_attention_static_scratch_limit(void) { return kStaticScratchBytes; }
+
+extern "C" int32_t b200q_decode_attention_static(const void* q, const void* cache_k, const void* cache_v,
+                                                 const int64_t* positions, void* out, int64_t batch,
+                                                 int64_t nq, int64_t nkv, int64_t head_dim, int64_t max_seq,
+                                                 int64_t splits, void* stream) {
+    B200Q_REQUIRE(batch >= 0 && nq > 0 && head_dim > 0 && splits >= 1, "decode_attention_static: bad shape");
+    const int64_t need = b200q_decode_attention_scratch_bytes(batch, nq, head_dim, splits);
+    B200Q_REQUIRE(need <= kStaticScratchBytes,
+                  "decode_attention_static: batch %lld x %lld heads x %lld splits needs %lld bytes of scratch, "
+                  "the built-in array holds %lld; use fewer splits or b200q_decode_attention with your own scratch",
+                  (long long)batch, (long long)nq, (long long)splits, (long long)need,
+                  (long long)kStaticScratchBytes);
+    void* scratch = static_scratch_address();
+    B200Q_REQUIRE(scratch != nullptr, "decode_attention_static: cudaGetSymbolAddress failed on this device");
+    return launch_attention("decode_attention_static", q, cache_k, cache_v, positions, out, scratch, batch, nq,
+                            nkv, head_dim, max_seq, splits, stream);
+}
+

@@ -67,7 +67,8 @@ struct GemmArgs {
     const uint8_t* zero;    // [N, K/G]
     uint16_t* y;            // [M, N] bf16
     int M, K, N, G;
-    int m_tiles, n_tiles;   // tiles of 256 rows of X, of 128 rows of W
+    int m_tiles, n_tiles;   // tiles of 256 rows of X, of BN rows of W
+    int k_splits;           // > 1: a cluster of k_splits blocks shares one tile, each a slice of K
 };
 
 // Non-zero after a bounded wait expired in some launch on this device (the value
@@ -152,6 +153,24 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                      smem_u32(bar))
                  : "memory");
 }
+// 32 consecutive f32 columns of this thread's tensor-memory lane.
+__device__ __forceinline__ void tmem_load_32(uint32_t (&v)[32], uint32_t taddr) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+          "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
+          "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
+          "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// All threads of all blocks of the cluster; orders shared-memory accesses across the blocks.
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release;\nbarrier.cluster.wait.acquire;" ::: "memory");
+}
 // K-major, 128-byte swizzle: rows of 128 bytes, 8-row atoms 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
     return uint64_t((addr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) |
@@ -182,8 +201,15 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     Pipeline* pipe = reinterpret_cast<Pipeline*>(smem + kStages * kStageBytes);
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const int ksteps = a.K / kBK;
     const int tiles = a.m_tiles * a.n_tiles;
+    // Few rows and a narrow weight leave most multiprocessors without a tile; then a cluster
+    // of k_splits blocks takes one tile, block r the r-th slice of K, and the slices' f32
+    // accumulators are added through distributed shared memory at the end.  (k_splits == 1:
+    // persistent blocks striding over the tiles, all of K each.)
+    const int splits = a.k_splits, split = blockIdx.x % splits;
+    const int tile_first = blockIdx.x / splits, tile_stride = gridDim.x / splits;
+    const int k_per_split = (a.K / kBK + splits - 1) / splits;
+    const int ks_begin = split * k_per_split, ks_end = min(a.K / kBK, ks_begin + k_per_split);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -214,10 +240,10 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
         if (lane == 0) {
             uint32_t it = 0;  // stage uses so far
             bool ok = true;
-            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+            for (int tile = tile_first; tile < tiles && ok; tile += tile_stride) {
                 const int m0 = (tile % a.m_tiles) * (2 * kBM);
                 const bool two = m0 + kBM < a.M;
-                for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
+                for (int ks = ks_begin; ks < ks_end && ok; ++ks, ++it) {
                     const int s = it % kStages;
                     if (it >= kStages) ok = mbar_wait(&pipe->empty[s], ((it / kStages) - 1) & 1, &g_gemm_error, 1);
                     if (!ok) break;
@@ -233,14 +259,14 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
         if (lane == 0) {
             uint32_t it = 0, t = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++t) {
+            for (int tile = tile_first; tile < tiles && ok; tile += tile_stride, ++t) {
                 const int m0 = (tile % a.m_tiles) * (2 * kBM);
                 const bool two = m0 + kBM < a.M;
                 const uint32_t buf = t % kAccBufs;
                 if (t >= uint32_t(kAccBufs))
                     ok = mbar_wait(&pipe->acc_empty[buf], ((t / kAccBufs) - 1) & 1, &g_gemm_error, 2);
                 tc_fence_after();
-                for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
+                for (int ks = ks_begin; ks < ks_end && ok; ++ks, ++it) {
                     const int s = it % kStages;
                     const uint32_t parity = (it / kStages) & 1;
                     ok = mbar_wait(&pipe->full_a[s], parity, &g_gemm_error, 3) &&
@@ -251,7 +277,7 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
 #pragma unroll
                     for (int kk = 0; kk < kBK / 16; ++kk) {
                         const uint64_t b_desc = smem_desc(base + 2 * kATile + kk * 32);
-                        const uint32_t acc = (ks > 0 || kk > 0) ? 1u : 0u;
+                        const uint32_t acc = (ks > ks_begin || kk > 0) ? 1u : 0u;
                         umma_bf16(tmem + buf * (2 * kBN), smem_desc(base + kk * 32), b_desc, kIdesc, acc);
                         if (two) umma_bf16(tmem + buf * (2 * kBN) + kBN, smem_desc(base + kATile + kk * 32), b_desc, kIdesc, acc);
                     }
@@ -268,7 +294,7 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
         const int groups = a.K / a.G;
         uint32_t it = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        for (int tile = tile_first; tile < tiles && ok; tile += tile_stride) {
             const int n = min((tile / a.m_tiles) * kBN + row, a.N - 1);  // ragged tile: clamp
             const uint8_t* src = a.packed + size_t(n) * (a.K / 2) + half * 16;
             const uint16_t* srow = a.scale + size_t(n) * groups;
@@ -281,16 +307,16 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
                 sc = uint32_t(__ldg(srow + grp)) * 0x00010001u;
                 bias = 0x43004300u + uint32_t(__ldg(zrow + grp)) * 0x00010001u;
             };
-            const int first = int((group_id + kDequantGroups - it % kDequantGroups) % kDequantGroups);
+            const int first = ks_begin + int((group_id + kDequantGroups - it % kDequantGroups) % kDequantGroups);
             uint4 q_next = make_uint4(0, 0, 0, 0);
             uint32_t sc_next = 0, bias_next = 0;
-            if (first < ksteps) fetch(first, q_next, sc_next, bias_next);
-            for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
+            if (first < ks_end) fetch(first, q_next, sc_next, bias_next);
+            for (int ks = ks_begin; ks < ks_end && ok; ++ks, ++it) {
                 if (int(it % kDequantGroups) != group_id) continue;  // the other group's stage
                 const int s = it % kStages;
                 const uint4 q = q_next;
                 const uint32_t sc = sc_next, bias = bias_next;
-                if (ks + kDequantGroups < ksteps) fetch(ks + kDequantGroups, q_next, sc_next, bias_next);
+                if (ks + kDequantGroups < ks_end) fetch(ks + kDequantGroups, q_next, sc_next, bias_next);
                 if (it >= kStages) ok = mbar_wait(&pipe->empty[s], ((it / kStages) - 1) & 1, &g_gemm_error, 5);
                 if (!ok) break;
                 uint8_t* tile_b = smem + s * kStageBytes + 2 * kATile + row * 128;
@@ -322,12 +348,12 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
         // ---- epilogue (warps 0-3; warp w owns tensor-memory lanes 32w .. 32w+31) ---
         uint32_t t = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++t) {
+        for (int tile = tile_first; tile < tiles && ok; tile += tile_stride, ++t) {
             const int m0 = (tile % a.m_tiles) * (2 * kBM);
             const int n0 = (tile / a.m_tiles) * kBN;
             const uint32_t buf = t % kAccBufs;
             ok = mbar_wait(&pipe->acc_full[buf], (t / kAccBufs) & 1, &g_gemm_error, 6);
-            if (!ok) break;
+            if (!ok || splits > 1) break;  // a K slice: the cluster adds the slices below
             tc_fence_after();
 #pragma unroll 1
             for (int acc = 0; acc < 2; ++acc) {
@@ -337,17 +363,7 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
                 for (int c0 = 0; c0 < kBN; c0 += 32) {
                     uint32_t v[32];
                     const uint32_t taddr = tmem + (uint32_t(warp * 32) << 16) + buf * (2 * kBN) + acc * kBN + c0;
-                    asm volatile(
-                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-                        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-                          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-                          "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
-                          "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
-                          "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                        : "r"(taddr));
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    tmem_load_32(v, taddr);
                     if (m < a.M) {
                         uint16_t* dst = a.y + size_t(m) * a.N + n0 + c0;
                         if (n0 + c0 + 32 <= a.N && (a.N % 8) == 0) {
@@ -376,6 +392,46 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
     }
 
     // Every role falls through to here, also after an expired wait.
+    if (splits > 1) {
+        // The epilogue warps have seen acc_full, so once every thread of the cluster is here
+        // no tensor core, TMA or dequantizer of any block touches the stages any more:
+        // they become the exchange buffer [source block][128 rows][BN / splits columns] f32.
+        cluster_sync();
+        const int cps = kBN / splits;  // columns this block owns and reduces
+        float* exchange = reinterpret_cast<float*>(smem);
+        if (warp < kEpilogueWarps) {
+            tc_fence_after();
+            const int row = warp * 32 + lane;
+#pragma unroll 1
+            for (int c0 = 0; c0 < kBN; c0 += 32) {
+                uint32_t v[32];
+                tmem_load_32(v, tmem + (uint32_t(warp * 32) << 16) + c0);
+                if (row < a.M) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int col = c0 + 4 * j, owner = col / cps, within = col % cps;
+                        const uint32_t local = smem_u32(exchange + (size_t(split) * kBM + row) * cps + within);
+                        uint32_t remote;
+                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(owner));
+                        asm volatile("st.shared::cluster.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(remote), "r"(v[4 * j]),
+                                     "r"(v[4 * j + 1]), "r"(v[4 * j + 2]), "r"(v[4 * j + 3])
+                                     : "memory");
+                    }
+                }
+            }
+            tc_fence_before();
+        }
+        cluster_sync();  // every slice of my columns has arrived
+        const int n_base = (tile_first / a.m_tiles) * kBN + split * cps;
+        for (int item = threadIdx.x; item < kBM * cps; item += kThreads) {
+            const int row = item / cps, col = item % cps;
+            if (row < a.M && n_base + col < a.N) {
+                float sum = 0.0f;
+                for (int src = 0; src < splits; ++src) sum += exchange[(size_t(src) * kBM + row) * cps + col];
+                a.y[size_t(row) * a.N + n_base + col] = Half16<__nv_bfloat16>::from_float(sum);
+            }
+        }
+    }
     tc_fence_before();
     __syncthreads();
     if (warp == kMmaWarp) {
@@ -385,7 +441,8 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
     }
 }
 
-int g_force_bn = 0;  // measurement hook: B200Q_GEMM_BN=128|256 in the environment
+int g_force_bn = 0;      // measurement hook: B200Q_GEMM_BN=128|256 in the environment
+int g_force_splits = 0;  // measurement hook: B200Q_GEMM_SPLITS=1|2|4|8
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no libcuda link).
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -429,6 +486,8 @@ extern "C" int32_t b200q_int4_gemm(const void* x, const uint8_t* packed, const v
     static const bool env_read = [] {
         const char* v = getenv("B200Q_GEMM_BN");
         if (v != nullptr) g_force_bn = atoi(v);
+        v = getenv("B200Q_GEMM_SPLITS");
+        if (v != nullptr) g_force_splits = atoi(v);
         return true;
     }();
     (void)env_read;
@@ -452,12 +511,39 @@ extern "C" int32_t b200q_int4_gemm(const void* x, const uint8_t* packed, const v
     const int m_tiles = int((rows + 2 * kBM - 1) / (2 * kBM));
     const int64_t tiles128 = int64_t(m_tiles) * ((out + 127) / 128), tiles256 = int64_t(m_tiles) * ((out + 255) / 256);
     const double cost128 = double((tiles128 + sms - 1) / sms), cost256 = 1.25 * double((tiles256 + sms - 1) / sms);
-    const bool wide = g_force_bn == 256 || (g_force_bn != 128 && cost256 <= cost128);
+    // Up to 128 rows over a narrow weight: split K over a cluster while the tiles alone would
+    // leave more than half of the multiprocessors idle (every slice keeps >= 2 steps of 64).
+    int k_splits = 1;
+    const int ksteps = int(in / kBK);
+    if (rows <= kBM && g_force_splits != 1) {
+        const int64_t n_tiles = (out + 127) / 128;
+        while (k_splits < 8 && n_tiles * k_splits * 2 <= sms && ksteps / (k_splits * 2) >= 2) k_splits *= 2;
+        if (g_force_splits > 1) k_splits = g_force_splits;
+        while (k_splits > 1 && (k_splits - 1) * ((ksteps + k_splits - 1) / k_splits) >= ksteps) k_splits /= 2;
+    }
+    const bool wide = k_splits == 1 && (g_force_bn == 256 || (g_force_bn != 128 && cost256 <= cost128));
     GemmArgs a{packed, static_cast<const uint16_t*>(scale), zero, static_cast<uint16_t*>(y),
-               int(rows), int(in), int(out), int(group), m_tiles, int(wide ? (out + 255) / 256 : (out + 127) / 128)};
+               int(rows), int(in), int(out), int(group), m_tiles, int(wide ? (out + 255) / 256 : (out + 127) / 128),
+               k_splits};
     const int tiles = a.m_tiles * a.n_tiles;
-    const int grid = tiles < sms ? tiles : sms;
+    const int grid = k_splits > 1 ? tiles * k_splits : (tiles < sms ? tiles : sms);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (k_splits > 1) {
+        cudaFuncSetAttribute(int4_gemm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(Shape<128>::kSmem));
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(unsigned(grid));
+        config.blockDim = dim3(kThreads);
+        config.dynamicSmemBytes = Shape<128>::kSmem;
+        config.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = unsigned(k_splits);
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        config.attrs = attr;
+        config.numAttrs = 1;
+        return launch_status("int4_gemm", cudaLaunchKernelEx(&config, int4_gemm_kernel<128>, x_map, a));
+    }
     if (wide) {
         cudaFuncSetAttribute(int4_gemm_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(Shape<256>::kSmem));
         int4_gemm_kernel<256><<<grid, kThreads, Shape<256>::kSmem, s>>>(x_map, a);

@@ -1,0 +1,172 @@
+// Tensor-parallel epilogue of a row-split layer in ONE kernel: all-reduce of the ranks'
+// partial sums over NVLink peer memory + residual add + RMSNorm.
+//
+// The reference sums the partial results of a `Shards` card with
+// `std.nn.parallel::all_reduce` (stdlib/nn/parallel.linnet:9-11), which its runtime runs
+// as a one-shot Triton kernel over symmetric memory for messages up to 128 KiB and NCCL
+// otherwise (python/linnet/src/linnet/torch/collectives.py:145-167; kernel at
+// python/linnet/src/linnet/torch/kernels.py:1107-1156, which spins without a bound).  A
+// batch-1 decode step has 64 such reductions of 8 KiB: their latency, not their bytes,
+// is the cost, and each is followed by a residual add and a norm.  This kernel does the
+// three in one launch with plain peer loads (no multimem, no TMA):
+//   1. every rank's decode kernel has written its partial sums [rows, hidden] into its
+//      own symmetric buffer of this call site (one buffer per site, so a fast rank's next
+//      write to a site can only happen after every rank has passed the NEXT site, i.e.
+//      after it finished reading this one);
+//   2. block 0 publishes "rank r is at epoch e of this site" to every peer's flag word
+//      (fence.sys + st.release.sys); every block then waits, with a bound, until all
+//      ranks' flags of the site reach e;
+//   3. one block per row adds the ranks' partial sums in rank order (the same order on
+//      every rank, so all ranks get the same bits), rounds the sum to bf16 as an
+//      all-reduce of bf16 tensors returns it, adds it to the residual stream x in place
+//      and writes y = rms_norm(x) * weight.
+// Epochs live in device memory and advance once per call (the last block to finish bumps
+// the site's counter), so the kernel replays inside a CUDA graph.  A wait that runs out
+// (about a second) records an error code and lets the kernel finish with whatever it
+// has; the context stays usable, and later calls skip their waits until the host clears the code.
+#include "common.cuh"
+
+namespace b200q {
+namespace {
+
+constexpr int kMaxRanks = 8;
+
+struct Peers {
+    const uint16_t* partial[kMaxRanks];  // every rank's buffer of this site [rows, hidden] bf16
+    uint32_t* flags[kMaxRanks];          // every rank's flag words of this site [world]
+    int world, rank;
+};
+
+__device__ __forceinline__ float lo16(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float hi16(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+    __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&p);
+}
+__device__ __forceinline__ uint4 load_peer(const uint4* p) {  // never from a stale L1 line
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__global__ void __launch_bounds__(256)
+allreduce_add_rmsnorm_kernel(const Peers p, uint32_t* __restrict__ epoch, uint32_t* __restrict__ done,
+                             int* __restrict__ error, uint16_t* __restrict__ x,
+                             const uint16_t* __restrict__ weight, uint16_t* __restrict__ y, int hidden,
+                             float eps) {
+    __shared__ float partial_sums[8];
+    __shared__ int gave_up;
+    pdl_wait();  // this rank's partial sums come from the kernel before this one
+    pdl_launch_dependents();
+    const uint32_t e = *reinterpret_cast<volatile uint32_t*>(epoch) + 1;
+    // After one wait has run out every later call returns at once instead of waiting again.
+    if (threadIdx.x == 0) gave_up = *reinterpret_cast<volatile int*>(error) != 0;
+    if (blockIdx.x == 0 && int(threadIdx.x) < p.world) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flags[threadIdx.x] + p.rank), "r"(e) : "memory");
+    }
+    __syncthreads();
+    if (int(threadIdx.x) < p.world && !gave_up) {
+        const uint32_t* mine = p.flags[p.rank] + threadIdx.x;
+        uint64_t start = 0;
+        for (uint32_t spins = 0;; ++spins) {
+            uint32_t seen;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+            if (int32_t(seen - e) >= 0) break;
+            if ((spins & 255u) == 255u) {
+                uint64_t now;
+                asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+                if (start == 0) start = now;
+                if (now - start > 1000000000ull) {  // a peer never arrived: give up, stay usable
+                    atomicCAS(error, 0, 100 + int(threadIdx.x));
+                    gave_up = 1;
+                    break;
+                }
+            }
+        }
+    }
+    __syncthreads();
+
+    const int row = blockIdx.x, chunks = hidden / 8;
+    uint4* xr = reinterpret_cast<uint4*>(x + size_t(row) * hidden);
+    float sum_sq = 0.0f;
+    if (!gave_up) {
+        for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+            float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int r = 0; r < p.world; ++r) {
+                const uint4 v = load_peer(reinterpret_cast<const uint4*>(p.partial[r] + size_t(row) * hidden) + c);
+                s[0] += lo16(v.x); s[1] += hi16(v.x); s[2] += lo16(v.y); s[3] += hi16(v.y);
+                s[4] += lo16(v.z); s[5] += hi16(v.z); s[6] += lo16(v.w); s[7] += hi16(v.w);
+            }
+            uint4 v = xr[c];
+            // the reduced tensor is bf16 (one rounding), then the residual add rounds again
+            const uint32_t d0 = pack16(s[0], s[1]), d1 = pack16(s[2], s[3]), d2 = pack16(s[4], s[5]),
+                           d3 = pack16(s[6], s[7]);
+            v.x = pack16(lo16(v.x) + lo16(d0), hi16(v.x) + hi16(d0));
+            v.y = pack16(lo16(v.y) + lo16(d1), hi16(v.y) + hi16(d1));
+            v.z = pack16(lo16(v.z) + lo16(d2), hi16(v.z) + hi16(d2));
+            v.w = pack16(lo16(v.w) + lo16(d3), hi16(v.w) + hi16(d3));
+            xr[c] = v;
+            const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sum_sq += lo16(u[i]) * lo16(u[i]) + hi16(u[i]) * hi16(u[i]);
+        }
+    }
+    for (int d = 16; d >= 1; d >>= 1) sum_sq += __shfl_xor_sync(0xFFFFFFFFu, sum_sq, d);
+    if (threadIdx.x % 32 == 0) partial_sums[threadIdx.x / 32] = sum_sq;
+    __syncthreads();
+    float total = 0.0f;
+    for (int i = 0; i < int(blockDim.x) / 32; ++i) total += partial_sums[i];
+    const float rstd = rsqrtf(total / float(hidden) + eps);
+    const uint4* wr = reinterpret_cast<const uint4*>(weight);
+    uint4* yr = reinterpret_cast<uint4*>(y + size_t(row) * hidden);
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+        const uint4 v = xr[c], g = wr[c];
+        uint4 o;
+        o.x = pack16(lo16(v.x) * rstd * lo16(g.x), hi16(v.x) * rstd * hi16(g.x));
+        o.y = pack16(lo16(v.y) * rstd * lo16(g.y), hi16(v.y) * rstd * hi16(g.y));
+        o.z = pack16(lo16(v.z) * rstd * lo16(g.z), hi16(v.z) * rstd * hi16(g.z));
+        o.w = pack16(lo16(v.w) * rstd * lo16(g.w), hi16(v.w) * rstd * hi16(g.w));
+        yr[c] = o;
+    }
+    // The last block to finish advances the site's epoch (every block has read it by then).
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(done, 1u) == gridDim.x - 1) {
+            *done = 0;
+            *reinterpret_cast<volatile uint32_t*>(epoch) = e;
+        }
+    }
+}
+
+}  // namespace
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" int32_t b200q_tp_allreduce_add_rmsnorm(const int64_t* peer_partials, const int64_t* peer_flags,
+                                                  int32_t world, int32_t rank, void* epoch, void* done,
+                                                  void* error, void* x, const void* weight, void* y,
+                                                  int64_t rows, int64_t hidden, float eps, void* stream) {
+    B200Q_REQUIRE(world >= 2 && world <= kMaxRanks && rank >= 0 && rank < world,
+                  "tp_allreduce_add_rmsnorm: 2..8 ranks, got world=%d rank=%d", world, rank);
+    B200Q_REQUIRE(rows >= 0 && hidden > 0 && hidden % 8 == 0, "tp_allreduce_add_rmsnorm: hidden must be a multiple of 8");
+    if (rows == 0) return B200Q_OK;
+    B200Q_REQUIRE(peer_partials && peer_flags && epoch && done && error && x && weight && y,
+                  "tp_allreduce_add_rmsnorm: null argument");
+    Peers p{};
+    p.world = world;
+    p.rank = rank;
+    for (int r = 0; r < world; ++r) {
+        p.partial[r] = reinterpret_cast<const uint16_t*>(peer_partials[r]);
+        p.flags[r] = reinterpret_cast<uint32_t*>(peer_flags[r]);
+        B200Q_REQUIRE(p.partial[r] && p.flags[r] && aligned(p.partial[r], 16), "tp_allreduce_add_rmsnorm: bad peer pointer");
+    }
+    return launch_status("tp_allreduce_add_rmsnorm", launch_overlapped(
+        allreduce_add_rmsnorm_kernel, dim3(unsigned(rows)), dim3(256), 0, static_cast<cudaStream_t>(stream), p,
+        static_cast<uint32_t*>(epoch), static_cast<uint32_t*>(done), static_cast<int*>(error),
+        static_cast<uint16_t*>(x), static_cast<const uint16_t*>(weight), static_cast<uint16_t*>(y), int(hidden), eps));
+}

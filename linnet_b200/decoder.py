@@ -140,6 +140,7 @@ class Int4Decoder:
         self.linear, self.rank, self.tp, self.group = linear, rank, tp, group
         self.cache_k: list[torch.Tensor] = []
         self.cache_v: list[torch.Tensor] = []
+        self.peer_reduce = None  # set by enable_peer_reduce()
 
     # -- state ---------------------------------------------------------------------
     def allocate_cache(self, batch: int, fill: "torch.Generator | None" = None) -> None:
@@ -178,23 +179,41 @@ class Int4Decoder:
             return self._step_fused(tokens, positions)
         return self._step_torch(tokens, positions)
 
+    def enable_peer_reduce(self, max_rows: int) -> None:
+        """Replaces each NCCL all-reduce + residual add + norm of the fused route by one
+        peer-memory kernel (`linnet_b200.tp.PeerReduce`); collective: every rank calls it."""
+        from .tp import PeerReduce
+
+        if self.tp > 1:
+            self.peer_reduce = PeerReduce(2 * self.cfg.layers, max_rows, self.cfg.hidden, self.embed.device,
+                                          self.group)
+
+    def _reduce_norm(self, site: int, x: torch.Tensor, inputs: torch.Tensor, weight: Int4,
+                     norm: torch.Tensor) -> torch.Tensor:
+        """x += all_reduce(linear(inputs, weight)); returns rms_norm(x) * norm."""
+        from . import glue
+
+        if self.peer_reduce is not None and x.shape[0] <= self.peer_reduce.max_rows:
+            self.linear(inputs, *weight, out=self.peer_reduce.partial(site, x.shape[0]))
+            return self.peer_reduce.add_rmsnorm(site, x, norm, self.cfg.eps)
+        delta = self._all_reduce(self.linear(inputs, *weight))
+        return glue.add_rmsnorm(x, delta, norm, self.cfg.eps)
+
     def _step_fused(self, tokens: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         from . import glue
 
         cfg, tp = self.cfg, self.tp
         nq, nkv = cfg.heads // tp, cfg.kv_heads // tp
         x = self.embed[tokens]           # the residual stream, updated in place
-        delta = None                     # what the previous sub-layer adds to it
+        h = glue.add_rmsnorm(x, None, self.layers[0].norm1, cfg.eps)
         for i, w in enumerate(self.layers):
-            h = glue.add_rmsnorm(x, delta, w.norm1, cfg.eps)
             qkv = self.linear(h, *w.qkv)
             q = glue.rope_cache(qkv, positions, self.cache_k[i], self.cache_v[i], nq, nkv, cfg.rope_theta)
             attn = glue.decode_attention(q, self.cache_k[i], self.cache_v[i], positions)
-            delta = self._all_reduce(self.linear(attn, *w.o))
-            h = glue.add_rmsnorm(x, delta, w.norm2, cfg.eps)
+            h = self._reduce_norm(2 * i, x, attn, w.o, w.norm2)
             act = glue.silu_mul(self.linear(h, *w.gate_up))
-            delta = self._all_reduce(self.linear(act, *w.down))
-        h = glue.add_rmsnorm(x, delta, self.final_norm, cfg.eps)
+            following = self.layers[i + 1].norm1 if i + 1 < len(self.layers) else self.final_norm
+            h = self._reduce_norm(2 * i + 1, x, act, w.down, following)
         return self._all_gather(self.linear(h, *self.head))
 
     def _step_torch(self, tokens: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
@@ -283,12 +302,25 @@ def bench(args, rank: int, world: int, device: torch.device, barrier, reduce_max
     model = build_random(cfg, device, rank=rank, tp=world, seed=0, linear=kernels.int4_linear,
                          quantize=quant.quantize_int4_groups)
     results: dict[int, dict] = {}
+    nccl_results: dict[int, dict] = {}
     clocks = None
     stream = torch.cuda.Stream(device)
-    batches = [args.batch] + [b for b in (1, 8, 64) if b != args.batch]
+    batches = [args.batch]
+    if not getattr(args, "single_batch", False):
+        batches += [b for b in (1, 8, 64) if b != args.batch]
     e2e = {}
+    route = getattr(args, "reduce", "peer") if world > 1 else "none"
+    peer_reduce = None
+    if route == "peer":
+        model.enable_peer_reduce(max(batches))
+        peer_reduce = model.peer_reduce
+    # With the peer route on, the NCCL route is timed beside it (it is the baseline the
+    # fused kernel has to beat); the headline numbers are the selected route's.
+    passes = [(route, batches)] + ([("nccl", sorted(set(batches)))] if route == "peer" else [])
     with torch.cuda.stream(stream):
-        for batch in batches:
+        for which, batch in [(w, b) for w, bs in passes for b in bs]:
+            headline = which == route
+            model.peer_reduce = peer_reduce if which == "peer" else None
             fill = torch.Generator(device=device).manual_seed(7 + rank)
             model.allocate_cache(batch, fill)
             tok_gen = torch.Generator().manual_seed(11)
@@ -301,8 +333,9 @@ def bench(args, rank: int, world: int, device: torch.device, barrier, reduce_max
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 logits = model.step(tokens, positions)
-            steps = args.steps if batch == args.batch else max(5, args.steps // 4)
-            for _ in range(max(3, args.warmup if batch == args.batch else 3)):
+            main = headline and batch == args.batch
+            steps = args.steps if main else max(5, args.steps // 4)
+            for _ in range(max(3, args.warmup if main else 3)):
                 graph.replay()
             torch.cuda.synchronize()
             barrier()
@@ -317,16 +350,16 @@ def bench(args, rank: int, world: int, device: torch.device, barrier, reduce_max
                 torch.cuda.synchronize()
                 return start.elapsed_time(stop)
 
-            if batch == args.batch:
+            if main:
                 with clocks_cls(device.index or 0) as clocks:
                     ms = timed()
             else:
                 ms = timed()
             barrier()
             ms_step = reduce_max(ms) / steps
-            results[batch] = {"tok_s": batch / (ms_step / 1e3), "ms_per_step": ms_step,
+            (results if headline else nccl_results)[batch] = {"tok_s": batch / (ms_step / 1e3), "ms_per_step": ms_step,
                               "GB_s_per_gpu": decode_bytes(cfg, batch, world) / (ms_step / 1e3) / 1e9}
-            if batch == args.batch:
+            if main:
                 # End to end: token ids from pinned host memory in, sampled ids back out.
                 host_out = torch.empty(batch, dtype=torch.long).pin_memory()
                 barrier()
@@ -344,8 +377,12 @@ def bench(args, rank: int, world: int, device: torch.device, barrier, reduce_max
             torch.cuda.empty_cache()
     peaks_path = Path(__file__).resolve().parents[1] / "MEASURED_PEAKS.json"
     peak = float(json.loads(peaks_path.read_text())["hbm_gbs"]) if peaks_path.exists() else 6650.0
+    if peer_reduce is not None and peer_reduce.error():
+        raise RuntimeError(f"peer reduction gave up waiting for a rank (code {peer_reduce.error()})")
     main = results[args.batch]
-    launches_per_step = cfg.layers * 4 + 1
+    # per layer: 4 linears, 2 (reduce +) add + norm, rotary + cache write, attention + merge, silu*mul;
+    # then the first norm and the output head
+    launches_per_step = cfg.layers * 10 + 2
     return {
         "metric": "W4A16 g128 GEMV GB/s (% HBM peak); 8B-shape int4 decode tok/s at 1/2/4/8 GPU",
         "value": main["tok_s"], "unit": "tok/s", "n_gpus": world, "steps": args.steps,
@@ -363,6 +400,11 @@ def bench(args, rank: int, world: int, device: torch.device, barrier, reduce_max
                      "algorithmic_bytes_per_step_per_gpu": decode_bytes(cfg, args.batch, world),
                      "traffic": None},
         "per_batch": {str(b): results[b] for b in sorted(results)},
+        "reduce_route": {"none": "single GPU: no reduction",
+                         "peer": "one peer-memory kernel per row-split layer: all-reduce + residual add + RMSNorm",
+                         "nccl": "NCCL all-reduce, then the add + RMSNorm kernel"}[route],
+        **({"per_batch_nccl_route": {str(b): nccl_results[b] for b in sorted(nccl_results)}}
+           if nccl_results else {}),
         "e2e": e2e,
         "gpu_launches": args.steps * launches_per_step,
         "clocks": clocks.summary() if clocks else None,

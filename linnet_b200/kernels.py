@@ -60,7 +60,7 @@ class _Device:
 
 
 def _int4_linear(x: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor,
-                 zero: torch.Tensor) -> torch.Tensor:
+                 zero: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     rows, depth = x.shape
     width, groups, half = packed.shape
     group = 2 * half
@@ -76,7 +76,12 @@ def _int4_linear(x: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor,
         raise ValueError("int4_linear: packed weights and zero points are uint8")
     device = _on_gpu("int4_linear", x, packed, scale, zero)
     x, packed, scale, zero = x.contiguous(), packed.contiguous(), scale.contiguous(), zero.contiguous()
-    y = torch.empty(rows, width, dtype=x.dtype, device=device)
+    if out is None:
+        y = torch.empty(rows, width, dtype=x.dtype, device=device)
+    else:
+        if out.shape != (rows, width) or out.dtype != x.dtype or out.device != device or not out.is_contiguous():
+            raise ValueError(f"int4_linear: out must be a contiguous [{rows}, {width}] {x.dtype} tensor on {device}")
+        y = out
     with _Device(device):
         _lib.check(_lib.load().b200q_int4_linear(
             x.data_ptr(), packed.data_ptr(), scale.data_ptr(), zero.data_ptr(), y.data_ptr(),
@@ -96,14 +101,16 @@ def _(x, packed, scale, zero):
 
 
 def int4_linear(x: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor,
-                zero: torch.Tensor) -> torch.Tensor:
+                zero: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """`F.linear(x, W)` for `x` [rows, In] (bf16 or f16) and the group-wise 4-bit weight
     of `std.quant::linear_int4_groups`: `packed` [Out, Groups, Group/2] u8 (even value
     low), `scale` and `zero` [Out, Groups].  Any row count: up to 16 rows stream the
-    weight once at HBM speed, more go through the tensor-memory GEMM."""
-    if torch.compiler.is_compiling():
+    weight once at HBM speed, more go through the tensor-memory GEMM.  `out` (eager
+    calls only) receives the result in place of a new tensor, e.g. a buffer in peer-mapped
+    memory that a tensor-parallel reduction reads next."""
+    if out is None and torch.compiler.is_compiling():
         return _int4_linear_op(x, packed, scale, zero)
-    return _int4_linear(x, packed, scale, zero)
+    return _int4_linear(x, packed, scale, zero, out)
 
 
 def int4_dequantize(packed: torch.Tensor, scale: torch.Tensor, zero: torch.Tensor) -> torch.Tensor:

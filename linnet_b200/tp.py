@@ -1,0 +1,85 @@
+"""Peer-memory reduction for the tensor-parallel decoder: the all-reduce after a
+row-split layer, the residual add and the RMSNorm that follow it, as one launch of
+`b200q_tp_allreduce_add_rmsnorm` per call site.
+
+The reference routes `std.nn.parallel::all_reduce` through a one-shot kernel over
+symmetric memory when the message is small and through NCCL otherwise
+(python/linnet/src/linnet/torch/collectives.py:145-167).  This is the same idea with the
+two ops that always follow it in a decoder layer folded in, and with every wait bounded.
+
+Memory comes from `torch.distributed._symmetric_memory` (one allocation per rank, mapped
+into every peer by `rendezvous`); the kernel uses plain peer loads and stores only.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+
+class PeerReduce:
+    """`sites` independent call sites of up to `max_rows` x `hidden` bf16 partial sums each.
+
+    Per call site: `partial(site, rows)` is the tensor this rank's row-split linear writes
+    its partial result into; `add_rmsnorm(site, x, weight, eps)` then reduces the ranks'
+    partials, adds the sum to `x` in place and returns `rms_norm(x) * weight`.  Every rank
+    must visit the sites in the same order, and at least two different sites must alternate
+    (a site's buffer is safe to rewrite once any other site's reduction has been issued).
+    """
+
+    def __init__(self, sites: int, max_rows: int, hidden: int, device: torch.device,
+                 group: "dist.ProcessGroup | None" = None) -> None:
+        import torch.distributed._symmetric_memory as symm
+
+        if sites < 2:
+            raise ValueError("PeerReduce needs at least two call sites")
+        group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if not 2 <= self.world <= 8:
+            raise ValueError(f"PeerReduce runs on 2..8 ranks, not {self.world}")
+        self.sites, self.max_rows, self.hidden, self.device = sites, max_rows, hidden, device
+        self.site_bytes = max_rows * hidden * 2
+        self.flag_bytes = 32  # 8 ranks x uint32 per site
+        total = sites * (self.site_bytes + self.flag_bytes)
+        self.memory = symm.empty(total, dtype=torch.uint8, device=device)
+        self.memory.zero_()
+        self.handle = symm.rendezvous(self.memory, group=group)
+        self.bases = [int(p) for p in self.handle.buffer_ptrs]
+        # epoch and done counters per site, one error word
+        self.state = torch.zeros(2 * sites + 1, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)  # nobody signals before every rank's flags are zero
+        int64s = ctypes.c_int64 * self.world
+        self._partials = [int64s(*[b + s * self.site_bytes for b in self.bases]) for s in range(sites)]
+        flags0 = sites * self.site_bytes
+        self._flags = [int64s(*[b + flags0 + s * self.flag_bytes for b in self.bases]) for s in range(sites)]
+
+    def partial(self, site: int, rows: int) -> torch.Tensor:
+        """This rank's `[rows, hidden]` bf16 buffer of a call site (a view of the symmetric memory)."""
+        if not 0 <= site < self.sites or not 0 < rows <= self.max_rows:
+            raise ValueError(f"PeerReduce: site {site} / rows {rows} outside {self.sites} sites of {self.max_rows} rows")
+        start = site * self.site_bytes
+        return self.memory[start:start + rows * self.hidden * 2].view(torch.bfloat16).view(rows, self.hidden)
+
+    def add_rmsnorm(self, site: int, x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+        rows, hidden = x.shape
+        if hidden != self.hidden or not 0 < rows <= self.max_rows or not 0 <= site < self.sites:
+            raise ValueError("PeerReduce.add_rmsnorm: shape or site outside what was allocated")
+        if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or not x.is_contiguous():
+            raise ValueError("PeerReduce.add_rmsnorm: contiguous bf16 tensors only")
+        y = torch.empty_like(x)
+        state = self.state.data_ptr()
+        _lib.check(_lib.load().b200q_tp_allreduce_add_rmsnorm(
+            ctypes.addressof(self._partials[site]), ctypes.addressof(self._flags[site]), self.world, self.rank,
+            state + 4 * site, state + 4 * (self.sites + site), state + 8 * self.sites,
+            x.data_ptr(), weight.contiguous().data_ptr(), y.data_ptr(), rows, hidden, float(eps),
+            torch.cuda.current_stream(self.device).cuda_stream))
+        return y
+
+    def error(self) -> int:
+        """0, or 100 + r when a wait for rank r ran out (synchronises the device)."""
+        return int(self.state[2 * self.sites].item())

@@ -44,6 +44,9 @@ def close(got, want, what):
 @pytest.mark.parametrize(("rows", "depth", "out", "group"), [
     (128, 64, 128, 64), (256, 128, 128, 128), (48, 512, 72, 128), (129, 256, 200, 64),
     (300, 1024, 384, 128), (257, 512, 130, 256), (1, 128, 16, 128), (640, 192, 136, 64),
+    # up to 128 rows over a narrow weight: K split over a cluster of 2, 4 or 8 blocks
+    (64, 4096, 4096, 128), (64, 14336, 512, 128), (100, 1024, 200, 64), (33, 640, 130, 64),
+    (128, 1152, 256, 128), (17, 448, 130, 64),
 ])
 def test_gemm_matches_oracle(rows, depth, out, group):
     packed, scale, zero, gen = random_int4(out, depth, group, rows + depth + out)

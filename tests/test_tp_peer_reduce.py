@@ -1,0 +1,104 @@
+"""The peer-memory all-reduce + residual add + RMSNorm kernel against NCCL + the
+single-GPU kernel it replaces, on two GPUs of one box (skipped with fewer)."""
+
+from __future__ import annotations
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from linnet_b200 import decoder as dec
+from tests import decoder_util as du
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
+    from linnet_b200 import glue, kernels
+    from linnet_b200.tp import PeerReduce
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    report: dict = {}
+    try:
+        # 1. the kernel alone, three call sites visited round-robin, several epochs
+        hidden, rows, sites = 1024, 5, 3
+        reduce = PeerReduce(sites, 8, hidden, dev)
+        gen = torch.Generator(device=dev).manual_seed(100 + rank)
+        shared = torch.Generator(device=dev).manual_seed(7)
+        weight = (1 + 0.1 * torch.randn(hidden, device=dev, generator=shared)).to(torch.bfloat16)
+        exact = True
+        for epoch in range(4):
+            for site in range(sites):
+                part = torch.randn(rows, hidden, device=dev, generator=gen).to(torch.bfloat16)
+                x = torch.randn(rows, hidden, device=dev, generator=shared).to(torch.bfloat16)
+                reduce.partial(site, rows).copy_(part)
+                x_peer = x.clone()
+                y_peer = reduce.add_rmsnorm(site, x_peer, weight, 1e-5)
+                # what it replaces: all ranks' partials summed in rank order in f32, rounded once
+                parts = [torch.empty_like(part) for _ in range(world)]
+                dist.all_gather(parts, part)
+                total = torch.zeros(rows, hidden, device=dev)
+                for p in parts:
+                    total += p.float()
+                x_ref = x.clone()
+                y_ref = glue.add_rmsnorm(x_ref, total.to(torch.bfloat16), weight, 1e-5)
+                exact &= bool(torch.equal(x_peer, x_ref)) and bool(torch.equal(y_peer, y_ref))
+        report["kernel_exact"] = exact
+        report["kernel_error"] = reduce.error()
+
+        # 2. the decoder: NCCL route and peer route produce the same logits, eagerly and replayed
+        cfg = dec.DecoderConfig.tiny()
+        whole = du.whole_model(cfg)
+        logits = {}
+        for route in ("nccl", "peer"):
+            model = du.rank_model(cfg, whole, rank, world, kernels.int4_linear, device=dev)
+            if route == "peer":
+                model.enable_peer_reduce(4)
+            logits[route] = du.run_steps(model, cfg, batch=4, steps=3, device=dev).float()
+        report["decoder_max_diff"] = (logits["nccl"] - logits["peer"]).abs().max().item()
+        report["decoder_scale"] = logits["nccl"].abs().max().item()
+
+        tokens = torch.tensor([3, 5, 7, 9], device=dev)
+        positions = torch.full((4,), 3, device=dev, dtype=torch.long)
+        stream = torch.cuda.Stream(dev)
+        with torch.cuda.stream(stream):
+            eager = model.step(tokens, positions).clone()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                out = model.step(tokens, positions)
+            for _ in range(5):
+                graph.replay()
+            torch.cuda.synchronize()
+        report["replay_equal"] = bool(torch.equal(out, eager))
+        report["decoder_error"] = model.peer_reduce.error()
+        dist.barrier()
+        torch.save(report, os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_reduce_matches_nccl_route(tmp_path):
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for rank in range(world):
+        report = torch.load(tmp_path / f"rank{rank}.pt")
+        assert report["kernel_error"] == 0 and report["decoder_error"] == 0
+        assert report["kernel_exact"], "peer reduction differs from the rank-ordered f32 sum"
+        # two ranks: NCCL's bf16 sum and the f32 sum rounded once are the same number
+        assert report["decoder_max_diff"] <= 1e-3 * report["decoder_scale"]
+        assert report["replay_equal"]
