@@ -151,6 +151,15 @@ int32_t b200q_decode_attention(const void* q, const void* cache_k, const void* c
                                int64_t batch, int64_t nq, int64_t nkv, int64_t head_dim,
                                int64_t max_seq, int64_t splits, void* stream);
 
+
+/* b200q_decode_attention in one launch and without scratch: the `splits` (1 to 8) blocks
+ * of a (row, kv head) form one thread-block cluster and merge their partial results through
+ * distributed shared memory.  Allocates nothing.  No reference counterpart: the reference
+ * runs PyTorch's attention here. */
+int32_t b200q_decode_attention_cluster(const void* q, const void* cache_k, const void* cache_v,
+                                       const int64_t* positions, void* out, int64_t batch,
+                                       int64_t nq, int64_t nkv, int64_t head_dim,
+                                       int64_t max_seq, int64_t splits, void* stream);
 /* b200q_decode_attention for hosts that cannot give it scratch memory (a runtime with a
  * fixed arena, a plug-in without access to the allocator, a caller inside a stream
  * capture): the partial results go to a 4 MiB array built into the library, which every

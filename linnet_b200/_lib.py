@@ -40,6 +40,8 @@ PROTOTYPES: dict[str, list] = {
     "b200q_decode_attention_scratch_bytes": [c_int64, c_int64, c_int64, c_int64],
     "b200q_decode_attention": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p],
+    "b200q_decode_attention_cluster": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                       c_int64, c_int64, c_int64, c_int64, c_void_p],
     "b200q_decode_attention_static_scratch_limit": [],
     "b200q_decode_attention_static": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                       c_int64, c_int64, c_int64, c_int64, c_void_p],

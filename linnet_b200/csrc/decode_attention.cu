@@ -8,7 +8,7 @@
 //
 // Block (split, kv head, batch row), four warps.  The block streams its keys and values
 // through shared memory in chunks of 64 positions with 16-byte cp.async copies, three
-// chunks deep; each warp owns 16 positions of a chunk and runs them through the tensor
+// chunks deep (six when there are fewer blocks than multiprocessors); each warp owns 16 positions of a chunk and runs them through the tensor
 // cores for all REP heads at once:
 //   scores [heads x 16 positions] = Q [heads(padded to 16) x HD] . K^T   (mma m16n8k16, K
 //       fragments by ldmatrix from the position-major tile),
@@ -20,13 +20,17 @@
 // (max, sum, accumulator) are merged through shared memory into partial
 // [B, nq, splits, HD + 2] f32 (max in natural-log units), and a second small kernel merges
 // the splits.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace b200q {
+namespace cg = cooperative_groups;
 namespace {
 
 constexpr int kAttnChunk = 64;   // positions per shared-memory stage
-constexpr int kAttnStages = 3;
+constexpr int kAttnStages = 3;      // with more blocks than multiprocessors (two blocks fit on one)
+constexpr int kAttnStagesDeep = 6;  // with fewer: one block a multiprocessor, more of its keys in flight
 constexpr int kAttnWarps = 4;    // 16 positions of a chunk each
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
@@ -52,7 +56,8 @@ template <int HD, int REP>
 __global__ void __launch_bounds__(32 * kAttnWarps)
 attention_partial_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ cache_k,
                          const uint16_t* __restrict__ cache_v, const int64_t* __restrict__ positions,
-                         float* __restrict__ partial, int nq, int nkv, int S, int splits, float scale_log2) {
+                         float* __restrict__ partial, uint16_t* __restrict__ out_final, int nq, int nkv,
+                         int S, int splits, int stages, float scale_log2) {
     static_assert(REP <= 8 && (HD == 64 || HD == 128), "heads of a group sit in rows 0..7 of the MMA");
     constexpr int kRowBytes = HD * 2;
     constexpr int kPieces = kRowBytes / 16;          // 16-byte pieces per row
@@ -74,7 +79,7 @@ attention_partial_kernel(const uint16_t* __restrict__ q, const uint16_t* __restr
 
     auto issue = [&](int c) {  // chunk c of this split -> stage c % kAttnStages (an empty group past the end)
         if (c < chunks) {
-            const uint32_t dst = smem0 + (c % kAttnStages) * 2 * kStage;
+            const uint32_t dst = smem0 + (c % stages) * 2 * kStage;
             const int first = k0 + c * kAttnChunk;
             for (int piece = threadIdx.x; piece < 2 * kStage / 16; piece += kThreads) {
                 const int which = piece / (kStage / 16), within = piece % (kStage / 16);
@@ -87,8 +92,7 @@ attention_partial_kernel(const uint16_t* __restrict__ q, const uint16_t* __restr
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    issue(0);
-    issue(1);
+    for (int c = 0; c < stages - 1; ++c) issue(c);
 
     // Q as the A operand: row g = head g of the group (zero rows past REP), two registers per 16 dims.
     uint32_t qa[HD / 16][2];
@@ -110,12 +114,13 @@ attention_partial_kernel(const uint16_t* __restrict__ q, const uint16_t* __restr
     const int r0 = warp * 16;                       // this warp's rows of a chunk
     const int lm_row = lane & 7, lm_mat = lane >> 3;  // ldmatrix: this lane addresses row lm_row of matrix lm_mat
     for (int c = 0; c < chunks; ++c) {
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        if (stages == kAttnStagesDeep) asm volatile("cp.async.wait_group 4;" ::: "memory");
+        else asm volatile("cp.async.wait_group 1;" ::: "memory");
         __syncthreads();  // chunk c has landed for everyone; everyone is done with chunk c - 1
-        issue(c + 2);     // into the stage chunk c - 1 used
+        issue(c + stages - 1);  // into the stage chunk c - 1 used
         const int first = k0 + c * kAttnChunk;
         if (first + r0 >= k1) continue;  // warp-uniform: none of this warp's 16 positions exist
-        const uint32_t ks = smem0 + (c % kAttnStages) * 2 * kStage, vs = ks + kStage;
+        const uint32_t ks = smem0 + (c % stages) * 2 * kStage, vs = ks + kStage;
 
         float sc[2][4];
 #pragma unroll
@@ -187,6 +192,10 @@ attention_partial_kernel(const uint16_t* __restrict__ q, const uint16_t* __restr
         }
     }
     __syncthreads();
+    // partial == nullptr: the splits of a (row, kv head) form one thread-block cluster and
+    // merge through distributed shared memory; otherwise a second kernel merges `partial`.
+    const bool in_cluster = partial == nullptr;
+    float* block_result = merge + kAttnWarps * REP * (HD + 2);  // [head][HD + 2], max in log2 units
     for (int item = threadIdx.x; item < REP * (HD + 1); item += kThreads) {
         const int head = item / (HD + 1), col = item % (HD + 1);  // col HD: the (max, sum) pair
         float m_all = -INFINITY;
@@ -199,14 +208,47 @@ attention_partial_kernel(const uint16_t* __restrict__ q, const uint16_t* __restr
             const float weight = theirs[HD] == -INFINITY ? 0.0f : exp2f(theirs[HD] - m_all);
             total += weight * theirs[col == HD ? HD + 1 : col];
         }
-        float* out = partial + ((size_t(b) * nq + kvh * REP + head) * splits + split) * (HD + 2);
+        float* out = in_cluster ? block_result + head * (HD + 2)
+                                : partial + ((size_t(b) * nq + kvh * REP + head) * splits + split) * (HD + 2);
         if (col == HD) {
-            out[HD] = m_all * kLn2;
+            out[HD] = in_cluster ? m_all : m_all * kLn2;
             out[HD + 1] = total;
         } else {
             out[col] = total;
         }
     }
+    if (!in_cluster) return;
+
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();  // every split's result is in its block's shared memory
+    // Block r of the cluster finishes every splits-th (head, dim) pair.
+    for (int item = split + splits * threadIdx.x; item < REP * HD; item += splits * kThreads) {
+        const int head = item / HD, dcol = item % HD;
+        float m_s[8], l_s[8], a_s[8];
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp) {
+            m_s[sp] = -INFINITY;
+            l_s[sp] = a_s[sp] = 0.0f;
+            if (sp < splits) {
+                const float* theirs = cluster.map_shared_rank(block_result, sp) + head * (HD + 2);
+                m_s[sp] = theirs[HD];
+                l_s[sp] = theirs[HD + 1];
+                a_s[sp] = theirs[dcol];
+            }
+        }
+        float m_all = -INFINITY;
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp) m_all = fmaxf(m_all, m_s[sp]);
+        float l_all = 0.0f, a_all = 0.0f;
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp) {
+            const float c = m_s[sp] == -INFINITY ? 0.0f : exp2f(m_s[sp] - m_all);
+            l_all += l_s[sp] * c;
+            a_all += a_s[sp] * c;
+        }
+        out_final[(size_t(b) * nq + kvh * REP + head) * HD + dcol] = uint16_t(bf16_pack(a_all / l_all, 0.0f) & 0xFFFF);
+    }
+    cluster.sync();  // nobody leaves while a peer may still read its shared memory
 }
 
 template <int HD>
@@ -247,40 +289,61 @@ namespace {
 
 int32_t launch_attention(const char* who, const void* q, const void* cache_k, const void* cache_v,
                          const int64_t* positions, void* out, void* scratch, int64_t batch, int64_t nq,
-                         int64_t nkv, int64_t head_dim, int64_t max_seq, int64_t splits, void* stream) {
+                         int64_t nkv, int64_t head_dim, int64_t max_seq, int64_t splits, void* stream,
+                         bool in_cluster = false) {
     B200Q_REQUIRE(batch >= 0 && nq > 0 && nkv > 0 && nq % nkv == 0 && splits >= 1 && splits <= 65535,
                   "%s: bad shape", who);
     if (batch == 0) return B200Q_OK;
     const int rep = int(nq / nkv);
     B200Q_REQUIRE((head_dim == 128 || head_dim == 64) && (rep == 1 || rep == 2 || rep == 4 || rep == 8),
                   "%s: head_dim is 64 or 128 and heads / kv_heads is 1, 2, 4 or 8", who);
-    B200Q_REQUIRE(q && cache_k && cache_v && positions && out && scratch && aligned(q, 16) &&
+    B200Q_REQUIRE(q && cache_k && cache_v && positions && out && (scratch || in_cluster) && aligned(q, 16) &&
                       aligned(cache_k, 16) && aligned(cache_v, 16) && aligned(scratch, 16),
                   "%s: tensors must be 16-byte aligned", who);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const dim3 grid{unsigned(splits), unsigned(nkv), unsigned(batch)};
     const float scale_log2 = 1.4426950408889634f / sqrtf(float(head_dim));  // softmax in base 2
 #define B200Q_ATTN(HD, REP) do {                                                                      \
-    constexpr int kSmem = kAttnStages * 2 * kAttnChunk * HD * 2;                                      \
+    const int kSmem = stages * 2 * kAttnChunk * HD * 2;                                               \
     cudaFuncSetAttribute(attention_partial_kernel<HD, REP>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                         kSmem);                                                                      \
-    launch_overlapped(attention_partial_kernel<HD, REP>, grid, dim3(32 * kAttnWarps), size_t(kSmem), s, \
+                         kAttnStagesDeep * 2 * kAttnChunk * HD * 2);                                  \
+    cudaLaunchConfig_t config = {};                                                                   \
+    config.gridDim = grid;                                                                            \
+    config.blockDim = dim3(32 * kAttnWarps);                                                          \
+    config.dynamicSmemBytes = kSmem;                                                                  \
+    config.stream = s;                                                                                \
+    cudaLaunchAttribute attr[2];                                                                      \
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                                  \
+    attr[0].val.programmaticStreamSerializationAllowed = 1;                                           \
+    attr[1].id = cudaLaunchAttributeClusterDimension;                                                 \
+    attr[1].val.clusterDim.x = unsigned(splits);                                                      \
+    attr[1].val.clusterDim.y = 1;                                                                     \
+    attr[1].val.clusterDim.z = 1;                                                                     \
+    config.attrs = attr;                                                                              \
+    config.numAttrs = in_cluster ? 2 : 1;                                                             \
+    err = cudaLaunchKernelEx(&config, attention_partial_kernel<HD, REP>,                              \
                       static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(cache_k),         \
-                      static_cast<const uint16_t*>(cache_v), positions, static_cast<float*>(scratch), \
-                      int(nq), int(nkv), int(max_seq), int(splits), scale_log2); } while (0)
+                      static_cast<const uint16_t*>(cache_v), positions,                               \
+                      in_cluster ? static_cast<float*>(nullptr) : static_cast<float*>(scratch),      \
+                      static_cast<uint16_t*>(out), int(nq), int(nkv), int(max_seq), int(splits),      \
+                      stages, scale_log2); } while (0)
+    cudaError_t err = cudaSuccess;
+    const int stages = splits * nkv * batch <= sm_count() ? kAttnStagesDeep : kAttnStages;
     if (head_dim == 128) {
         if (rep == 1) B200Q_ATTN(128, 1); else if (rep == 2) B200Q_ATTN(128, 2);
         else if (rep == 4) B200Q_ATTN(128, 4); else B200Q_ATTN(128, 8);
-        launch_overlapped(attention_merge_kernel<128>, dim3(unsigned(batch * nq)), dim3(128), 0, s,
-                          static_cast<const float*>(scratch), static_cast<uint16_t*>(out), int(splits));
+        if (!in_cluster && err == cudaSuccess)
+            err = launch_overlapped(attention_merge_kernel<128>, dim3(unsigned(batch * nq)), dim3(128), 0, s,
+                              static_cast<const float*>(scratch), static_cast<uint16_t*>(out), int(splits));
     } else {
         if (rep == 1) B200Q_ATTN(64, 1); else if (rep == 2) B200Q_ATTN(64, 2);
         else if (rep == 4) B200Q_ATTN(64, 4); else B200Q_ATTN(64, 8);
-        launch_overlapped(attention_merge_kernel<64>, dim3(unsigned(batch * nq)), dim3(64), 0, s,
-                          static_cast<const float*>(scratch), static_cast<uint16_t*>(out), int(splits));
+        if (!in_cluster && err == cudaSuccess)
+            err = launch_overlapped(attention_merge_kernel<64>, dim3(unsigned(batch * nq)), dim3(64), 0, s,
+                              static_cast<const float*>(scratch), static_cast<uint16_t*>(out), int(splits));
     }
 #undef B200Q_ATTN
-    return launched(who);
+    return launch_status(who, err);
 }
 
 }  // namespace
@@ -292,6 +355,17 @@ extern "C" int32_t b200q_decode_attention(const void* q, const void* cache_k, co
                                           int64_t max_seq, int64_t splits, void* stream) {
     return launch_attention("decode_attention", q, cache_k, cache_v, positions, out, scratch, batch, nq,
                             nkv, head_dim, max_seq, splits, stream);
+}
+
+// One launch and no scratch: the splits (at most 8) of a (row, kv head) run as one
+// thread-block cluster and merge through distributed shared memory.
+extern "C" int32_t b200q_decode_attention_cluster(const void* q, const void* cache_k, const void* cache_v,
+                                                  const int64_t* positions, void* out, int64_t batch,
+                                                  int64_t nq, int64_t nkv, int64_t head_dim, int64_t max_seq,
+                                                  int64_t splits, void* stream) {
+    B200Q_REQUIRE(splits >= 1 && splits <= 8, "decode_attention_cluster: 1 to 8 splits, not %lld", (long long)splits);
+    return launch_attention("decode_attention_cluster", q, cache_k, cache_v, positions, out, nullptr, batch, nq,
+                            nkv, head_dim, max_seq, splits, stream, true);
 }
 
 // ---- the same attention for callers that cannot allocate device memory ----------------

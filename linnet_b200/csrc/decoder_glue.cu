@@ -16,29 +16,54 @@ namespace {
 
 // ---- x (+= delta); y = rms_norm(x) * w --------------------------------------------
 // One block per row; hidden is a multiple of 8.  x is updated in place when delta != null.
-__global__ void __launch_bounds__(256)
+// A decode step runs this on a handful of rows, so what counts is the length of the chain
+// of dependent memory round trips: the norm weights do not depend on the kernel before, so
+// they are fetched before waiting for it, and the row stays in registers between the sum of
+// squares and the scaling (CPT 16-byte pieces per thread; CPT = 0 re-reads x, any width).
+template <int CPT>
+__global__ void __launch_bounds__(512)
 add_rmsnorm_kernel(uint16_t* __restrict__ x, const uint16_t* __restrict__ delta,
                    const uint16_t* __restrict__ w, uint16_t* __restrict__ y, int hidden, float eps) {
-    __shared__ float partial[8];
+    __shared__ float partial[16];
+    constexpr int kHeld = CPT > 0 ? CPT : 1;
+    const int row = blockIdx.x, chunks = hidden / 8;
+    const uint4* wr = reinterpret_cast<const uint4*>(w);
+    uint4 g[kHeld], v[kHeld];
+    if (CPT > 0) {
+#pragma unroll
+        for (int u = 0; u < kHeld; ++u) {
+            const int c = threadIdx.x + u * blockDim.x;
+            g[u] = c < chunks ? __ldg(wr + c) : make_uint4(0, 0, 0, 0);
+        }
+    }
     pdl_wait();
     pdl_launch_dependents();
-    const int row = blockIdx.x, chunks = hidden / 8;
     uint4* xr = reinterpret_cast<uint4*>(x + size_t(row) * hidden);
     const uint4* dr = delta ? reinterpret_cast<const uint4*>(delta + size_t(row) * hidden) : nullptr;
     float sum = 0.0f;
-    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
-        uint4 v = xr[c];
+    auto add_and_square = [&](int c) {
+        uint4 t = xr[c];
         if (dr) {
             const uint4 d = dr[c];
-            v.x = bf16_pack(bf16_lo(v.x) + bf16_lo(d.x), bf16_hi(v.x) + bf16_hi(d.x));
-            v.y = bf16_pack(bf16_lo(v.y) + bf16_lo(d.y), bf16_hi(v.y) + bf16_hi(d.y));
-            v.z = bf16_pack(bf16_lo(v.z) + bf16_lo(d.z), bf16_hi(v.z) + bf16_hi(d.z));
-            v.w = bf16_pack(bf16_lo(v.w) + bf16_lo(d.w), bf16_hi(v.w) + bf16_hi(d.w));
-            xr[c] = v;
+            t.x = bf16_pack(bf16_lo(t.x) + bf16_lo(d.x), bf16_hi(t.x) + bf16_hi(d.x));
+            t.y = bf16_pack(bf16_lo(t.y) + bf16_lo(d.y), bf16_hi(t.y) + bf16_hi(d.y));
+            t.z = bf16_pack(bf16_lo(t.z) + bf16_lo(d.z), bf16_hi(t.z) + bf16_hi(d.z));
+            t.w = bf16_pack(bf16_lo(t.w) + bf16_lo(d.w), bf16_hi(t.w) + bf16_hi(d.w));
+            xr[c] = t;
         }
-        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+        const uint32_t e[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) sum += bf16_lo(u[i]) * bf16_lo(u[i]) + bf16_hi(u[i]) * bf16_hi(u[i]);
+        for (int i = 0; i < 4; ++i) sum += bf16_lo(e[i]) * bf16_lo(e[i]) + bf16_hi(e[i]) * bf16_hi(e[i]);
+        return t;
+    };
+    if (CPT > 0) {
+#pragma unroll
+        for (int u = 0; u < kHeld; ++u) {
+            const int c = threadIdx.x + u * blockDim.x;
+            v[u] = c < chunks ? add_and_square(c) : make_uint4(0, 0, 0, 0);
+        }
+    } else {
+        for (int c = threadIdx.x; c < chunks; c += blockDim.x) add_and_square(c);
     }
     for (int d = 16; d >= 1; d >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, d);
     if (threadIdx.x % 32 == 0) partial[threadIdx.x / 32] = sum;
@@ -46,16 +71,23 @@ add_rmsnorm_kernel(uint16_t* __restrict__ x, const uint16_t* __restrict__ delta,
     float total = 0.0f;
     for (int i = 0; i < int(blockDim.x) / 32; ++i) total += partial[i];
     const float rstd = rsqrtf(total / float(hidden) + eps);
-    const uint4* wr = reinterpret_cast<const uint4*>(w);
     uint4* yr = reinterpret_cast<uint4*>(y + size_t(row) * hidden);
-    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
-        const uint4 v = xr[c], g = wr[c];
+    auto scaled = [&](const uint4& t, const uint4& gw) {
         uint4 o;
-        o.x = bf16_pack(bf16_lo(v.x) * rstd * bf16_lo(g.x), bf16_hi(v.x) * rstd * bf16_hi(g.x));
-        o.y = bf16_pack(bf16_lo(v.y) * rstd * bf16_lo(g.y), bf16_hi(v.y) * rstd * bf16_hi(g.y));
-        o.z = bf16_pack(bf16_lo(v.z) * rstd * bf16_lo(g.z), bf16_hi(v.z) * rstd * bf16_hi(g.z));
-        o.w = bf16_pack(bf16_lo(v.w) * rstd * bf16_lo(g.w), bf16_hi(v.w) * rstd * bf16_hi(g.w));
-        yr[c] = o;
+        o.x = bf16_pack(bf16_lo(t.x) * rstd * bf16_lo(gw.x), bf16_hi(t.x) * rstd * bf16_hi(gw.x));
+        o.y = bf16_pack(bf16_lo(t.y) * rstd * bf16_lo(gw.y), bf16_hi(t.y) * rstd * bf16_hi(gw.y));
+        o.z = bf16_pack(bf16_lo(t.z) * rstd * bf16_lo(gw.z), bf16_hi(t.z) * rstd * bf16_hi(gw.z));
+        o.w = bf16_pack(bf16_lo(t.w) * rstd * bf16_lo(gw.w), bf16_hi(t.w) * rstd * bf16_hi(gw.w));
+        return o;
+    };
+    if (CPT > 0) {
+#pragma unroll
+        for (int u = 0; u < kHeld; ++u) {
+            const int c = threadIdx.x + u * blockDim.x;
+            if (c < chunks) yr[c] = scaled(v[u], g[u]);
+        }
+    } else {
+        for (int c = threadIdx.x; c < chunks; c += blockDim.x) yr[c] = scaled(xr[c], wr[c]);
     }
 }
 
@@ -120,10 +152,22 @@ extern "C" int32_t b200q_add_rmsnorm(void* x, const void* delta, const void* wei
     B200Q_REQUIRE(x && weight && y && aligned(x, 16) && aligned(weight, 16) && aligned(y, 16) &&
                       (!delta || aligned(delta, 16)),
                   "add_rmsnorm: tensors must be 16-byte aligned");
-    return launch_status("add_rmsnorm", launch_overlapped(
-        add_rmsnorm_kernel, dim3(unsigned(rows)), dim3(256), 0, static_cast<cudaStream_t>(stream),
-        static_cast<uint16_t*>(x), static_cast<const uint16_t*>(delta), static_cast<const uint16_t*>(weight),
-        static_cast<uint16_t*>(y), int(hidden), eps));
+    const int chunks = int(hidden / 8);
+    int threads = ((chunks + 31) / 32) * 32;
+    threads = threads > 512 ? 512 : threads;
+    const int held = (chunks + threads - 1) / threads;
+    const dim3 grid{unsigned(rows)}, block{unsigned(threads)};
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    uint16_t* xp = static_cast<uint16_t*>(x);
+    const uint16_t* dp = static_cast<const uint16_t*>(delta);
+    const uint16_t* wp = static_cast<const uint16_t*>(weight);
+    uint16_t* yp = static_cast<uint16_t*>(y);
+    cudaError_t err;
+    if (held <= 1) err = launch_overlapped(add_rmsnorm_kernel<1>, grid, block, 0, s, xp, dp, wp, yp, int(hidden), eps);
+    else if (held <= 2) err = launch_overlapped(add_rmsnorm_kernel<2>, grid, block, 0, s, xp, dp, wp, yp, int(hidden), eps);
+    else if (held <= 4) err = launch_overlapped(add_rmsnorm_kernel<4>, grid, block, 0, s, xp, dp, wp, yp, int(hidden), eps);
+    else err = launch_overlapped(add_rmsnorm_kernel<0>, grid, block, 0, s, xp, dp, wp, yp, int(hidden), eps);
+    return launch_status("add_rmsnorm", err);
 }
 
 extern "C" int32_t b200q_rope_cache(const void* qkv, const int64_t* positions, void* q_out, void* cache_k,

@@ -38,6 +38,7 @@ constexpr int kEpilogueWarps = 4, kTmaWarp = 4, kMmaWarp = 5, kFirstDequantWarp 
 constexpr int kAllDequantWarps = 16;
 constexpr int kThreads = (kFirstDequantWarp + kAllDequantWarps) * 32;  // 704
 constexpr uint32_t kTmemColumns = 512;
+constexpr int kPrefetch = 4;  // stages of packed weights each dequantizer thread keeps in flight
 
 // The tile's width BN (rows of W = columns of Y) decides how often X is re-read from L2:
 // every X element is loaded once per BN output columns.  At BN = 128 the X tiles alone
@@ -299,8 +300,10 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
             const uint8_t* src = a.packed + size_t(n) * (a.K / 2) + half * 16;
             const uint16_t* srow = a.scale + size_t(n) * groups;
             const uint8_t* zrow = a.zero + size_t(n) * groups;
-            // This thread's loads for its next stage are issued one stage ahead, so the
-            // L2 latency of the packed weights hides behind the previous stage's arithmetic.
+            // With few rows the weights stream from HBM exactly once, and what bounds the
+            // kernel is how many bytes each multiprocessor keeps in flight: the loads of this
+            // thread's next kPrefetch stages are always outstanding (16 bytes each, 512 or
+            // 256 threads a stage), so the HBM latency hides behind several stages of work.
             auto fetch = [&](int ks, uint4& q, uint32_t& sc, uint32_t& bias) {
                 q = __ldg(reinterpret_cast<const uint4*>(src + size_t(ks) * (kBK / 2)));
                 const int grp = (ks * kBK) / a.G;
@@ -308,41 +311,54 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
                 bias = 0x43004300u + uint32_t(__ldg(zrow + grp)) * 0x00010001u;
             };
             const int first = ks_begin + int((group_id + kDequantGroups - it % kDequantGroups) % kDequantGroups);
-            uint4 q_next = make_uint4(0, 0, 0, 0);
-            uint32_t sc_next = 0, bias_next = 0;
-            if (first < ks_end) fetch(first, q_next, sc_next, bias_next);
-            for (int ks = ks_begin; ks < ks_end && ok; ++ks, ++it) {
-                if (int(it % kDequantGroups) != group_id) continue;  // the other group's stage
-                const int s = it % kStages;
-                const uint4 q = q_next;
-                const uint32_t sc = sc_next, bias = bias_next;
-                if (ks + kDequantGroups < ks_end) fetch(ks + kDequantGroups, q_next, sc_next, bias_next);
-                if (it >= kStages) ok = mbar_wait(&pipe->empty[s], ((it / kStages) - 1) & 1, &g_gemm_error, 5);
-                if (!ok) break;
-                uint8_t* tile_b = smem + s * kStageBytes + 2 * kATile + row * 128;
-                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+            uint4 q_ring[kPrefetch];
+            uint32_t sc_ring[kPrefetch], bias_ring[kPrefetch];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    // (k0,k4) (k1,k5) (k2,k6) (k3,k7): magic + q, then exactly (q - zero) * scale
-                    uint32_t f[4];
-                    f[0] = lop3_and_or(w[i], 0x000F000Fu, 0x43004300u);
-                    f[1] = lop3_and_or(w[i] >> 4, 0x000F000Fu, 0x43004300u);
-                    f[2] = lop3_and_or(w[i] >> 8, 0x000F000Fu, 0x43004300u);
-                    f[3] = lop3_and_or(w[i] >> 12, 0x000F000Fu, 0x43004300u);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) f[e] = sub_mul<__nv_bfloat16>(f[e], bias, sc);
-                    uint4 out;  // natural order (k0,k1) (k2,k3) (k4,k5) (k6,k7)
-                    out.x = __byte_perm(f[0], f[1], 0x5410);
-                    out.y = __byte_perm(f[2], f[3], 0x5410);
-                    out.z = __byte_perm(f[0], f[1], 0x7632);
-                    out.w = __byte_perm(f[2], f[3], 0x7632);
-                    const int chunk = half * 4 + i;  // 16-byte chunk of the 128-byte row
-                    *reinterpret_cast<uint4*>(tile_b + ((chunk ^ (row & 7)) * 16)) = out;
-                }
-                fence_proxy_async();  // generic-proxy stores -> visible to the tensor core
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&pipe->full_b[s]);
+            for (int u = 0; u < kPrefetch; ++u) {
+                q_ring[u] = make_uint4(0, 0, 0, 0);
+                sc_ring[u] = bias_ring[u] = 0;
+                if (first + u * kDequantGroups < ks_end) fetch(first + u * kDequantGroups, q_ring[u], sc_ring[u], bias_ring[u]);
             }
+            for (int ks0 = first; ks0 < ks_end && ok; ks0 += kPrefetch * kDequantGroups) {
+#pragma unroll
+                for (int u = 0; u < kPrefetch; ++u) {
+                    const int ks = ks0 + u * kDequantGroups;
+                    if (ks >= ks_end || !ok) break;
+                    const uint32_t mine = it + uint32_t(ks - ks_begin);  // this stage's use number
+                    const int s = mine % kStages;
+                    const uint4 q = q_ring[u];
+                    const uint32_t sc = sc_ring[u], bias = bias_ring[u];
+                    if (ks + kPrefetch * kDequantGroups < ks_end)
+                        fetch(ks + kPrefetch * kDequantGroups, q_ring[u], sc_ring[u], bias_ring[u]);
+                    if (mine >= uint32_t(kStages))
+                        ok = mbar_wait(&pipe->empty[s], ((mine / kStages) - 1) & 1, &g_gemm_error, 5);
+                    if (!ok) break;
+                    uint8_t* tile_b = smem + s * kStageBytes + 2 * kATile + row * 128;
+                    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        // (k0,k4) (k1,k5) (k2,k6) (k3,k7): magic + q, then exactly (q - zero) * scale
+                        uint32_t f[4];
+                        f[0] = lop3_and_or(w[i], 0x000F000Fu, 0x43004300u);
+                        f[1] = lop3_and_or(w[i] >> 4, 0x000F000Fu, 0x43004300u);
+                        f[2] = lop3_and_or(w[i] >> 8, 0x000F000Fu, 0x43004300u);
+                        f[3] = lop3_and_or(w[i] >> 12, 0x000F000Fu, 0x43004300u);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) f[e] = sub_mul<__nv_bfloat16>(f[e], bias, sc);
+                        uint4 out;  // natural order (k0,k1) (k2,k3) (k4,k5) (k6,k7)
+                        out.x = __byte_perm(f[0], f[1], 0x5410);
+                        out.y = __byte_perm(f[2], f[3], 0x5410);
+                        out.z = __byte_perm(f[0], f[1], 0x7632);
+                        out.w = __byte_perm(f[2], f[3], 0x7632);
+                        const int chunk = half * 4 + i;  // 16-byte chunk of the 128-byte row
+                        *reinterpret_cast<uint4*>(tile_b + ((chunk ^ (row & 7)) * 16)) = out;
+                    }
+                    fence_proxy_async();  // generic-proxy stores -> visible to the tensor core
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&pipe->full_b[s]);
+                }
+            }
+            it += uint32_t(ks_end - ks_begin);
         }
     } else {
         // ---- epilogue (warps 0-3; warp w owns tensor-memory lanes 32w .. 32w+31) ---

@@ -375,11 +375,16 @@ bool run_rows(const GemvArgs& a, cudaStream_t stream, int32_t* status) {
     // Widest block (most sharing of the staged activations) among those that keep every
     // block resident at once and still put a block on every multiprocessor.
     const int candidates[4] = {14, 7, 4, 2};
+    // warps a multiprocessor holds at this kernel's register count (72 / ~136 / ~168 a thread;
+    // the 14-warp block of the 64-row kernel is held to 128)
+    const int warps_by_regs = MB <= 2 ? 28 : MB <= 4 ? 14 : 12;
     int best = 4;
     double best_cost = 1e30;
     for (int w : candidates) {
         const size_t smem = size_t(MB * 8) * 2048 + size_t(w) * 16 * (MB * 8) * 4 + 1024;
-        const int by_smem = int((size_t(220) << 10) / smem), by_regs = 28 / w;
+        const int by_smem = int((size_t(220) << 10) / smem);
+        const int by_regs = w == 14 && warps_by_regs < 14 ? 1 : warps_by_regs / w;
+        if (by_smem < 1 || by_regs < 1) continue;
         const int resident = sms * (by_smem < by_regs ? by_smem : by_regs);
         const int blocks = ((r.tiles + w - 1) / w) * r.ksplit;
         const double waves = double((blocks + resident - 1) / resident);
@@ -428,11 +433,28 @@ int32_t run_gemv(GemvArgs a, int64_t rows, cudaStream_t stream) {
     const size_t elt = 2;
     const uint8_t* x = static_cast<const uint8_t*>(a.x);
     uint8_t* y = static_cast<uint8_t*>(a.y);
-    for (int64_t m0 = 0; m0 < rows; m0 += 16) {
-        a.M = int(rows - m0 < 16 ? rows - m0 : 16);
+    int64_t step = 16;
+    for (int64_t m0 = 0; m0 < rows; m0 += step) {
+        // Up to 64 rows a pass when the kernel with shared activations takes the shape
+        // (the weight streams from HBM once per pass), else passes of 16.
+        const int64_t left = rows - m0;
+        step = left > 32 ? 64 : left > 16 ? 32 : 16;
+        a.M = int(left < step ? left : step);
         a.x = x + size_t(m0) * a.K * elt;
         a.y = y + size_t(m0) * a.N * elt;
         int32_t status = B200Q_OK;
+        if (a.M > 32 && run_rows<T, 8>(a, stream, &status)) {
+            if (status != B200Q_OK) return status;
+            continue;
+        }
+        if (a.M > 16) {
+            if (a.M <= 32 && run_rows<T, 4>(a, stream, &status)) {
+                if (status != B200Q_OK) return status;
+                continue;
+            }
+            step = 16;
+            a.M = 16;
+        }
         if (a.M >= 9 && run_rows<T, 2>(a, stream, &status)) {
             // 9..16 rows: activations staged once per block (15.7 us against 21.7 us at 16
             // rows, K=4096, N=14336; up to 8 rows the per-lane loads are as fast or faster)

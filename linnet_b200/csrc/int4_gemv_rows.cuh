@@ -1,4 +1,4 @@
-// int4-g128 decode kernel for 3..16 activation rows: the warps of a block take
+// int4-g128 decode kernel for 3..64 activation rows (MB blocks of 8): the warps of a block take
 // different 16-row tiles of W and the SAME inputs, so the activations are staged once
 // per block in shared memory.
 //
@@ -32,7 +32,7 @@ struct RowsArgs {
 };
 
 template <typename T, int MB, int W, int D>
-__global__ void __launch_bounds__(W * 32, 28 / W)
+__global__ void __launch_bounds__(W * 32, MB <= 2 ? 28 / W : 1)  // more rows: more accumulators a thread
 int4_gemv_rows_kernel(const RowsArgs a) {
     using H = Half16<T>;
     constexpr int MP = MB * 8;  // activation rows as staged (zero padded)

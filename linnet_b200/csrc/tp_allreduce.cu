@@ -51,13 +51,27 @@ __device__ __forceinline__ uint4 load_peer(const uint4* p) {  // never from a st
     return v;
 }
 
-__global__ void __launch_bounds__(256)
+// CPT: 16-byte pieces of a row each thread keeps in registers between the reduction and
+// the scaling (0: any width, x re-read).
+template <int CPT>
+__global__ void __launch_bounds__(512)
 allreduce_add_rmsnorm_kernel(const Peers p, uint32_t* __restrict__ epoch, uint32_t* __restrict__ done,
                              int* __restrict__ error, uint16_t* __restrict__ x,
                              const uint16_t* __restrict__ weight, uint16_t* __restrict__ y, int hidden,
                              float eps) {
-    __shared__ float partial_sums[8];
+    __shared__ float partial_sums[16];
     __shared__ int gave_up;
+    constexpr int kHeld = CPT > 0 ? CPT : 1;
+    const int row = blockIdx.x, chunks = hidden / 8;
+    const uint4* wr = reinterpret_cast<const uint4*>(weight);
+    uint4 g[kHeld], v[kHeld];
+    if (CPT > 0) {  // the norm weights do not depend on the kernel before this one
+#pragma unroll
+        for (int u = 0; u < kHeld; ++u) {
+            const int c = threadIdx.x + u * blockDim.x;
+            g[u] = c < chunks ? __ldg(wr + c) : make_uint4(0, 0, 0, 0);
+        }
+    }
     pdl_wait();  // this rank's partial sums come from the kernel before this one
     pdl_launch_dependents();
     const uint32_t e = *reinterpret_cast<volatile uint32_t*>(epoch) + 1;
@@ -89,30 +103,38 @@ allreduce_add_rmsnorm_kernel(const Peers p, uint32_t* __restrict__ epoch, uint32
     }
     __syncthreads();
 
-    const int row = blockIdx.x, chunks = hidden / 8;
     uint4* xr = reinterpret_cast<uint4*>(x + size_t(row) * hidden);
     float sum_sq = 0.0f;
-    if (!gave_up) {
-        for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
-            float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            for (int r = 0; r < p.world; ++r) {
-                const uint4 v = load_peer(reinterpret_cast<const uint4*>(p.partial[r] + size_t(row) * hidden) + c);
-                s[0] += lo16(v.x); s[1] += hi16(v.x); s[2] += lo16(v.y); s[3] += hi16(v.y);
-                s[4] += lo16(v.z); s[5] += hi16(v.z); s[6] += lo16(v.w); s[7] += hi16(v.w);
-            }
-            uint4 v = xr[c];
-            // the reduced tensor is bf16 (one rounding), then the residual add rounds again
-            const uint32_t d0 = pack16(s[0], s[1]), d1 = pack16(s[2], s[3]), d2 = pack16(s[4], s[5]),
-                           d3 = pack16(s[6], s[7]);
-            v.x = pack16(lo16(v.x) + lo16(d0), hi16(v.x) + hi16(d0));
-            v.y = pack16(lo16(v.y) + lo16(d1), hi16(v.y) + hi16(d1));
-            v.z = pack16(lo16(v.z) + lo16(d2), hi16(v.z) + hi16(d2));
-            v.w = pack16(lo16(v.w) + lo16(d3), hi16(v.w) + hi16(d3));
-            xr[c] = v;
-            const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) sum_sq += lo16(u[i]) * lo16(u[i]) + hi16(u[i]) * hi16(u[i]);
+    auto reduce_add_square = [&](int c) {
+        float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        uint4 t = xr[c];
+        for (int r = 0; r < p.world; ++r) {
+            const uint4 q = load_peer(reinterpret_cast<const uint4*>(p.partial[r] + size_t(row) * hidden) + c);
+            s[0] += lo16(q.x); s[1] += hi16(q.x); s[2] += lo16(q.y); s[3] += hi16(q.y);
+            s[4] += lo16(q.z); s[5] += hi16(q.z); s[6] += lo16(q.w); s[7] += hi16(q.w);
         }
+        // the reduced tensor is bf16 (one rounding), then the residual add rounds again
+        const uint32_t d0 = pack16(s[0], s[1]), d1 = pack16(s[2], s[3]), d2 = pack16(s[4], s[5]),
+                       d3 = pack16(s[6], s[7]);
+        t.x = pack16(lo16(t.x) + lo16(d0), hi16(t.x) + hi16(d0));
+        t.y = pack16(lo16(t.y) + lo16(d1), hi16(t.y) + hi16(d1));
+        t.z = pack16(lo16(t.z) + lo16(d2), hi16(t.z) + hi16(d2));
+        t.w = pack16(lo16(t.w) + lo16(d3), hi16(t.w) + hi16(d3));
+        xr[c] = t;
+        const uint32_t u[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sum_sq += lo16(u[i]) * lo16(u[i]) + hi16(u[i]) * hi16(u[i]);
+        return t;
+    };
+    if (CPT > 0) {
+#pragma unroll
+        for (int u = 0; u < kHeld; ++u) {
+            const int c = threadIdx.x + u * blockDim.x;
+            v[u] = make_uint4(0, 0, 0, 0);
+            if (c < chunks) v[u] = gave_up ? xr[c] : reduce_add_square(c);
+        }
+    } else if (!gave_up) {
+        for (int c = threadIdx.x; c < chunks; c += blockDim.x) reduce_add_square(c);
     }
     for (int d = 16; d >= 1; d >>= 1) sum_sq += __shfl_xor_sync(0xFFFFFFFFu, sum_sq, d);
     if (threadIdx.x % 32 == 0) partial_sums[threadIdx.x / 32] = sum_sq;
@@ -120,16 +142,23 @@ allreduce_add_rmsnorm_kernel(const Peers p, uint32_t* __restrict__ epoch, uint32
     float total = 0.0f;
     for (int i = 0; i < int(blockDim.x) / 32; ++i) total += partial_sums[i];
     const float rstd = rsqrtf(total / float(hidden) + eps);
-    const uint4* wr = reinterpret_cast<const uint4*>(weight);
     uint4* yr = reinterpret_cast<uint4*>(y + size_t(row) * hidden);
-    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
-        const uint4 v = xr[c], g = wr[c];
+    auto scaled = [&](const uint4& t, const uint4& gw) {
         uint4 o;
-        o.x = pack16(lo16(v.x) * rstd * lo16(g.x), hi16(v.x) * rstd * hi16(g.x));
-        o.y = pack16(lo16(v.y) * rstd * lo16(g.y), hi16(v.y) * rstd * hi16(g.y));
-        o.z = pack16(lo16(v.z) * rstd * lo16(g.z), hi16(v.z) * rstd * hi16(g.z));
-        o.w = pack16(lo16(v.w) * rstd * lo16(g.w), hi16(v.w) * rstd * hi16(g.w));
-        yr[c] = o;
+        o.x = pack16(lo16(t.x) * rstd * lo16(gw.x), hi16(t.x) * rstd * hi16(gw.x));
+        o.y = pack16(lo16(t.y) * rstd * lo16(gw.y), hi16(t.y) * rstd * hi16(gw.y));
+        o.z = pack16(lo16(t.z) * rstd * lo16(gw.z), hi16(t.z) * rstd * hi16(gw.z));
+        o.w = pack16(lo16(t.w) * rstd * lo16(gw.w), hi16(t.w) * rstd * hi16(gw.w));
+        return o;
+    };
+    if (CPT > 0) {
+#pragma unroll
+        for (int u = 0; u < kHeld; ++u) {
+            const int c = threadIdx.x + u * blockDim.x;
+            if (c < chunks) yr[c] = scaled(v[u], g[u]);
+        }
+    } else {
+        for (int c = threadIdx.x; c < chunks; c += blockDim.x) yr[c] = scaled(xr[c], wr[c]);
     }
     // The last block to finish advances the site's epoch (every block has read it by then).
     __syncthreads();
@@ -165,8 +194,18 @@ extern "C" int32_t b200q_tp_allreduce_add_rmsnorm(const int64_t* peer_partials, 
         p.flags[r] = reinterpret_cast<uint32_t*>(peer_flags[r]);
         B200Q_REQUIRE(p.partial[r] && p.flags[r] && aligned(p.partial[r], 16), "tp_allreduce_add_rmsnorm: bad peer pointer");
     }
-    return launch_status("tp_allreduce_add_rmsnorm", launch_overlapped(
-        allreduce_add_rmsnorm_kernel, dim3(unsigned(rows)), dim3(256), 0, static_cast<cudaStream_t>(stream), p,
-        static_cast<uint32_t*>(epoch), static_cast<uint32_t*>(done), static_cast<int*>(error),
-        static_cast<uint16_t*>(x), static_cast<const uint16_t*>(weight), static_cast<uint16_t*>(y), int(hidden), eps));
+    const int chunks = int(hidden / 8);
+    int threads = ((chunks + 31) / 32) * 32;
+    threads = threads > 512 ? 512 : threads;
+    const int held = (chunks + threads - 1) / threads;
+    const dim3 grid{unsigned(rows)}, block{unsigned(threads)};
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define B200Q_TP_LAUNCH(CPT)                                                                              \
+    launch_overlapped(allreduce_add_rmsnorm_kernel<CPT>, grid, block, 0, s, p, static_cast<uint32_t*>(epoch), \
+                      static_cast<uint32_t*>(done), static_cast<int*>(error), static_cast<uint16_t*>(x),  \
+                      static_cast<const uint16_t*>(weight), static_cast<uint16_t*>(y), int(hidden), eps)
+    const cudaError_t err = held <= 1 ? B200Q_TP_LAUNCH(1) : held <= 2 ? B200Q_TP_LAUNCH(2)
+                          : held <= 4 ? B200Q_TP_LAUNCH(4) : B200Q_TP_LAUNCH(0);
+#undef B200Q_TP_LAUNCH
+    return launch_status("tp_allreduce_add_rmsnorm", err);
 }

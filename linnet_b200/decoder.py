@@ -158,7 +158,6 @@ class Int4Decoder:
                 else:
                     t.zero_()
                 store.append(t)
-
     # -- collectives ---------------------------------------------------------------
     def _all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         if self.tp > 1:

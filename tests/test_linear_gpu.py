@@ -94,6 +94,27 @@ def test_int4_shapes(rows, depth, out, group):
     close(got, want, f"rows={rows} depth={depth} out={out} group={group}")
 
 
+@pytest.mark.parametrize("rows", [17, 20, 32, 33, 47, 64, 65, 100])
+@pytest.mark.parametrize(("depth", "out", "dtype"), [
+    (1024, 200, torch.bfloat16), (14336, 64, torch.bfloat16), (4096, 1000, torch.bfloat16),
+    (2048, 72, torch.float16),
+])
+def test_int4_decode_kernel_many_rows(rows, depth, out, dtype):
+    """b200q_int4_gemv directly (the dispatcher would send 33 rows and more to the GEMM):
+    17..32 and 33..64 rows per pass share the activations of a block in shared memory."""
+    from linnet_b200 import _lib
+
+    packed, scale, zero, gen = random_int4(out, depth, 128, dtype, rows * 7 + depth)
+    x = torch.randn(rows, depth, generator=gen).to(dtype)
+    want = lo.int4_groups_linear(x, packed, scale, zero)
+    xd, pd, sd, zd = x.cuda(), packed.cuda(), scale.cuda(), zero.cuda()
+    y = torch.empty(rows, out, dtype=dtype, device="cuda")
+    _lib.check(_lib.load().b200q_int4_gemv(xd.data_ptr(), pd.data_ptr(), sd.data_ptr(), zd.data_ptr(), y.data_ptr(),
+                                           rows, depth, out, 128, _lib.BF16 if dtype == torch.bfloat16 else _lib.F16,
+                                           torch.cuda.current_stream().cuda_stream))
+    close(y, want, f"rows={rows} depth={depth} out={out}")
+
+
 @pytest.mark.parametrize("rows", [1, 5, 16])
 def test_int4_f16(rows):
     from linnet_b200 import kernels

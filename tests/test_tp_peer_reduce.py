@@ -3,6 +3,8 @@ single-GPU kernel it replaces, on two GPUs of one box (skipped with fewer)."""
 
 from __future__ import annotations
 
+import faulthandler
+import gc
 import os
 import socket
 
@@ -24,15 +26,30 @@ def _free_port() -> int:
 
 
 def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
-    from linnet_b200 import glue, kernels
-    from linnet_b200.tp import PeerReduce
-
+    faulthandler.dump_traceback_later(240, exit=True)  # a stuck rank ends itself, with a traceback
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dev = torch.device("cuda", rank)
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-    report: dict = {}
     try:
+        report = _checks(rank, world, dev)
+        gc.collect()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.save(report, os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        # every graph, model and symmetric-memory handle is gone by now (locals of _checks):
+        # a captured NCCL collective that is still alive would keep this call waiting
+        dist.destroy_process_group()
+        faulthandler.cancel_dump_traceback_later()
+
+
+def _checks(rank: int, world: int, dev: torch.device) -> dict:
+    from linnet_b200 import glue, kernels
+    from linnet_b200.tp import PeerReduce
+
+    report: dict = {}
+    if True:
         # 1. the kernel alone, three call sites visited round-robin, several epochs
         hidden, rows, sites = 1024, 5, 3
         reduce = PeerReduce(sites, 8, hidden, dev)
@@ -85,10 +102,8 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
             torch.cuda.synchronize()
         report["replay_equal"] = bool(torch.equal(out, eager))
         report["decoder_error"] = model.peer_reduce.error()
-        dist.barrier()
-        torch.save(report, os.path.join(out_dir, f"rank{rank}.pt"))
-    finally:
-        dist.destroy_process_group()
+        del graph, out
+    return report
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
