@@ -1,7 +1,7 @@
 """Benchmark of the quantized-linear hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload gemv|decode] [--rows M]
+                    [--workload gemv|decode|kernels] [--rows M] [--batch B]
 
 Prints ONE JSON line.  Workloads:
 
@@ -14,6 +14,8 @@ Prints ONE JSON line.  Workloads:
   The line also carries `decode`: tokens/s of a Llama-3.1-8B-shaped int4 decoder step,
   tensor-parallel over the N ranks (linnet_b200/decoder.py), at batch 1, 8 and 64.
 * `--workload decode` -- only the decoder, tokens/s as `value`.
+* `--workload kernels [--case attention|glue|linear] [--rows M] [--batch B]` -- every kernel
+  of a decode step timed alone (linnet_b200/kernel_times.py); not a bench line, a table.
 
 `--impl reference` times the reference's own CPU route for the same workload (its
 torch path: weight dequantized once, then bf16 `F.linear`) on the host cores.
@@ -360,9 +362,11 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--workload", default=None, choices=["gemv", "decode"])
-    parser.add_argument("--rows", type=int, default=1)
-    parser.add_argument("--batch", type=int, default=1)
+    parser.add_argument("--workload", default=None, choices=["gemv", "decode", "kernels"])
+    parser.add_argument("--case", default="all", choices=["all", "attention", "glue", "linear"],
+                        help="kernels: which kernel family to time")
+    parser.add_argument("--rows", type=int, default=None)
+    parser.add_argument("--batch", type=int, default=None)
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-other-configs", action="store_true")
     parser.add_argument("--no-decode", action="store_true")
@@ -372,6 +376,9 @@ def main() -> None:
                         help="tensor-parallel decode: one peer-memory kernel per reduction, or NCCL")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
+    one_size = (args.rows, args.batch)  # kernels: None sweeps the sizes
+    args.rows = args.rows if args.rows is not None else 1
+    args.batch = args.batch if args.batch is not None else 1
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -409,7 +416,14 @@ def main() -> None:
 
     from linnet_b200 import decoder
 
-    if args.workload == "decode":
+    if args.workload == "kernels":
+        from linnet_b200 import kernel_times
+
+        if world > 1:
+            raise SystemExit("--workload kernels runs on one GPU")
+        line = {"workload": "kernels", "case": args.case, "unit": "us per launch, CUDA graph over rotating inputs",
+                "results": kernel_times.run(device, args.case, *one_size)}
+    elif args.workload == "decode":
         line = decoder.bench(args, rank, world, device, barrier, reduce_max, Clocks)
     else:
         # The headline line is the same at every N: the GEMV of BASELINE's configs[1], each

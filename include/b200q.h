@@ -152,6 +152,19 @@ int32_t b200q_decode_attention(const void* q, const void* cache_k, const void* c
                                int64_t max_seq, int64_t splits, void* stream);
 
 
+/* Rotary embedding + cache write + attention in one launch (b200q_rope_cache followed by
+ * b200q_decode_attention_cluster): `qkv` is the fused projection [batch, (nq + 2 nkv) *
+ * head_dim] of this step; `rope` is a table [max_seq, head_dim / 2] of (cos, sin) f32 pairs
+ * filled once by b200q_rope_table (the same arithmetic as b200q_rope_cache).  The queries are
+ * rotated in registers; the block whose keys end at positions[b] rotates the new key, puts it
+ * and the new value into its tile and writes both to the caches.  1 to 8 splits.  No
+ * reference counterpart (the reference runs PyTorch ops here). */
+int32_t b200q_rope_table(void* table, int64_t max_seq, int64_t head_dim, float theta, void* stream);
+int32_t b200q_rope_attention(const void* qkv, const int64_t* positions, const void* rope,
+                             void* cache_k, void* cache_v, void* out, int64_t batch, int64_t nq,
+                             int64_t nkv, int64_t head_dim, int64_t max_seq, int64_t splits,
+                             void* stream);
+
 /* b200q_decode_attention in one launch and without scratch: the `splits` (1 to 8) blocks
  * of a (row, kv head) form one thread-block cluster and merge their partial results through
  * distributed shared memory.  Allocates nothing.  No reference counterpart: the reference

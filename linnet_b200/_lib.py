@@ -42,6 +42,9 @@ PROTOTYPES: dict[str, list] = {
                                c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p],
     "b200q_decode_attention_cluster": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                        c_int64, c_int64, c_int64, c_int64, c_void_p],
+    "b200q_rope_table": [c_void_p, c_int64, c_int64, c_float, c_void_p],
+    "b200q_rope_attention": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                             c_int64, c_int64, c_int64, c_int64, c_void_p],
     "b200q_decode_attention_static_scratch_limit": [],
     "b200q_decode_attention_static": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                       c_int64, c_int64, c_int64, c_int64, c_void_p],

@@ -70,6 +70,56 @@ cudaError_t launch_overlapped(void (*kernel)(Params...), dim3 grid, dim3 block, 
 
 // ---- device helpers -------------------------------------------------------
 
+// Data written by earlier kernels of the stream (activations, positions, partial results)
+// and programmatic dependent launch.  A kernel launched that way starts while the kernels
+// before it are still running, and inside a CUDA graph the read-only data cache is not
+// invalidated between such kernels: a decode step that reuses an address for a new tensor
+// (the allocator does all the time) was served the old tensor's lines through __ldg.  So
+// such data is never read through the non-coherent path here (no __ldg, no ld.global.nc, no
+// const __restrict__ pointer, which lets the compiler pick it), and only after pdl_wait():
+//   * ld_mutable(): ld.global.cg, which neither allocates in L1 nor hits in it; used wherever
+//     a value is read once (the small kernels, staging into shared memory);
+//   * ordinary coherent loads (ld.global.ca) where L1 reuse pays (the decode product's
+//     activation fragments), which griddepcontrol.wait orders after the producer's stores.
+// Weights, scales, zero points, norm weights and tables never change: any path will do.
+__device__ __forceinline__ uint4 ld_mutable(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ld_mutable(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint16_t ld_mutable(const uint16_t* p) {
+    uint16_t v;
+    asm volatile("ld.global.cg.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float ld_mutable(const float* p) {
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ int64_t ld_mutable(const int64_t* p) {
+    int64_t v;
+    asm volatile("ld.global.cg.s64 %0, [%1];" : "=l"(v) : "l"(p));
+    return v;
+}
+// An ordinary coherent load (through L1) as an instruction the compiler may move like
+// arithmetic; it stays below pdl_wait() because its address is derived from a pointer that
+// went through below_pdl_wait() after the wait.
+__device__ __forceinline__ uint4 ld_activation_free(const uint4* p) {
+    uint4 v;
+    asm("ld.global.ca.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+template <typename P>
+__device__ __forceinline__ P* below_pdl_wait(P* p) {
+    asm volatile("" : "+l"(p));  // volatile: stays after the wait; opaque: nothing derived from p moves above it
+    return p;
+}
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     // 128-bit read-only load that does not allocate in L1: weight bytes are
     // used exactly once.

@@ -54,10 +54,11 @@ __device__ __forceinline__ void mma_top(float (&d)[4], uint32_t a0, uint32_t a2,
 
 template <int HD, int REP>
 __global__ void __launch_bounds__(32 * kAttnWarps)
-attention_partial_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ cache_k,
-                         const uint16_t* __restrict__ cache_v, const int64_t* __restrict__ positions,
-                         float* __restrict__ partial, uint16_t* __restrict__ out_final, int nq, int nkv,
-                         int S, int splits, int stages, float scale_log2) {
+attention_partial_kernel(const uint16_t* q, uint16_t* cache_k,  // q and positions: ld_mutable()
+                         uint16_t* cache_v, const int64_t* positions,
+                         const float2* __restrict__ rope, float* __restrict__ partial,
+                         uint16_t* __restrict__ out_final, int nq, int nkv, int S, int splits, int stages,
+                         float scale_log2) {
     static_assert(REP <= 8 && (HD == 64 || HD == 128), "heads of a group sit in rows 0..7 of the MMA");
     constexpr int kRowBytes = HD * 2;
     constexpr int kPieces = kRowBytes / 16;          // 16-byte pieces per row
@@ -70,7 +71,13 @@ attention_partial_kernel(const uint16_t* __restrict__ q, const uint16_t* __restr
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
     const int g = lane / 4, t = lane % 4;
-    const int keys = int(positions[b]) + 1;  // attend to positions 0 .. pos
+    // rope != nullptr: q is the fused projection [B, (nq + 2 nkv) * HD] straight from the
+    // linear layer; this kernel rotates the query and key heads itself (cos / sin of every
+    // position in `rope`), and the block whose keys end at the current position puts the new
+    // key and value into its tile and into the cache.
+    const bool fused = rope != nullptr;
+    const int q_heads = fused ? nq + 2 * nkv : nq;  // heads per row of q
+    const int keys = int(ld_mutable(positions + b)) + 1;  // attend to positions 0 .. pos
     const int per_split = (keys + splits - 1) / splits;
     const int k0 = split * per_split, k1 = min(k0 + per_split, keys);
     const int chunks = k1 > k0 ? (k1 - k0 + kAttnChunk - 1) / kAttnChunk : 0;
@@ -97,13 +104,30 @@ attention_partial_kernel(const uint16_t* __restrict__ q, const uint16_t* __restr
     // Q as the A operand: row g = head g of the group (zero rows past REP), two registers per 16 dims.
     uint32_t qa[HD / 16][2];
     {
-        const uint16_t* qp = q + (size_t(b) * nq + kvh * REP + (g < REP ? g : 0)) * HD;
+        const uint16_t* qp = q + (size_t(b) * q_heads + kvh * REP + (g < REP ? g : 0)) * HD;
 #pragma unroll
         for (int s = 0; s < HD / 16; ++s) {
-            const uint32_t lo = *reinterpret_cast<const uint32_t*>(qp + 16 * s + 2 * t);
-            const uint32_t hi = *reinterpret_cast<const uint32_t*>(qp + 16 * s + 8 + 2 * t);
-            qa[s][0] = g < REP ? lo : 0u;
-            qa[s][1] = g < REP ? hi : 0u;
+            qa[s][0] = ld_mutable(reinterpret_cast<const uint32_t*>(qp + 16 * s + 2 * t));
+            qa[s][1] = ld_mutable(reinterpret_cast<const uint32_t*>(qp + 16 * s + 8 + 2 * t));
+        }
+        if (fused) {  // dims d and d + HD/2 rotate together: registers s and s + HD/32 of this lane
+            const float2* cs = rope + size_t(keys - 1) * (HD / 2);
+#pragma unroll
+            for (int s = 0; s < HD / 32; ++s)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int d = 16 * s + 8 * h + 2 * t;
+                    const float2 c0 = __ldg(cs + d), c1 = __ldg(cs + d + 1);
+                    const uint32_t lo = qa[s][h], hi = qa[s + HD / 32][h];
+                    const float a0 = bf16_lo(lo), a1 = bf16_hi(lo), b0 = bf16_lo(hi), b1 = bf16_hi(hi);
+                    qa[s][h] = bf16_pack(a0 * c0.x - b0 * c0.y, a1 * c1.x - b1 * c1.y);
+                    qa[s + HD / 32][h] = bf16_pack(b0 * c0.x + a0 * c0.y, b1 * c1.x + a1 * c1.y);
+                }
+        }
+#pragma unroll
+        for (int s = 0; s < HD / 16; ++s) {
+            qa[s][0] = g < REP ? qa[s][0] : 0u;
+            qa[s][1] = g < REP ? qa[s][1] : 0u;
         }
     }
     float m = -INFINITY, l = 0.0f;  // running max (log2 units) and this lane's share of the sum, head g
@@ -119,6 +143,33 @@ attention_partial_kernel(const uint16_t* __restrict__ q, const uint16_t* __restr
         __syncthreads();  // chunk c has landed for everyone; everyone is done with chunk c - 1
         issue(c + stages - 1);  // into the stage chunk c - 1 used
         const int first = k0 + c * kAttnChunk;
+        if (fused && k1 == keys && c == chunks - 1) {
+            // The current position is the last row of this chunk: its key (rotated) and value
+            // come from the projection, not from the cache, and are stored for later steps.
+            const int row = keys - 1 - first, half = HD / 2;
+            uint8_t* tile = attn_smem + (c % stages) * 2 * kStage;
+            for (int i = threadIdx.x; i < half; i += kThreads) {
+                const uint16_t* kp = q + (size_t(b) * q_heads + nq + kvh) * HD;
+                const uint16_t* vp = kp + size_t(nkv) * HD;
+                const float2 cs = __ldg(rope + size_t(keys - 1) * half + i);
+                const float a = bf16_lo(ld_mutable(kp + i)), bb = bf16_lo(ld_mutable(kp + i + half));
+                const uint16_t v_lo = ld_mutable(vp + i), v_hi = ld_mutable(vp + i + half);
+                const uint16_t lo = uint16_t(bf16_pack(a * cs.x - bb * cs.y, 0.0f) & 0xFFFF);
+                const uint16_t hi = uint16_t(bf16_pack(bb * cs.x + a * cs.y, 0.0f) & 0xFFFF);
+                const int at_lo = row * kRowBytes + (((i / 8) ^ (row & 7)) * 16) + (i % 8) * 2;
+                const int at_hi = row * kRowBytes + ((((i + half) / 8) ^ (row & 7)) * 16) + (i % 8) * 2;
+                *reinterpret_cast<uint16_t*>(tile + at_lo) = lo;
+                *reinterpret_cast<uint16_t*>(tile + at_hi) = hi;
+                *reinterpret_cast<uint16_t*>(tile + kStage + at_lo) = v_lo;
+                *reinterpret_cast<uint16_t*>(tile + kStage + at_hi) = v_hi;
+                const size_t dst = base + size_t(keys - 1) * HD;
+                cache_k[dst + i] = lo;
+                cache_k[dst + i + half] = hi;
+                cache_v[dst + i] = v_lo;
+                cache_v[dst + i + half] = v_hi;
+            }
+            __syncthreads();
+        }
         if (first + r0 >= k1) continue;  // warp-uniform: none of this warp's 16 positions exist
         const uint32_t ks = smem0 + (c % stages) * 2 * kStage, vs = ks + kStage;
 
@@ -252,7 +303,7 @@ attention_partial_kernel(const uint16_t* __restrict__ q, const uint16_t* __restr
 }
 
 template <int HD>
-__global__ void attention_merge_kernel(const float* __restrict__ partial, uint16_t* __restrict__ out,
+__global__ void attention_merge_kernel(const float* partial, uint16_t* __restrict__ out,
                                        int splits) {
     pdl_wait();
     pdl_launch_dependents();
@@ -260,15 +311,15 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial, uint16
     const float* p = partial + head * splits * (HD + 2);
     float m_all = -INFINITY;
 #pragma unroll 8
-    for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, p[s * (HD + 2) + HD]);
+    for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, ld_mutable(p + s * (HD + 2) + HD));
     for (int dcol = threadIdx.x; dcol < HD; dcol += blockDim.x) {
         float l_all = 0.0f, a_all = 0.0f;
 #pragma unroll 8
         for (int s = 0; s < splits; ++s) {
-            const float ms = p[s * (HD + 2) + HD];
+            const float ms = ld_mutable(p + s * (HD + 2) + HD);
             const float c = ms == -INFINITY ? 0.0f : __expf(ms - m_all);
-            l_all += p[s * (HD + 2) + HD + 1] * c;
-            a_all += p[s * (HD + 2) + dcol] * c;
+            l_all += ld_mutable(p + s * (HD + 2) + HD + 1) * c;
+            a_all += ld_mutable(p + s * (HD + 2) + dcol) * c;
         }
         out[head * HD + dcol] = uint16_t(bf16_pack(a_all / l_all, 0.0f) & 0xFFFF);
     }
@@ -290,7 +341,7 @@ namespace {
 int32_t launch_attention(const char* who, const void* q, const void* cache_k, const void* cache_v,
                          const int64_t* positions, void* out, void* scratch, int64_t batch, int64_t nq,
                          int64_t nkv, int64_t head_dim, int64_t max_seq, int64_t splits, void* stream,
-                         bool in_cluster = false) {
+                         bool in_cluster = false, const void* rope = nullptr) {
     B200Q_REQUIRE(batch >= 0 && nq > 0 && nkv > 0 && nq % nkv == 0 && splits >= 1 && splits <= 65535,
                   "%s: bad shape", who);
     if (batch == 0) return B200Q_OK;
@@ -322,9 +373,10 @@ int32_t launch_attention(const char* who, const void* q, const void* cache_k, co
     config.attrs = attr;                                                                              \
     config.numAttrs = in_cluster ? 2 : 1;                                                             \
     err = cudaLaunchKernelEx(&config, attention_partial_kernel<HD, REP>,                              \
-                      static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(cache_k),         \
-                      static_cast<const uint16_t*>(cache_v), positions,                               \
-                      in_cluster ? static_cast<float*>(nullptr) : static_cast<float*>(scratch),      \
+                      static_cast<const uint16_t*>(q),                                               \
+                      static_cast<uint16_t*>(const_cast<void*>(cache_k)),                             \
+                      static_cast<uint16_t*>(const_cast<void*>(cache_v)), positions,                  \
+                      static_cast<const float2*>(rope), in_cluster ? static_cast<float*>(nullptr) : static_cast<float*>(scratch),      \
                       static_cast<uint16_t*>(out), int(nq), int(nkv), int(max_seq), int(splits),      \
                       stages, scale_log2); } while (0)
     cudaError_t err = cudaSuccess;
@@ -366,6 +418,44 @@ extern "C" int32_t b200q_decode_attention_cluster(const void* q, const void* cac
     B200Q_REQUIRE(splits >= 1 && splits <= 8, "decode_attention_cluster: 1 to 8 splits, not %lld", (long long)splits);
     return launch_attention("decode_attention_cluster", q, cache_k, cache_v, positions, out, nullptr, batch, nq,
                             nkv, head_dim, max_seq, splits, stream, true);
+}
+
+// Rotary embedding, cache write and attention in one launch: qkv is the fused projection of
+// the step, `rope` the table of b200q_rope_table.
+extern "C" int32_t b200q_rope_attention(const void* qkv, const int64_t* positions, const void* rope,
+                                        void* cache_k, void* cache_v, void* out, int64_t batch, int64_t nq,
+                                        int64_t nkv, int64_t head_dim, int64_t max_seq, int64_t splits,
+                                        void* stream) {
+    B200Q_REQUIRE(splits >= 1 && splits <= 8, "rope_attention: 1 to 8 splits, not %lld", (long long)splits);
+    B200Q_REQUIRE(rope != nullptr && aligned(rope, 8), "rope_attention: no table of cosines and sines");
+    return launch_attention("rope_attention", qkv, cache_k, cache_v, positions, out, nullptr, batch, nq, nkv,
+                            head_dim, max_seq, splits, stream, true, rope);
+}
+
+namespace b200q {
+namespace {
+// table[pos][i] = (cos, sin)(pos * theta^(-i / half)), the arithmetic of rope_cache_kernel.
+__global__ void rope_table_kernel(float2* __restrict__ table, int half, int64_t total, float theta) {
+    for (int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += int64_t(gridDim.x) * blockDim.x) {
+        const int64_t pos = e / half;
+        const int i = int(e % half);
+        const float freq = powf(theta, -float(i) / float(half));
+        float s, c;
+        sincosf(float(pos) * freq, &s, &c);
+        table[e] = make_float2(c, s);
+    }
+}
+}  // namespace
+}  // namespace b200q
+
+extern "C" int32_t b200q_rope_table(void* table, int64_t max_seq, int64_t head_dim, float theta, void* stream) {
+    B200Q_REQUIRE(table && aligned(table, 8) && max_seq > 0 && head_dim > 0 && head_dim % 2 == 0,
+                  "rope_table: bad arguments");
+    const int64_t total = max_seq * (head_dim / 2);
+    rope_table_kernel<<<unsigned((total + 255) / 256 > 4096 ? 4096 : (total + 255) / 256), 256, 0,
+                        static_cast<cudaStream_t>(stream)>>>(static_cast<float2*>(table), int(head_dim / 2), total,
+                                                            theta);
+    return launched("rope_table");
 }
 
 // ---- the same attention for callers that cannot allocate device memory ----------------

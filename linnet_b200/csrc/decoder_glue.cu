@@ -22,7 +22,7 @@ namespace {
 // squares and the scaling (CPT 16-byte pieces per thread; CPT = 0 re-reads x, any width).
 template <int CPT>
 __global__ void __launch_bounds__(512)
-add_rmsnorm_kernel(uint16_t* __restrict__ x, const uint16_t* __restrict__ delta,
+add_rmsnorm_kernel(uint16_t* x, const uint16_t* delta,  // read with ld_mutable()
                    const uint16_t* __restrict__ w, uint16_t* __restrict__ y, int hidden, float eps) {
     __shared__ float partial[16];
     constexpr int kHeld = CPT > 0 ? CPT : 1;
@@ -42,9 +42,9 @@ add_rmsnorm_kernel(uint16_t* __restrict__ x, const uint16_t* __restrict__ delta,
     const uint4* dr = delta ? reinterpret_cast<const uint4*>(delta + size_t(row) * hidden) : nullptr;
     float sum = 0.0f;
     auto add_and_square = [&](int c) {
-        uint4 t = xr[c];
+        uint4 t = ld_mutable(xr + c);
         if (dr) {
-            const uint4 d = dr[c];
+            const uint4 d = ld_mutable(dr + c);
             t.x = bf16_pack(bf16_lo(t.x) + bf16_lo(d.x), bf16_hi(t.x) + bf16_hi(d.x));
             t.y = bf16_pack(bf16_lo(t.y) + bf16_lo(d.y), bf16_hi(t.y) + bf16_hi(d.y));
             t.z = bf16_pack(bf16_lo(t.z) + bf16_lo(d.z), bf16_hi(t.z) + bf16_hi(d.z));
@@ -87,13 +87,13 @@ add_rmsnorm_kernel(uint16_t* __restrict__ x, const uint16_t* __restrict__ delta,
             if (c < chunks) yr[c] = scaled(v[u], g[u]);
         }
     } else {
-        for (int c = threadIdx.x; c < chunks; c += blockDim.x) yr[c] = scaled(xr[c], wr[c]);
+        for (int c = threadIdx.x; c < chunks; c += blockDim.x) yr[c] = scaled(ld_mutable(xr + c), wr[c]);
     }
 }
 
 // ---- rotary embedding of q and k, cache write of k and v -----------------------------
 // qkv [B, (nq + 2 nkv) * hd]; q_out [B, nq, hd]; cache_{k,v} [B, nkv, S, hd]; halves rotated.
-__global__ void rope_cache_kernel(const uint16_t* __restrict__ qkv, const int64_t* __restrict__ positions,
+__global__ void rope_cache_kernel(const uint16_t* qkv, const int64_t* positions,
                                   uint16_t* __restrict__ q_out, uint16_t* __restrict__ cache_k,
                                   uint16_t* __restrict__ cache_v, int nq, int nkv, int hd, int S,
                                   float theta) {
@@ -101,14 +101,14 @@ __global__ void rope_cache_kernel(const uint16_t* __restrict__ qkv, const int64_
     pdl_launch_dependents();
     const int b = blockIdx.y, head = blockIdx.x;  // head < nq: q; < nq + nkv: k; else v
     const int half = hd / 2;
-    const int64_t pos = positions[b];
+    const int64_t pos = ld_mutable(positions + b);
     const uint16_t* src = qkv + (size_t(b) * (nq + 2 * nkv) + head) * hd;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         if (head < nq + nkv) {
             const float freq = powf(theta, -float(i) / float(half));
             float s, c;
             sincosf(float(pos) * freq, &s, &c);
-            const float a = bf16_lo(src[i]), bb = bf16_lo(src[i + half]);
+            const float a = bf16_lo(ld_mutable(src + i)), bb = bf16_lo(ld_mutable(src + i + half));
             const uint16_t lo = uint16_t(bf16_pack(a * c - bb * s, 0.0f) & 0xFFFF);
             const uint16_t hi = uint16_t(bf16_pack(bb * c + a * s, 0.0f) & 0xFFFF);
             uint16_t* dst = head < nq ? q_out + (size_t(b) * nq + head) * hd
@@ -117,8 +117,8 @@ __global__ void rope_cache_kernel(const uint16_t* __restrict__ qkv, const int64_
             dst[i + half] = hi;
         } else {
             uint16_t* dst = cache_v + ((size_t(b) * nkv + (head - nq - nkv)) * S + pos) * hd;
-            dst[i] = src[i];
-            dst[i + half] = src[i + half];
+            dst[i] = ld_mutable(src + i);
+            dst[i + half] = ld_mutable(src + i + half);
         }
     }
 }
@@ -126,15 +126,15 @@ __global__ void rope_cache_kernel(const uint16_t* __restrict__ qkv, const int64_
 // ---- silu(gate) * up ---------------------------------------------------------------------
 // gate_up [B, 2 I] -> out [B, I]; silu is rounded to bf16 before the product, as the two
 // PyTorch ops do.
-__global__ void silu_mul_kernel(const uint16_t* __restrict__ gate_up, uint16_t* __restrict__ out,
+__global__ void silu_mul_kernel(const uint16_t* gate_up, uint16_t* __restrict__ out,
                                 int inner, int64_t total) {
     pdl_wait();
     pdl_launch_dependents();
     for (int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
          e += int64_t(gridDim.x) * blockDim.x) {
         const int64_t row = e / inner, col = e % inner;
-        const float g = bf16_lo(gate_up[row * 2 * inner + col]);
-        const float u = bf16_lo(gate_up[row * 2 * inner + inner + col]);
+        const float g = bf16_lo(ld_mutable(gate_up + row * 2 * inner + col));
+        const float u = bf16_lo(ld_mutable(gate_up + row * 2 * inner + inner + col));
         const float s = bf16_round(g / (1.0f + expf(-g)));
         out[e] = uint16_t(bf16_pack(s * u, 0.0f) & 0xFFFF);
     }

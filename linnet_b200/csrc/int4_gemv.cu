@@ -23,6 +23,8 @@
 //   * the warps of a block split K; a cluster of blocks may split it further, the
 //     partial sums meeting in (distributed) shared memory, so no global scratch
 //     and no atomics are used.
+#include <cstdlib>
+
 #include "gemv_common.cuh"
 #include "int4_gemv_oct.cuh"
 #include "int4_gemv_rows.cuh"
@@ -145,7 +147,7 @@ int4_gemv_kernel(const GemvArgs a) {
                 if (e < pieces) {
                     const int m = e / per_row, rem = e - m * per_row;
                     const int j = rem / 16, c = rem % 16;
-                    raw[u] = __ldg(xg + (size_t(m) * K + size_t(kb0 + wb0 + j) * 128) / 8 + c);
+                    raw[u] = ld_mutable(xg + (size_t(m) * K + size_t(kb0 + wb0 + j) * 128) / 8 + c);
                     where[u] = ((j * 4 + (c % 4)) * M + m) * 4 + c / 4;
                     if (MODE == kPost && c == 0) where[u] |= (j * 16 + m) << 16;
                 }
@@ -401,6 +403,29 @@ bool run_rows(const GemvArgs& a, cudaStream_t stream, int32_t* status) {
     return true;
 }
 
+// Set by b200q_int4_gemv: this call reads the activations of the previous call of this thread.
+thread_local bool g_same_activations = false;
+
+// The short-run variants (KB = 4 or 2 k-blocks per warp) for up to 8 rows: the most warps
+// per block (of 8, 4, 7, 2, 1) that divide the runs along K with at most 8 blocks per cluster.
+template <typename T, int KB>
+bool run_short(OctArgs o, int G, cudaStream_t stream, int32_t* status) {
+    const bool deep = o.M <= 2;  // every weight load of the kernel issued up front (cp.async)
+#define B200Q_SHORT(W)                                                                       \
+    if (oct_plan(o.K, G, W, o.scale, o.zero, &o.ksplit, KB)) {                               \
+        *status = deep ? launch_oct<T, 1, 1, W, 0, false, KB>(o, stream)                     \
+                       : launch_oct<T, 1, 1, W, 2, false, KB>(o, stream);                    \
+        return true;                                                                         \
+    }
+    B200Q_SHORT(8)
+    B200Q_SHORT(4)
+    B200Q_SHORT(7)
+    B200Q_SHORT(2)
+    B200Q_SHORT(1)
+#undef B200Q_SHORT
+    return false;
+}
+
 // The specialised g128 kernel when the shape allows it: the most warps per block
 // (of 4, 7, 2, 1) that divide K / 1024 with at most 8 blocks per cluster.
 template <typename T>
@@ -409,12 +434,39 @@ bool run_oct(const GemvArgs& a, cudaStream_t stream, int32_t* status) {
     // prefetch overlaps the tail of the kernel before it.
     OctArgs o{a.x, a.packed, a.scale, a.zero, a.y, a.M, a.K, a.N, 1, 1};
     const bool few = a.M <= 8;
+    static const bool no_short = getenv("B200Q_NO_SHORT") != nullptr;  // measurement hook
+    if (few && a.G == 128 && !no_short) {
+        // A warp's run through 8 k-blocks takes ~2.7 us however little else the GPU has to
+        // do; while all warps of the problem would fill less than half of the resident warp
+        // slots (14 of 28 a multiprocessor), halve the run and double the warps.
+        // Halving stops where it would need a cluster to split K (more than 8 runs a tile):
+        // at K=4096, N=4096 two k-blocks a warp with clusters of 2 took 7.6 us, eight
+        // k-blocks without a cluster 6.2.
+        const int64_t tiles = (a.N + 15) / 16, slots = int64_t(14) * sm_count();
+        int kb = 8;
+        while (kb > 2) {
+            const bool fits = a.K % (128 * kb) == 0;
+            const bool half_fits = a.K % (64 * kb) == 0 && a.K / (64 * kb) <= 8;
+            if (fits && (tiles * (a.K / (128 * kb)) >= slots || !half_fits)) break;
+            kb /= 2;
+        }
+        if (kb == 4 && run_short<T, 4>(o, a.G, stream, status)) return true;
+        if (kb == 2 && a.K % 256 == 0 && run_short<T, 2>(o, a.G, stream, status)) return true;
+    }
     if (oct_plan(a.K, a.G, 4, a.scale, a.zero, &o.ksplit)) {
+        // A product that reads the same activations as the one launched before it on this
+        // host thread is part of a fan-out (q, k and v of one input; gate and up; a chain of
+        // products in a benchmark): let the next kernel start early (see EARLY).
+        const bool early = g_same_activations;
         if (a.M <= 2) {
             // One or two rows: every weight load of the kernel is issued up front (cp.async).
-            *status = launch_oct<T, 1, 1, 4, 0>(o, stream);
+            *status = early ? launch_oct<T, 1, 1, 4, 0, false, 8, true>(o, stream)
+                            : launch_oct<T, 1, 1, 4, 0>(o, stream);
+        } else if (few) {
+            *status = early ? launch_oct<T, 1, 1, 4, 2, false, 8, true>(o, stream)
+                            : launch_oct<T, 1, 1, 4, 2>(o, stream);
         } else {
-            *status = few ? launch_oct<T, 1, 1, 4, 2>(o, stream) : launch_oct<T, 2, 1, 4, 2>(o, stream);
+            *status = launch_oct<T, 2, 1, 4, 2>(o, stream);
         }
     } else if (oct_plan(a.K, a.G, 7, a.scale, a.zero, &o.ksplit)) {
         *status = few ? launch_oct<T, 1, 1, 7, 2>(o, stream) : launch_oct<T, 2, 1, 7, 2>(o, stream);
@@ -577,6 +629,9 @@ extern "C" int32_t b200q_int4_gemv(const void* x, const uint8_t* packed, const v
     if (ok != B200Q_OK || rows == 0) return ok;
     GemvArgs a{x, packed, scale, zero, y, 0, int(in), int(out), int(group), int(in / 128), 0, 1};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    static thread_local const void* last_x = nullptr;
+    g_same_activations = x == last_x;
+    last_x = x;
     return dtype == B200Q_BF16 ? run_gemv<__nv_bfloat16>(a, rows, s) : run_gemv<__half>(a, rows, s);
 }
 

@@ -30,7 +30,7 @@ struct OctArgs {
     const uint8_t* zero;    // [N, K/128]
     void* y;                // [M, N]
     int M, K, N;
-    int ksplit;             // blocks per cluster; K == 1024 * W * ksplit
+    int ksplit;             // blocks per cluster; K == 128 * KB * W * ksplit
     int overlap;            // launched with programmatic stream serialization
 };
 
@@ -73,10 +73,25 @@ __device__ __forceinline__ uint32_t shr(uint32_t w) {
 // (sum_k x_k comes from a product with a fragment of ones) instead of dequantizing
 // every weight; cheaper, and closer to exact arithmetic, but not the reference's
 // rounding of each weight to the 16-bit type.
-template <typename T, int MB, int NT, int W, int D, bool FAST>
-__global__ void __launch_bounds__(W * 32, (NT == 1 ? 28 : 20) / W)  // warps wanted per multiprocessor
+// KB: k-blocks per warp (8 = an oct; 4 or 2 for small problems, where a warp's serial run
+// through 8 k-blocks -- 1,500 instructions, ~2.7 us -- is the whole kernel time and most
+// multiprocessors hold only a few warps: shorter runs, proportionally more warps).
+// The activations are read with ordinary coherent loads (ld.global.ca).  The read-only path
+// (__ldg) is about 1 us faster on the headline shape but is not safe here: launched
+// programmatically inside a CUDA graph, kernels do not get that cache invalidated between
+// them, and a decode step that reuses an address for a new activation tensor was served the
+// old tensor's lines (found by replaying a captured step against its eager result).
+// EARLY: when the kernels that depend on this one may start (programmatic dependent launch).
+//   false: after the last k-block.  Inside a decode step this is the faster order: a
+//     dependent that starts early (the attention kernel with its 96-192 KB of shared memory,
+//     say) only takes shared memory and warp slots from this kernel while it waits.
+//   true: at once, so that a following product overlaps its weight prefetch with this
+//     kernel's arithmetic (1.4 us per launch in a chain of products on the headline shape).
+template <typename T, int MB, int NT, int W, int D, bool FAST, int KB = 8, bool EARLY = false>
+__global__ void __launch_bounds__(W * 32, ((NT == 1 ? 28 : 20) / W) > 0 ? (NT == 1 ? 28 : 20) / W : 1)
 int4_gemv_oct_kernel(const OctArgs a) {
     static_assert(D > 0 || NT == 1, "the deep variant handles one tile per warp");
+    static_assert(KB == 8 || KB == 4 || KB == 2, "k-blocks per warp");
     using H = Half16<T>;
     extern __shared__ __align__(16) uint8_t smem[];
     const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
@@ -84,13 +99,13 @@ int4_gemv_oct_kernel(const OctArgs a) {
     const int M = a.M, K = a.K, N = a.N;
     const int groups = K / 128;
     const int tile_row = blockIdx.x * (16 * NT);
-    const int oct = blockIdx.y * W + warp;  // this warp's oct along K
+    const int kb0 = (blockIdx.y * W + warp) * KB;  // this warp's first k-block along K
 
     // Shared memory: the block's reduction buffer, then (deep variant) each lane's
-    // private slots [7 k-blocks][2 rows] x 16 B, laid out [slot][lane] per warp.
+    // private slots [KB - 1 k-blocks][2 rows] x 16 B, laid out [slot][lane] per warp.
     float* red = reinterpret_cast<float*>(smem);
     uint4* slots = reinterpret_cast<uint4*>(smem + size_t(W) * NT * 16 * MB * 8 * 4) +
-                   size_t(warp) * (14 * 32) + lane;
+                   size_t(warp) * ((KB - 1) * 2 * 32) + lane;
 
     const uint8_t* rowp[NT][2];
     uint4 s8[NT][2];
@@ -100,7 +115,7 @@ int4_gemv_oct_kernel(const OctArgs a) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int r = min(tile_row + nt * 16 + h * 8 + g, N - 1);  // ragged tile: clamp
-            rowp[nt][h] = a.packed + size_t(r) * (K / 2) + size_t(oct) * 512 + t * 16;
+            rowp[nt][h] = a.packed + size_t(r) * (K / 2) + size_t(kb0) * 64 + t * 16;
         }
 
     // One pipeline step is one k-block of all NT tiles (2 * NT 16-byte loads a lane).
@@ -117,11 +132,11 @@ int4_gemv_oct_kernel(const OctArgs a) {
     if (D > 0) {
 #pragma unroll
         for (int d = 0; d < D; ++d)
-            if (d < 8) load_step(d, d);
+            if (d < KB) load_step(d, d);
     } else {
         load_step(0, 0);
 #pragma unroll
-        for (int j = 1; j < 8; ++j) {
+        for (int j = 1; j < KB; ++j) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const uint32_t dst = uint32_t(__cvta_generic_to_shared(slots + ((j - 1) * 2 + h) * 32));
@@ -135,25 +150,39 @@ int4_gemv_oct_kernel(const OctArgs a) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int r = min(tile_row + nt * 16 + h * 8 + g, N - 1);
-            const size_t at = size_t(r) * groups + size_t(oct) * 8;
-            s8[nt][h] = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(a.scale) + at));
-            z8[nt][h] = __ldg(reinterpret_cast<const uint2*>(a.zero + at));
+            const size_t at = size_t(r) * groups + size_t(kb0);
+            const uint16_t* sp = static_cast<const uint16_t*>(a.scale) + at;
+            s8[nt][h] = make_uint4(0, 0, 0, 0);
+            z8[nt][h] = make_uint2(0, 0);
+            if (KB == 8) {
+                s8[nt][h] = __ldg(reinterpret_cast<const uint4*>(sp));
+                z8[nt][h] = __ldg(reinterpret_cast<const uint2*>(a.zero + at));
+            } else if (KB == 4) {
+                const uint2 s4 = __ldg(reinterpret_cast<const uint2*>(sp));
+                s8[nt][h].x = s4.x;
+                s8[nt][h].y = s4.y;
+                z8[nt][h].x = __ldg(reinterpret_cast<const uint32_t*>(a.zero + at));
+            } else {
+                s8[nt][h].x = __ldg(reinterpret_cast<const uint32_t*>(sp));
+                z8[nt][h].x = uint32_t(__ldg(reinterpret_cast<const uint16_t*>(a.zero + at)));
+            }
         }
     if (a.overlap) {
-        pdl_launch_dependents();
+        if (EARLY) pdl_launch_dependents();
         pdl_wait();  // activations may come from the kernel before this one
     }
 
-    // 2. This lane's activations: row mb*8 + g, inputs oct*1024 + j*128 + t*32 + i*8 ...
+    // 2. This lane's activations: row mb*8 + g, inputs kb0*128 + j*128 + t*32 + i*8 ...
+    // Lanes past the last row read the last row again: their columns of the product are
+    // never stored, and an unconditional load needs no zeroed registers and no predicate.
     const uint4* xp[MB];
 #pragma unroll
     for (int mb = 0; mb < MB; ++mb) {
-        const int m = mb * 8 + g;
-        xp[mb] = m < M ? static_cast<const uint4*>(a.x) + (size_t(m) * K + size_t(oct) * 1024 + t * 32) / 8
-                       : nullptr;
+        const int m = min(mb * 8 + g, M - 1);
+        xp[mb] = below_pdl_wait(static_cast<const uint4*>(a.x)) + (size_t(m) * K + size_t(kb0) * 128 + t * 32) / 8;
     }
 
-    // 3. The 8 * NT steps, fully unrolled.
+    // 3. The KB * NT steps, fully unrolled.
     float acc[NT][MB][2][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
@@ -166,7 +195,7 @@ int4_gemv_oct_kernel(const OctArgs a) {
 
     const uint32_t kMask = 0x000F000Fu;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < KB; ++j) {
         uint4 q[NT][2];
         if (D > 0) {
 #pragma unroll
@@ -174,12 +203,12 @@ int4_gemv_oct_kernel(const OctArgs a) {
                 q[nt][0] = st[j % (D > 0 ? D : 1)][nt][0];
                 q[nt][1] = st[j % (D > 0 ? D : 1)][nt][1];
             }
-            if (j + D < 8) load_step(j % (D > 0 ? D : 1), j + D);
+            if (j + D < KB) load_step(j % (D > 0 ? D : 1), j + D);
         } else if (j == 0) {
             q[0][0] = st[0][0][0];
             q[0][1] = st[0][0][1];
         } else {
-            cp_async_wait(7 - j);
+            cp_async_wait(KB - 1 - j);
             q[0][0] = slots[((j - 1) * 2 + 0) * 32];
             q[0][1] = slots[((j - 1) * 2 + 1) * 32];
         }
@@ -210,11 +239,10 @@ int4_gemv_oct_kernel(const OctArgs a) {
             uint4 b[MB];  // (x0,x4) (x1,x5) (x2,x6) (x3,x7) of this lane's 8 inputs
 #pragma unroll
             for (int mb = 0; mb < MB; ++mb) {
-                uint4 raw = make_uint4(0, 0, 0, 0);
 #ifndef B200Q_KO_X
-                if (xp[mb] != nullptr) raw = __ldg(xp[mb] + j * 16 + i);
+                const uint4 raw = ld_activation_free(xp[mb] + j * 16 + i);
 #else
-                raw = make_uint4(lane, j, i, mb);
+                const uint4 raw = make_uint4(lane, j, i, mb);
 #endif
                 b[mb].x = __byte_perm(raw.x, raw.z, 0x5410);
                 b[mb].y = __byte_perm(raw.x, raw.z, 0x7632);
@@ -296,6 +324,7 @@ int4_gemv_oct_kernel(const OctArgs a) {
         }
     }
 
+    if (a.overlap && !EARLY) pdl_launch_dependents();
     // 4. Sum the two accumulator sets, the warps, the cluster; write y.
     float total[NT][MB][4];
 #pragma unroll
@@ -307,21 +336,22 @@ int4_gemv_oct_kernel(const OctArgs a) {
     reduce_and_store<H, MB, NT, W>(total, red, a.ksplit, tile_row, M, N, static_cast<uint16_t*>(a.y));
 }
 
-// Whether the oct kernel takes this problem with W warps per block; sets ksplit.
-inline bool oct_plan(int K, int G, int W, const void* scale, const uint8_t* zero, int* ksplit) {
-    if (G != 128 || K % 1024 != 0) return false;
-    const int octs = K / 1024;
-    if (octs % W != 0 || octs / W > 8) return false;
+// Whether the oct kernel takes this problem with W warps per block and KB k-blocks per
+// warp; sets ksplit.
+inline bool oct_plan(int K, int G, int W, const void* scale, const uint8_t* zero, int* ksplit, int KB = 8) {
+    if (G != 128 || K % (128 * KB) != 0) return false;
+    const int runs = K / (128 * KB);
+    if (runs % W != 0 || runs / W > 8) return false;
     if (!aligned(scale, 16) || !aligned(zero, 8)) return false;
-    *ksplit = octs / W;
+    *ksplit = runs / W;
     return true;
 }
 
-template <typename T, int MB, int NT, int W, int D, bool FAST = false>
+template <typename T, int MB, int NT, int W, int D, bool FAST = false, int KB = 8, bool EARLY = false>
 int32_t launch_oct(const OctArgs& args, cudaStream_t stream) {
     const int tiles = (args.N + 16 * NT - 1) / (16 * NT);
-    const size_t smem = size_t(W) * NT * 16 * MB * 8 * 4 + (D == 0 ? size_t(W) * 14 * 32 * 16 : 0);
-    auto kernel = int4_gemv_oct_kernel<T, MB, NT, W, D, FAST>;
+    const size_t smem = size_t(W) * NT * 16 * MB * 8 * 4 + (D == 0 ? size_t(W) * (KB - 1) * 2 * 32 * 16 : 0);
+    auto kernel = int4_gemv_oct_kernel<T, MB, NT, W, D, FAST, KB, EARLY>;
     if (D == 0)  // 7 blocks of 30 KB per multiprocessor need the largest carve-out
         cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                              cudaSharedmemCarveoutMaxShared);

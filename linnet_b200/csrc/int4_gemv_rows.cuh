@@ -105,7 +105,7 @@ int4_gemv_rows_kernel(const RowsArgs a) {
                     const int m = e / 128, piece = e % 128;
                     raw[u] = make_uint4(0, 0, 0, 0);
                     if (e < kPieces && m < M)
-                        raw[u] = __ldg(xg + (size_t(m) * K + size_t(oct) * 1024) / 8 + piece);
+                        raw[u] = ld_mutable(xg + (size_t(m) * K + size_t(oct) * 1024) / 8 + piece);
                 }
 #pragma unroll
                 for (int u = 0; u < kBatch; ++u) {

@@ -120,7 +120,7 @@ int8_gemv_kernel(const Gemv8Args a) {
         for (int e = threadIdx.x; e < total; e += W * 32) {
             const int m = e / per_row, rem = e % per_row;
             const int j = rem / 8, c = rem % 8;
-            const uint4 raw = __ldg(xg + (size_t(m) * K + size_t(kb0 + j) * 64) / 8 + c);
+            const uint4 raw = ld_mutable(xg + (size_t(m) * K + size_t(kb0 + j) * 64) / 8 + c);
             xs[(size_t(j * 2 + (c & 1)) * M + m) * 4 + (c >> 1)] = raw;
         }
     }

@@ -107,7 +107,7 @@ allreduce_add_rmsnorm_kernel(const Peers p, uint32_t* __restrict__ epoch, uint32
     float sum_sq = 0.0f;
     auto reduce_add_square = [&](int c) {
         float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        uint4 t = xr[c];
+        uint4 t = ld_mutable(xr + c);
         for (int r = 0; r < p.world; ++r) {
             const uint4 q = load_peer(reinterpret_cast<const uint4*>(p.partial[r] + size_t(row) * hidden) + c);
             s[0] += lo16(q.x); s[1] += hi16(q.x); s[2] += lo16(q.y); s[3] += hi16(q.y);
@@ -131,7 +131,7 @@ allreduce_add_rmsnorm_kernel(const Peers p, uint32_t* __restrict__ epoch, uint32
         for (int u = 0; u < kHeld; ++u) {
             const int c = threadIdx.x + u * blockDim.x;
             v[u] = make_uint4(0, 0, 0, 0);
-            if (c < chunks) v[u] = gave_up ? xr[c] : reduce_add_square(c);
+            if (c < chunks) v[u] = gave_up ? ld_mutable(xr + c) : reduce_add_square(c);
         }
     } else if (!gave_up) {
         for (int c = threadIdx.x; c < chunks; c += blockDim.x) reduce_add_square(c);
@@ -158,7 +158,7 @@ allreduce_add_rmsnorm_kernel(const Peers p, uint32_t* __restrict__ epoch, uint32
             if (c < chunks) yr[c] = scaled(v[u], g[u]);
         }
     } else {
-        for (int c = threadIdx.x; c < chunks; c += blockDim.x) yr[c] = scaled(xr[c], wr[c]);
+        for (int c = threadIdx.x; c < chunks; c += blockDim.x) yr[c] = scaled(ld_mutable(xr + c), wr[c]);
     }
     // The last block to finish advances the site's epoch (every block has read it by then).
     __syncthreads();

@@ -18,7 +18,7 @@ CPU tests pass the oracle, so the sharding and the collectives are exercised on 
 ranks without a GPU.  Between the linears (RMSNorm, rotary embedding, cache write,
 attention, SwiGLU) `step` has two routes with the same arithmetic: plain PyTorch ops (any
 device; what the reference's generated source does, and what the CPU tests run) and, on a
-GPU, the fused kernels of `linnet_b200.glue` (six launches a layer instead of about fifty).
+GPU, the fused kernels of `linnet_b200.glue` (eight launches a layer instead of about fifty).
 Either way a step is recorded into one CUDA graph per batch size, which is how the
 reference's serving engine replays a decode step
 (python/linnet/src/linnet/torch/compiled.py:430-503).
@@ -141,6 +141,7 @@ class Int4Decoder:
         self.cache_k: list[torch.Tensor] = []
         self.cache_v: list[torch.Tensor] = []
         self.peer_reduce = None  # set by enable_peer_reduce()
+        self.rope_table = None   # cos / sin of every position, made by allocate_cache()
 
     # -- state ---------------------------------------------------------------------
     def allocate_cache(self, batch: int, fill: "torch.Generator | None" = None) -> None:
@@ -158,6 +159,11 @@ class Int4Decoder:
                 else:
                     t.zero_()
                 store.append(t)
+        if self.fused and dev.type == "cuda" and self.rope_table is None:
+            from . import glue
+
+            self.rope_table = glue.rope_table(cfg.max_seq, cfg.head_dim, cfg.rope_theta, dev)
+
     # -- collectives ---------------------------------------------------------------
     def _all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         if self.tp > 1:
@@ -207,8 +213,7 @@ class Int4Decoder:
         h = glue.add_rmsnorm(x, None, self.layers[0].norm1, cfg.eps)
         for i, w in enumerate(self.layers):
             qkv = self.linear(h, *w.qkv)
-            q = glue.rope_cache(qkv, positions, self.cache_k[i], self.cache_v[i], nq, nkv, cfg.rope_theta)
-            attn = glue.decode_attention(q, self.cache_k[i], self.cache_v[i], positions)
+            attn = glue.rope_attention(qkv, positions, self.rope_table, self.cache_k[i], self.cache_v[i], nq, nkv)
             h = self._reduce_norm(2 * i, x, attn, w.o, w.norm2)
             act = glue.silu_mul(self.linear(h, *w.gate_up))
             following = self.layers[i + 1].norm1 if i + 1 < len(self.layers) else self.final_norm
@@ -379,9 +384,9 @@ def bench(args, rank: int, world: int, device: torch.device, barrier, reduce_max
     if peer_reduce is not None and peer_reduce.error():
         raise RuntimeError(f"peer reduction gave up waiting for a rank (code {peer_reduce.error()})")
     main = results[args.batch]
-    # per layer: 4 linears, 2 (reduce +) add + norm, rotary + cache write, attention + merge, silu*mul;
+    # per layer: 4 linears, 2 (reduce +) add + norm, rotary + cache write + attention, silu*mul;
     # then the first norm and the output head
-    launches_per_step = cfg.layers * 10 + 2
+    launches_per_step = cfg.layers * 8 + 2
     return {
         "metric": "W4A16 g128 GEMV GB/s (% HBM peak); 8B-shape int4 decode tok/s at 1/2/4/8 GPU",
         "value": main["tok_s"], "unit": "tok/s", "n_gpus": world, "steps": args.steps,

@@ -80,6 +80,33 @@ def decode_attention(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tens
     return out
 
 
+def rope_table(max_seq: int, head_dim: int, theta: float, device: torch.device) -> torch.Tensor:
+    """(cos, sin) of every position and frequency, f32 [max_seq, head_dim / 2, 2], for `rope_attention`."""
+    table = torch.empty(max_seq, head_dim // 2, 2, dtype=torch.float32, device=device)
+    with torch.cuda.device(device):
+        _lib.check(_lib.load().b200q_rope_table(table.data_ptr(), max_seq, head_dim, float(theta),
+                                                torch.cuda.current_stream(device).cuda_stream))
+    return table
+
+
+def rope_attention(qkv: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, cache_k: torch.Tensor,
+                   cache_v: torch.Tensor, nq: int, nkv: int, splits: int | None = None) -> torch.Tensor:
+    """`rope_cache` + `decode_attention` in one launch: rotates q and k of the fused projection
+    qkv [B, (nq + 2 nkv) * D] at positions[b], appends k and v to the caches and attends over
+    positions 0..positions[b]; returns [B, nq * D]."""
+    _bf16(qkv, cache_k, cache_v)
+    batch, _, max_seq, hd = cache_k.shape
+    if splits is None:
+        splits = min(8, attention_splits(batch, nkv, max_seq))
+    if table.shape != (max_seq, hd // 2, 2) or table.dtype != torch.float32:
+        raise ValueError("rope_attention: the table does not match the cache")
+    out = torch.empty(batch, nq * hd, device=qkv.device, dtype=qkv.dtype)
+    _lib.check(_lib.load().b200q_rope_attention(qkv.data_ptr(), positions.data_ptr(), table.data_ptr(),
+                                                cache_k.data_ptr(), cache_v.data_ptr(), out.data_ptr(), batch, nq,
+                                                nkv, hd, max_seq, splits, _stream(qkv)))
+    return out
+
+
 def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     """`silu(gate_up[:, :I]) * gate_up[:, I:]` for gate_up [B, 2 I]."""
     _bf16(gate_up)

@@ -156,6 +156,7 @@ def test_fused_glue_equals_torch_glue():
         pos = torch.randint(0, S, (batch,), generator=gen).to(dev)
         pos[0] = S - 1
         ck2, cv2 = ck.clone(), cv.clone()
+        ck_before, cv_before = ck.clone(), cv.clone()
         q, k, v = qkv.split([nq * hd, nkv * hd, nkv * hd], dim=-1)
         q_ref = dec.rotary(q.reshape(batch, nq, hd), pos, 500000.0)
         rows_i = torch.arange(batch, device=dev)
@@ -171,6 +172,14 @@ def test_fused_glue_equals_torch_glue():
         for splits in (None, 1, 3, 8, 16):  # up to 8: one cluster launch; 16: partials + merge kernel
             got = glue.decode_attention(q_ref, ck2, cv2, pos, splits)
             torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+        # rotary + cache write + attention in one launch, from the caches before the write
+        table = glue.rope_table(S, hd, 500000.0, dev)
+        for splits in (None, 1, 5):
+            ck3, cv3 = ck_before.clone(), cv_before.clone()
+            got = glue.rope_attention(qkv, pos, table, ck3, cv3, nq, nkv, splits)
+            torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+            torch.testing.assert_close(ck3.float(), ck2.float(), rtol=2e-2, atol=2e-2)
+            assert torch.equal(cv3, cv2)
 
 
 @pytest.mark.gpu
@@ -188,21 +197,29 @@ def test_fused_and_torch_steps_agree():
 
 
 @pytest.mark.gpu
-def test_gpu_decoder_graph_replay():
+@pytest.mark.parametrize("shape", ["tiny", "wide"])
+def test_gpu_decoder_graph_replay(shape):
+    """A captured step replays to the eager result, every time: inside a graph the kernels
+    of a step overlap through programmatic dependent launch far more than in eager mode, so
+    this is the test that catches a kernel reading its input too early or through a stale path."""
     from linnet_b200 import kernels, quant
 
-    cfg = dec.DecoderConfig.tiny()
+    cfg = dec.DecoderConfig.tiny() if shape == "tiny" else dec.DecoderConfig(
+        layers=3, hidden=1024, heads=8, kv_heads=2, head_dim=128, mlp=2048, vocab=1024, max_seq=256)
     dev = torch.device("cuda", 0)
     model = dec.build_random(cfg, dev, rank=0, tp=1, seed=1, linear=kernels.int4_linear,
                              quantize=quant.quantize_int4_groups)
-    model.allocate_cache(2, torch.Generator(device=dev).manual_seed(2))
-    tokens = torch.tensor([3, 5], device=dev)
-    positions = torch.full((2,), cfg.max_seq - 1, device=dev, dtype=torch.long)
-    eager = model.step(tokens, positions).clone()
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        out = model.step(tokens, positions)
-    graph.replay()
-    torch.cuda.synchronize()
-    torch.testing.assert_close(out, eager, rtol=0, atol=0)
+    for batch in (2, 5):
+        model.allocate_cache(batch, torch.Generator(device=dev).manual_seed(2))
+        tokens = torch.arange(3, 3 + batch, device=dev)
+        positions = torch.full((batch,), cfg.max_seq - 1, device=dev, dtype=torch.long)
+        eager = model.step(tokens, positions).clone()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = model.step(tokens, positions)
+        for _ in range(20):
+            graph.replay()
+            torch.cuda.synchronize()
+            torch.testing.assert_close(out, eager, rtol=0, atol=0)
+        del graph, out
