@@ -365,6 +365,8 @@ def main() -> None:
     parser.add_argument("--workload", default=None, choices=["gemv", "decode", "kernels"])
     parser.add_argument("--case", default="all", choices=["all", "attention", "glue", "linear"],
                         help="kernels: which kernel family to time")
+    parser.add_argument("--tp", type=int, default=1, choices=[1, 2, 4, 8],
+                        help="kernels: time the shapes of one rank of a tensor-parallel group of this size")
     parser.add_argument("--rows", type=int, default=None)
     parser.add_argument("--batch", type=int, default=None)
     parser.add_argument("--no-cpu-baseline", action="store_true")
@@ -422,7 +424,7 @@ def main() -> None:
         if world > 1:
             raise SystemExit("--workload kernels runs on one GPU")
         line = {"workload": "kernels", "case": args.case, "unit": "us per launch, CUDA graph over rotating inputs",
-                "results": kernel_times.run(device, args.case, *one_size)}
+                "tp_shard": args.tp, "results": kernel_times.run(device, args.case, *one_size, tp=args.tp)}
     elif args.workload == "decode":
         line = decoder.bench(args, rank, world, device, barrier, reduce_max, Clocks)
     else:

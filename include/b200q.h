@@ -205,20 +205,24 @@ int32_t b200q_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t inn
  * the reference's one-shot route: python/linnet/src/linnet/torch/collectives.py:145-167,
  * kernel python/linnet/src/linnet/torch/kernels.py:1107-1156) plus the residual add and norm
  * that follow it in a decoder layer.  bf16 only.
- *   peer_partials[r] / peer_flags[r]: HOST arrays of `world` device addresses -- rank r's
- *     buffer of this call site ([rows, hidden] bf16, 16-byte aligned, written by rank r's own
- *     kernels before this call in stream order) and rank r's `world` uint32 flag words of this
- *     call site, all mapped into this process (symmetric / peer memory), flags zeroed once.
+ *   peer_areas[r] / peer_flags[r]: HOST arrays of `world` device addresses, all mapped into
+ *     this process (symmetric / peer memory): rank r's receive area of this call site,
+ *     [world][slot_elems] bf16 with slot_elems >= max_rows * hidden (16-byte aligned), and
+ *     rank r's flag words of this call site, [world][max_rows] uint32, zeroed once.  Before
+ *     the call, this rank's own kernels (earlier in the stream) have written its partial
+ *     sums [rows, hidden] into slot `rank` of its OWN area; the kernel pushes them into slot
+ *     `rank` of every peer's area, raises the row flags there and sums what it received.
  *   epoch, done: this rank's uint32 counters of this call site (zeroed once); error: an int32
  *     the kernel sets to 100+r when rank r's flag did not arrive within about a second (the
  *     kernel then returns without reducing; the context stays usable).
- * Every rank must make the same sequence of calls per site; a site's buffer may be rewritten
+ * Every rank must make the same sequence of calls per site; a site's slot may be rewritten
  * only after a call on a DIFFERENT site has been issued in between (a decoder has 2 per layer).
- * Plain peer loads and stores only. */
-int32_t b200q_tp_allreduce_add_rmsnorm(const int64_t* peer_partials, const int64_t* peer_flags,
-                                       int32_t world, int32_t rank, void* epoch, void* done,
-                                       void* error, void* x, const void* weight, void* y,
-                                       int64_t rows, int64_t hidden, float eps, void* stream);
+ * Plain peer stores and local loads only. */
+int32_t b200q_tp_allreduce_add_rmsnorm(const int64_t* peer_areas, const int64_t* peer_flags,
+                                       int64_t slot_elems, int64_t max_rows, int32_t world,
+                                       int32_t rank, void* epoch, void* done, void* error, void* x,
+                                       const void* weight, void* y, int64_t rows, int64_t hidden,
+                                       float eps, void* stream);
 
 #ifdef __cplusplus
 }

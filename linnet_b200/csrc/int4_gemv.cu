@@ -507,7 +507,13 @@ int32_t run_gemv(GemvArgs a, int64_t rows, cudaStream_t stream) {
             step = 16;
             a.M = 16;
         }
-        if (a.M >= 9 && run_rows<T, 2>(a, stream, &status)) {
+        static const int rows_min = [] {  // measurement hook: B200Q_ROWS_MIN in the environment
+            const char* v = getenv("B200Q_ROWS_MIN");
+            return v != nullptr ? atoi(v) : 9;
+        }();
+        if (a.M >= rows_min && a.M <= 8 && run_rows<T, 1>(a, stream, &status)) {
+            // (measurement only: the shared-activation kernel below its break-even point)
+        } else if (a.M >= 9 && run_rows<T, 2>(a, stream, &status)) {
             // 9..16 rows: activations staged once per block (15.7 us against 21.7 us at 16
             // rows, K=4096, N=14336; up to 8 rows the per-lane loads are as fast or faster)
         } else if (run_oct<T>(a, stream, &status)) {

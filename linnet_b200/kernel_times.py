@@ -38,8 +38,8 @@ def _timed(fn, sets: int, reps: int = 3) -> float:
     return start.elapsed_time(stop) * 1e3 / (reps * sets)
 
 
-def attention(device: torch.device, batches=(1, 8, 64), max_seq: int = 2048) -> dict:
-    nq, nkv, hd = 32, 8, 128
+def attention(device: torch.device, batches=(1, 8, 64), max_seq: int = 2048, tp: int = 1) -> dict:
+    nq, nkv, hd = 32 // tp, 8 // tp, 128
     out = {}
     for batch in batches:
         nbytes = batch * nkv * max_seq * hd * 4
@@ -73,12 +73,16 @@ def glue_kernels(device: torch.device, batches=(1, 8, 64)) -> dict:
     return out
 
 
-def linear(device: torch.device, rows=(1, 8, 16, 32, 64, 128), shapes=None) -> dict:
+def linear(device: torch.device, rows=(1, 8, 16, 32, 64, 128), shapes=None, tp: int = 1) -> dict:
     gen = torch.Generator(device=device).manual_seed(0)
     out = {}
     for name in shapes or SHAPES:
         depth, width = SHAPES[name]
-        sets = max(2, int(300e6 / (depth * width * 0.53)))
+        if name in ("o", "down"):   # row split: a shard holds K / tp inputs
+            depth //= tp
+        else:                        # column split: a shard holds N / tp outputs
+            width //= tp
+        sets = max(2, min(64, int(300e6 / (depth * width * 0.53))))
         weights = []
         for _ in range(sets):
             packed = torch.randint(0, 256, (width, depth // 128, 64), device=device, dtype=torch.uint8, generator=gen)
@@ -94,13 +98,14 @@ def linear(device: torch.device, rows=(1, 8, 16, 32, 64, 128), shapes=None) -> d
     return out
 
 
-def run(device: torch.device, case: str, rows: int | None, batch: int | None) -> dict:
-    """`case`: attention | glue | linear | all.  `rows` / `batch` narrow the sweep to one size."""
+def run(device: torch.device, case: str, rows: int | None, batch: int | None, tp: int = 1) -> dict:
+    """`case`: attention | glue | linear | all.  `rows` / `batch` narrow the sweep to one size;
+    `tp` times the shapes one rank of a tensor-parallel group of that size holds."""
     results: dict = {}
     if case in ("attention", "all"):
-        results.update(attention(device, (batch,) if batch else (1, 8, 64)))
+        results.update(attention(device, (batch,) if batch else (1, 8, 64), tp=tp))
     if case in ("glue", "all"):
         results.update(glue_kernels(device, (batch,) if batch else (1, 8, 64)))
     if case in ("linear", "all"):
-        results.update(linear(device, (rows,) if rows else (1, 8, 16, 32, 64, 128)))
+        results.update(linear(device, (rows,) if rows else (1, 8, 16, 32, 64, 128), tp=tp))
     return results

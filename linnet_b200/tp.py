@@ -42,9 +42,11 @@ class PeerReduce:
         if not 2 <= self.world <= 8:
             raise ValueError(f"PeerReduce runs on 2..8 ranks, not {self.world}")
         self.sites, self.max_rows, self.hidden, self.device = sites, max_rows, hidden, device
-        self.site_bytes = max_rows * hidden * 2
-        self.flag_bytes = 32  # 8 ranks x uint32 per site
-        total = sites * (self.site_bytes + self.flag_bytes)
+        # per site: a receive area [source rank][max_rows][hidden] bf16, then flags [source rank][max_rows] u32
+        self.slot_elems = max_rows * hidden
+        self.area_bytes = self.world * self.slot_elems * 2
+        self.flag_bytes = self.world * max_rows * 4
+        total = sites * (self.area_bytes + self.flag_bytes)
         self.memory = symm.empty(total, dtype=torch.uint8, device=device)
         self.memory.zero_()
         self.handle = symm.rendezvous(self.memory, group=group)
@@ -54,15 +56,16 @@ class PeerReduce:
         torch.cuda.synchronize(device)
         dist.barrier(group=group)  # nobody signals before every rank's flags are zero
         int64s = ctypes.c_int64 * self.world
-        self._partials = [int64s(*[b + s * self.site_bytes for b in self.bases]) for s in range(sites)]
-        flags0 = sites * self.site_bytes
+        self._areas = [int64s(*[b + s * self.area_bytes for b in self.bases]) for s in range(sites)]
+        flags0 = sites * self.area_bytes
         self._flags = [int64s(*[b + flags0 + s * self.flag_bytes for b in self.bases]) for s in range(sites)]
 
     def partial(self, site: int, rows: int) -> torch.Tensor:
-        """This rank's `[rows, hidden]` bf16 buffer of a call site (a view of the symmetric memory)."""
+        """This rank's own slot of a call site's receive area, `[rows, hidden]` bf16 (a view of
+        the symmetric memory): where the row-split linear writes its partial sums."""
         if not 0 <= site < self.sites or not 0 < rows <= self.max_rows:
             raise ValueError(f"PeerReduce: site {site} / rows {rows} outside {self.sites} sites of {self.max_rows} rows")
-        start = site * self.site_bytes
+        start = site * self.area_bytes + self.rank * self.slot_elems * 2
         return self.memory[start:start + rows * self.hidden * 2].view(torch.bfloat16).view(rows, self.hidden)
 
     def add_rmsnorm(self, site: int, x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
@@ -74,10 +77,10 @@ class PeerReduce:
         y = torch.empty_like(x)
         state = self.state.data_ptr()
         _lib.check(_lib.load().b200q_tp_allreduce_add_rmsnorm(
-            ctypes.addressof(self._partials[site]), ctypes.addressof(self._flags[site]), self.world, self.rank,
-            state + 4 * site, state + 4 * (self.sites + site), state + 8 * self.sites,
-            x.data_ptr(), weight.contiguous().data_ptr(), y.data_ptr(), rows, hidden, float(eps),
-            torch.cuda.current_stream(self.device).cuda_stream))
+            ctypes.addressof(self._areas[site]), ctypes.addressof(self._flags[site]), self.slot_elems,
+            self.max_rows, self.world, self.rank, state + 4 * site, state + 4 * (self.sites + site),
+            state + 8 * self.sites, x.data_ptr(), weight.contiguous().data_ptr(), y.data_ptr(), rows, hidden,
+            float(eps), torch.cuda.current_stream(self.device).cuda_stream))
         return y
 
     def error(self) -> int:
