@@ -6,9 +6,9 @@
 // cached key and value once, so the kernel is bound by HBM: 2 * 2 * S * HD bytes per KV
 // head and row, shared by the REP = heads / kv_heads query heads of the group.
 //
-// Block (split, kv head, batch row), four warps.  The block streams its keys and values
-// through shared memory in chunks of 64 positions with 16-byte cp.async copies, three
-// chunks deep (six when there are fewer blocks than multiprocessors); each warp owns 16 positions of a chunk and runs them through the tensor
+// Block (split, kv head, batch row), four or eight warps.  The block streams its keys and values
+// through shared memory in chunks of 64 (or 128) positions with 16-byte cp.async copies, three
+// chunks deep; each warp owns 16 positions of a chunk and runs them through the tensor
 // cores for all REP heads at once:
 //   scores [heads x 16 positions] = Q [heads(padded to 16) x HD] . K^T   (mma m16n8k16, K
 //       fragments by ldmatrix from the position-major tile),
@@ -28,10 +28,12 @@ namespace b200q {
 namespace cg = cooperative_groups;
 namespace {
 
-constexpr int kAttnChunk = 64;   // positions per shared-memory stage
-constexpr int kAttnStages = 3;      // with more blocks than multiprocessors (two blocks fit on one)
-constexpr int kAttnStagesDeep = 6;  // with fewer: one block a multiprocessor, more of its keys in flight
-constexpr int kAttnWarps = 4;    // 16 positions of a chunk each
+// WARPS warps a block, 16 positions of a chunk each: a chunk (one shared-memory stage) is
+// 16 * WARPS positions.  With more blocks than multiprocessors: 4 warps, chunks of 64, 3
+// stages (two blocks fit on a multiprocessor).  With fewer: 8 warps, chunks of 128, 3
+// stages (one block a multiprocessor, twice the bytes in flight, half the copies to issue
+// per thread and half the block-wide barriers).
+constexpr int kAttnStages = 3;
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -52,8 +54,8 @@ __device__ __forceinline__ void mma_top(float (&d)[4], uint32_t a0, uint32_t a2,
         : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
 }
 
-template <int HD, int REP>
-__global__ void __launch_bounds__(32 * kAttnWarps)
+template <int HD, int REP, int WARPS>
+__global__ void __launch_bounds__(32 * WARPS)
 attention_partial_kernel(const uint16_t* q, uint16_t* cache_k,  // q and positions: ld_mutable()
                          uint16_t* cache_v, const int64_t* positions,
                          const float2* __restrict__ rope, float* __restrict__ partial,
@@ -62,6 +64,7 @@ attention_partial_kernel(const uint16_t* q, uint16_t* cache_k,  // q and positio
     static_assert(REP <= 8 && (HD == 64 || HD == 128), "heads of a group sit in rows 0..7 of the MMA");
     constexpr int kRowBytes = HD * 2;
     constexpr int kPieces = kRowBytes / 16;          // 16-byte pieces per row
+    constexpr int kAttnChunk = 16 * WARPS, kAttnWarps = WARPS;
     constexpr int kStage = kAttnChunk * kRowBytes;   // bytes of K (or V) per chunk
     constexpr int kThreads = 32 * kAttnWarps;
     constexpr float kLn2 = 0.6931471805599453f;
@@ -138,8 +141,7 @@ attention_partial_kernel(const uint16_t* q, uint16_t* cache_k,  // q and positio
     const int r0 = warp * 16;                       // this warp's rows of a chunk
     const int lm_row = lane & 7, lm_mat = lane >> 3;  // ldmatrix: this lane addresses row lm_row of matrix lm_mat
     for (int c = 0; c < chunks; ++c) {
-        if (stages == kAttnStagesDeep) asm volatile("cp.async.wait_group 4;" ::: "memory");
-        else asm volatile("cp.async.wait_group 1;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");  // stages - 2
         __syncthreads();  // chunk c has landed for everyone; everyone is done with chunk c - 1
         issue(c + stages - 1);  // into the stage chunk c - 1 used
         const int first = k0 + c * kAttnChunk;
@@ -354,13 +356,13 @@ int32_t launch_attention(const char* who, const void* q, const void* cache_k, co
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const dim3 grid{unsigned(splits), unsigned(nkv), unsigned(batch)};
     const float scale_log2 = 1.4426950408889634f / sqrtf(float(head_dim));  // softmax in base 2
-#define B200Q_ATTN(HD, REP) do {                                                                      \
-    const int kSmem = stages * 2 * kAttnChunk * HD * 2;                                               \
-    cudaFuncSetAttribute(attention_partial_kernel<HD, REP>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                         kAttnStagesDeep * 2 * kAttnChunk * HD * 2);                                  \
+#define B200Q_ATTN_W(HD, REP, WARPS) do {                                                             \
+    const int kSmem = kAttnStages * 2 * (16 * WARPS) * HD * 2;                                        \
+    cudaFuncSetAttribute(attention_partial_kernel<HD, REP, WARPS>,                                    \
+                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);                         \
     cudaLaunchConfig_t config = {};                                                                   \
     config.gridDim = grid;                                                                            \
-    config.blockDim = dim3(32 * kAttnWarps);                                                          \
+    config.blockDim = dim3(32 * WARPS);                                                               \
     config.dynamicSmemBytes = kSmem;                                                                  \
     config.stream = s;                                                                                \
     cudaLaunchAttribute attr[2];                                                                      \
@@ -372,15 +374,17 @@ int32_t launch_attention(const char* who, const void* q, const void* cache_k, co
     attr[1].val.clusterDim.z = 1;                                                                     \
     config.attrs = attr;                                                                              \
     config.numAttrs = in_cluster ? 2 : 1;                                                             \
-    err = cudaLaunchKernelEx(&config, attention_partial_kernel<HD, REP>,                              \
+    err = cudaLaunchKernelEx(&config, attention_partial_kernel<HD, REP, WARPS>,                       \
                       static_cast<const uint16_t*>(q),                                               \
                       static_cast<uint16_t*>(const_cast<void*>(cache_k)),                             \
                       static_cast<uint16_t*>(const_cast<void*>(cache_v)), positions,                  \
-                      static_cast<const float2*>(rope), in_cluster ? static_cast<float*>(nullptr) : static_cast<float*>(scratch),      \
+                      static_cast<const float2*>(rope), in_cluster ? static_cast<float*>(nullptr)     \
+                                                                   : static_cast<float*>(scratch),    \
                       static_cast<uint16_t*>(out), int(nq), int(nkv), int(max_seq), int(splits),      \
-                      stages, scale_log2); } while (0)
+                      kAttnStages, scale_log2); } while (0)
+#define B200Q_ATTN(HD, REP) do { if (few_blocks) B200Q_ATTN_W(HD, REP, 8); else B200Q_ATTN_W(HD, REP, 4); } while (0)
     cudaError_t err = cudaSuccess;
-    const int stages = splits * nkv * batch <= sm_count() ? kAttnStagesDeep : kAttnStages;
+    const bool few_blocks = splits * nkv * batch <= sm_count();
     if (head_dim == 128) {
         if (rep == 1) B200Q_ATTN(128, 1); else if (rep == 2) B200Q_ATTN(128, 2);
         else if (rep == 4) B200Q_ATTN(128, 4); else B200Q_ATTN(128, 8);
@@ -395,6 +399,7 @@ int32_t launch_attention(const char* who, const void* q, const void* cache_k, co
                               static_cast<const float*>(scratch), static_cast<uint16_t*>(out), int(splits));
     }
 #undef B200Q_ATTN
+#undef B200Q_ATTN_W
     return launch_status(who, err);
 }
 
