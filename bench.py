@@ -243,7 +243,10 @@ def run_gemv(args, rank: int, world: int, device: torch.device, barrier, reduce_
                      "frac": achieved / peak, "peak_kind": peak_kind,
                      "frac_of_8tbs_nominal": achieved / 8000.0,
                      "algorithmic_bytes_per_launch": gemv_bytes(args.rows),
-                     "us_per_launch": per_launch_s * 1e6, "traffic": None},
+                     "us_per_launch": per_launch_s * 1e6,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch at M=1, from the
+                     # ncu capture summarised in profiles/int4_gemv_oct_k4096_n14336_m1.md
+                     "traffic": 30774016 if args.rows == 1 else None},
         "per_rows": {str(m): {"GB/s": gemv_bytes(m) / (results[m] / 1e3 / LAUNCHES_PER_STEP) / 1e9,
                               "us_per_launch": results[m] * 1e3 / LAUNCHES_PER_STEP}
                      for m in sorted(results)},

@@ -307,8 +307,10 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
             auto fetch = [&](int ks, uint4& q, uint32_t& sc, uint32_t& bias) {
                 q = __ldg(reinterpret_cast<const uint4*>(src + size_t(ks) * (kBK / 2)));
                 const int grp = (ks * kBK) / a.G;
-                sc = uint32_t(__ldg(srow + grp)) * 0x00010001u;
-                bias = 0x43004300u + uint32_t(__ldg(zrow + grp)) * 0x00010001u;
+                // raw values only: any arithmetic here would make the thread wait for these two
+                // loads at once instead of when the stage is dequantized, kPrefetch stages later
+                sc = __ldg(srow + grp);
+                bias = __ldg(zrow + grp);
             };
             const int first = ks_begin + int((group_id + kDequantGroups - it % kDequantGroups) % kDequantGroups);
             uint4 q_ring[kPrefetch];
@@ -327,7 +329,8 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
                     const uint32_t mine = it + uint32_t(ks - ks_begin);  // this stage's use number
                     const int s = mine % kStages;
                     const uint4 q = q_ring[u];
-                    const uint32_t sc = sc_ring[u], bias = bias_ring[u];
+                    const uint32_t sc = sc_ring[u] * 0x00010001u;               // (scale, scale)
+                    const uint32_t bias = 0x43004300u + bias_ring[u] * 0x00010001u;  // (128 + zero) twice
                     if (ks + kPrefetch * kDequantGroups < ks_end)
                         fetch(ks + kPrefetch * kDequantGroups, q_ring[u], sc_ring[u], bias_ring[u]);
                     if (mine >= uint32_t(kStages))
