@@ -95,7 +95,9 @@ allreduce_add_rmsnorm_kernel(const Peers p, size_t slot_elems, int max_rows, uin
     } else {
         for (int c = threadIdx.x; c < chunks; c += blockDim.x) push(c, ld_mutable(mine + c));
     }
-    __threadfence_system();
+    // The flag stores below are releases at system scope by threads that the barrier has
+    // synchronised with every pushing thread: that orders all of the block's pushes before
+    // the flags without a system-wide fence in each of the 512 threads.
     __syncthreads();
     // 2. raise the row's flag on every peer, then wait for every peer's flag here
     if (int(threadIdx.x) < p.world && int(threadIdx.x) != p.rank) {
