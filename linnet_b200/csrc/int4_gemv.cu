@@ -434,8 +434,7 @@ bool run_oct(const GemvArgs& a, cudaStream_t stream, int32_t* status) {
     // prefetch overlaps the tail of the kernel before it.
     OctArgs o{a.x, a.packed, a.scale, a.zero, a.y, a.M, a.K, a.N, 1, 1};
     const bool few = a.M <= 8;
-    static const bool no_short = getenv("B200Q_NO_SHORT") != nullptr;  // measurement hook
-    if (few && a.G == 128 && !no_short) {
+    if (few && a.G == 128) {
         // A warp's run through 8 k-blocks takes ~2.7 us however little else the GPU has to
         // do; while all warps of the problem would fill less than half of the resident warp
         // slots (14 of 28 a multiprocessor), halve the run and double the warps.
@@ -507,13 +506,7 @@ int32_t run_gemv(GemvArgs a, int64_t rows, cudaStream_t stream) {
             step = 16;
             a.M = 16;
         }
-        static const int rows_min = [] {  // measurement hook: B200Q_ROWS_MIN in the environment
-            const char* v = getenv("B200Q_ROWS_MIN");
-            return v != nullptr ? atoi(v) : 9;
-        }();
-        if (a.M >= rows_min && a.M <= 8 && run_rows<T, 1>(a, stream, &status)) {
-            // (measurement only: the shared-activation kernel below its break-even point)
-        } else if (a.M >= 9 && run_rows<T, 2>(a, stream, &status)) {
+        if (a.M >= 9 && run_rows<T, 2>(a, stream, &status)) {
             // 9..16 rows: activations staged once per block (15.7 us against 21.7 us at 16
             // rows, K=4096, N=14336; up to 8 rows the per-lane loads are as fast or faster)
         } else if (run_oct<T>(a, stream, &status)) {
