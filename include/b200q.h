@@ -205,22 +205,23 @@ int32_t b200q_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t inn
  * the reference's one-shot route: python/linnet/src/linnet/torch/collectives.py:145-167,
  * kernel python/linnet/src/linnet/torch/kernels.py:1107-1156) plus the residual add and norm
  * that follow it in a decoder layer.  bf16 only.
- *   peer_areas[r] / peer_flags[r]: HOST arrays of `world` device addresses, all mapped into
- *     this process (symmetric / peer memory): rank r's receive area of this call site,
- *     [world][slot_elems] bf16 with slot_elems >= max_rows * hidden (16-byte aligned), and
- *     rank r's flag words of this call site, [world][max_rows] uint32, zeroed once.  Before
- *     the call, this rank's own kernels (earlier in the stream) have written its partial
- *     sums [rows, hidden] into slot `rank` of its OWN area; the kernel pushes them into slot
- *     `rank` of every peer's area, raises the row flags there and sums what it received.
+ *   peer_areas: HOST array of `world` device addresses, all mapped into this process
+ *     (symmetric / peer memory): rank r's receive area of this call site, [world][slot_words]
+ *     words of 8 bytes (two bf16 values + the call's 32-bit epoch), slot_words >= rows *
+ *     hidden / 2 and even, 16-byte aligned, zeroed once.
+ *   partial: this rank's partial sums [rows, hidden] (local memory, 16-byte aligned), written
+ *     by this rank's own kernels earlier in the stream.  The kernel stores them, each word
+ *     tagged with the epoch, into slot `rank` of every peer's area and reads the peers' words
+ *     from its own area, polling each until its epoch matches.
  *   epoch, done: this rank's uint32 counters of this call site (zeroed once); error: an int32
- *     the kernel sets to 100+r when rank r's flag did not arrive within about a second (the
+ *     the kernel sets to 100+r when rank r's words did not arrive within about a second (the
  *     kernel then returns without reducing; the context stays usable).
- * Every rank must make the same sequence of calls per site; a site's slot may be rewritten
- * only after a call on a DIFFERENT site has been issued in between (a decoder has 2 per layer).
- * Plain peer stores and local loads only. */
-int32_t b200q_tp_allreduce_add_rmsnorm(const int64_t* peer_areas, const int64_t* peer_flags,
-                                       int64_t slot_elems, int64_t max_rows, int32_t world,
-                                       int32_t rank, void* epoch, void* done, void* error, void* x,
+ * Every rank must make the same sequence of calls per site; a site may be used again only
+ * after a call on a DIFFERENT site has been issued in between (a decoder has 2 per layer).
+ * Plain peer stores and local loads only; no barrier, fence or flag between the ranks. */
+int32_t b200q_tp_allreduce_add_rmsnorm(const int64_t* peer_areas, int64_t slot_words,
+                                       const void* partial, int32_t world, int32_t rank,
+                                       void* epoch, void* done, void* error, void* x,
                                        const void* weight, void* y, int64_t rows, int64_t hidden,
                                        float eps, void* stream);
 

@@ -8,25 +8,28 @@
 // python/linnet/src/linnet/torch/kernels.py:1107-1156, which spins without a bound).  A
 // batch-1 decode step has 64 such reductions of 8 KiB: their latency, not their bytes,
 // is the cost, and each is followed by a residual add and a norm.  This kernel does the
-// three in one launch with plain peer stores and local loads (no multimem, no TMA):
-//   1. every rank has a receive area per call site, [source rank][rows][hidden] bf16, and
-//      its decode kernel has written its own partial sums into its own slot of it;
-//   2. one block per row pushes that row into its slot of every peer's area (16-byte
-//      stores over NVLink), fences, and raises the row's flag on every peer
-//      (st.release.sys of the site's epoch); one-way traffic only: nobody waits for a
-//      remote load;
-//   3. the block waits, with a bound, until every peer's flag for the row has reached the
-//      epoch, adds the ranks' rows in rank order (the same order on every rank, so all
-//      ranks get the same bits; the received rows are local memory by now), rounds the sum
-//      to bf16 as an all-reduce of bf16 tensors returns it, adds it to the residual stream
-//      x in place and writes y = rms_norm(x) * weight.
+// three in one launch with plain peer stores and local loads (no multimem, no TMA), and
+// with no barrier, fence or separate flag between the ranks:
+//   1. every rank has a receive area per call site, [source rank][rows][hidden / 2] words
+//      of 8 bytes: two bf16 values and the site's 32-bit epoch.  One block per row reads
+//      this rank's partial sums and stores them, word by word with the epoch attached,
+//      into its slot of every peer's area (16-byte stores of two words; an aligned 8-byte
+//      word arrives whole, so a word whose epoch matches carries this call's values);
+//   2. the block then reads the words the peers stored into its own area, polling (with a
+//      bound) each until its epoch matches, adds the rows in rank order (the same order on
+//      every rank, so all ranks get the same bits), rounds the sum to bf16 as an all-reduce
+//      of bf16 tensors returns it, adds it to the residual stream x in place and writes
+//      y = rms_norm(x) * weight.
+// Latency is one NVLink crossing: nobody waits for an acknowledgement, a release or a remote
+// load.  (The versions before this one: pull the peers' rows after a flag barrier; push the
+// rows, fence, then push a flag per row.  Each ordering step cost microseconds per call.)
 // One area per call site: a rank can only write a site's slots again after every rank has
-// passed the NEXT site, i.e. after it finished reading this one, so no second barrier is
-// needed (the caller alternates at least two sites).  Epochs live in device memory and
-// advance once per call (the last block to finish bumps the site's counter), so the kernel
-// replays inside a CUDA graph.  A wait that runs out (about a second) records an error code
-// and lets the kernel finish with whatever it has; the context stays usable, and later
-// calls skip their waits until the host clears the code.
+// passed the NEXT site, i.e. after it finished reading this one (the caller alternates at
+// least two sites).  Epochs live in device memory and advance once per call (the last
+// block to finish bumps the site's counter), so the kernel replays inside a CUDA graph.  A
+// poll that runs out (about a second) records an error code and lets the kernel finish
+// with whatever it has; the context stays usable, and later calls skip their polls until
+// the host clears the code.
 #include "common.cuh"
 
 namespace b200q {
@@ -35,8 +38,7 @@ namespace {
 constexpr int kMaxRanks = 8;
 
 struct Peers {
-    uint16_t* recv[kMaxRanks];   // every rank's receive area of this site [world][max_rows][hidden] bf16
-    uint32_t* flags[kMaxRanks];  // every rank's flag words of this site [world][max_rows]
+    uint2* area[kMaxRanks];  // every rank's receive area of this site [world][slot_words] of (2 bf16, epoch)
     int world, rank;
 };
 
@@ -46,21 +48,27 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
     __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&p);
 }
+__device__ __forceinline__ uint4 ld_words(const uint4* p) {  // two words, straight from L2
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
 
-// CPT: 16-byte pieces of a row each thread keeps in registers from the push to the scaling
-// (0: any width, rows re-read from memory).
+// One 16-byte piece (8 bf16) of a row per thread and step; CPT pieces are kept in registers
+// from the push to the scaling (0: any width, rows re-read from memory).
 template <int CPT>
 __global__ void __launch_bounds__(512)
-allreduce_add_rmsnorm_kernel(const Peers p, size_t slot_elems, int max_rows, uint32_t* __restrict__ epoch,
-                             uint32_t* __restrict__ done, int* __restrict__ error, uint16_t* x,
-                             const uint16_t* __restrict__ weight, uint16_t* __restrict__ y, int hidden,
-                             float eps) {
+allreduce_add_rmsnorm_kernel(const Peers p, size_t slot_words, const uint16_t* partial,
+                             uint32_t* __restrict__ epoch, uint32_t* __restrict__ done,
+                             int* __restrict__ error, uint16_t* x, const uint16_t* __restrict__ weight,
+                             uint16_t* __restrict__ y, int hidden, float eps) {
     __shared__ float partial_sums[16];
-    __shared__ int gave_up;
     constexpr int kHeld = CPT > 0 ? CPT : 1;
     const int row = blockIdx.x, chunks = hidden / 8;
     const uint4* wr = reinterpret_cast<const uint4*>(weight);
-    uint4 g[kHeld], own[kHeld], v[kHeld];
+    uint4 g[kHeld], v[kHeld];
     if (CPT > 0) {  // the norm weights do not depend on the kernel before this one
 #pragma unroll
         for (int u = 0; u < kHeld; ++u) {
@@ -71,78 +79,63 @@ allreduce_add_rmsnorm_kernel(const Peers p, size_t slot_elems, int max_rows, uin
     pdl_wait();  // this rank's partial sums come from the kernel before this one
     pdl_launch_dependents();
     const uint32_t e = *reinterpret_cast<volatile uint32_t*>(epoch) + 1;
-    // After one wait has run out every later call returns at once instead of waiting again.
-    if (threadIdx.x == 0) gave_up = *reinterpret_cast<volatile int*>(error) != 0;
+    // After one poll has run out every later call returns at once instead of waiting again.
+    bool gave_up = *reinterpret_cast<volatile int*>(error) != 0;
 
-    // 1. push this rank's row into its slot of every peer's area
-    const size_t row_at = size_t(p.rank) * slot_elems + size_t(row) * hidden;
-    const uint4* mine = reinterpret_cast<const uint4*>(p.recv[p.rank] + row_at);
-    auto push = [&](int c, const uint4& piece) {
-        for (int peer = 0; peer < p.world; ++peer)
-            if (peer != p.rank) reinterpret_cast<uint4*>(p.recv[peer] + row_at)[c] = piece;
-    };
-    if (CPT > 0) {
-#pragma unroll
-        for (int u = 0; u < kHeld; ++u) {
-            const int c = threadIdx.x + u * blockDim.x;
-            own[u] = c < chunks ? ld_mutable(mine + c) : make_uint4(0, 0, 0, 0);
-        }
-#pragma unroll
-        for (int u = 0; u < kHeld; ++u) {
-            const int c = threadIdx.x + u * blockDim.x;
-            if (c < chunks) push(c, own[u]);
-        }
-    } else {
-        for (int c = threadIdx.x; c < chunks; c += blockDim.x) push(c, ld_mutable(mine + c));
-    }
-    // The flag stores below are releases at system scope by threads that the barrier has
-    // synchronised with every pushing thread: that orders all of the block's pushes before
-    // the flags without a system-wide fence in each of the 512 threads.
-    __syncthreads();
-    // 2. raise the row's flag on every peer, then wait for every peer's flag here
-    if (int(threadIdx.x) < p.world && int(threadIdx.x) != p.rank) {
-        uint32_t* theirs = p.flags[threadIdx.x] + size_t(p.rank) * max_rows + row;
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(e) : "memory");
-        if (!gave_up) {
-            const uint32_t* here = p.flags[p.rank] + size_t(threadIdx.x) * max_rows + row;
-            uint64_t start = 0;
-            for (uint32_t spins = 0;; ++spins) {
-                uint32_t seen;
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(here) : "memory");
-                if (int32_t(seen - e) >= 0) break;
-                if ((spins & 255u) == 255u) {
-                    uint64_t now;
-                    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-                    if (start == 0) start = now;
-                    if (now - start > 1000000000ull) {  // a peer never arrived: give up, stay usable
-                        atomicCAS(error, 0, 100 + int(threadIdx.x));
-                        gave_up = 1;
-                        break;
-                    }
-                }
-            }
-        }
-    }
-    __syncthreads();
-
-    // 3. rows of all ranks in rank order (f32), one rounding, residual add, sum of squares
+    const uint4* mine = reinterpret_cast<const uint4*>(partial + size_t(row) * hidden);
+    const size_t row_words = size_t(row) * (hidden / 2);  // this row inside a slot, in words
     uint4* xr = reinterpret_cast<uint4*>(x + size_t(row) * hidden);
     float sum_sq = 0.0f;
-    auto reduce_add_square = [&](int c, const uint4& own_piece) {
-        float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+
+    // piece c: push it to every peer, collect the peers' pieces, reduce, add, square
+    auto exchange = [&](int c) {
+        const uint4 own = ld_mutable(mine + c);
+        const uint4 first = make_uint4(own.x, e, own.y, e), second = make_uint4(own.z, e, own.w, e);
+        for (int peer = 0; peer < p.world; ++peer)
+            if (peer != p.rank) {
+                uint4* dst = reinterpret_cast<uint4*>(p.area[peer] + size_t(p.rank) * slot_words + row_words + 4 * c);
+                dst[0] = first;
+                dst[1] = second;
+            }
         uint4 t = ld_mutable(xr + c);
         uint4 q[kMaxRanks];
+        unsigned pending = 0;
 #pragma unroll
         for (int r = 0; r < kMaxRanks; ++r) {
             q[r] = make_uint4(0, 0, 0, 0);
-            if (r < p.world && r != p.rank)
-                q[r] = ld_mutable(reinterpret_cast<const uint4*>(p.recv[p.rank] + size_t(r) * slot_elems +
-                                                                 size_t(row) * hidden) + c);
+            if (r < p.world && r != p.rank) pending |= 1u << r;
         }
+        if (gave_up) pending = 0;
+        uint64_t start = 0;
+        for (uint32_t spins = 0; pending != 0; ++spins) {
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (pending & (1u << r)) {
+                    const uint4* src = reinterpret_cast<const uint4*>(p.area[p.rank] + size_t(r) * slot_words +
+                                                                      row_words + 4 * c);
+                    const uint4 a = ld_words(src), b = ld_words(src + 1);
+                    if (a.y == e && a.w == e && b.y == e && b.w == e) {
+                        q[r] = make_uint4(a.x, a.z, b.x, b.z);
+                        pending &= ~(1u << r);
+                    }
+                }
+            if (pending != 0 && (spins & 63u) == 63u) {
+                uint64_t now;
+                asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+                if (start == 0) start = now;
+                if (now - start > 1000000000ull) {  // a peer never arrived: give up, stay usable
+                    atomicCAS(error, 0, 100 + (__ffs(int(pending)) - 1));
+                    gave_up = true;
+                    pending = 0;
+                }
+            }
+        }
+        if (gave_up) return t;
+        float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
         for (int r = 0; r < kMaxRanks; ++r) {
             if (r >= p.world) break;
-            const uint4 qr = r == p.rank ? own_piece : q[r];
+            const uint4 qr = r == p.rank ? own : q[r];
             s[0] += lo16(qr.x); s[1] += hi16(qr.x); s[2] += lo16(qr.y); s[3] += hi16(qr.y);
             s[4] += lo16(qr.z); s[5] += hi16(qr.z); s[6] += lo16(qr.w); s[7] += hi16(qr.w);
         }
@@ -164,10 +157,10 @@ allreduce_add_rmsnorm_kernel(const Peers p, size_t slot_elems, int max_rows, uin
         for (int u = 0; u < kHeld; ++u) {
             const int c = threadIdx.x + u * blockDim.x;
             v[u] = make_uint4(0, 0, 0, 0);
-            if (c < chunks) v[u] = gave_up ? ld_mutable(xr + c) : reduce_add_square(c, own[u]);
+            if (c < chunks) v[u] = exchange(c);
         }
-    } else if (!gave_up) {
-        for (int c = threadIdx.x; c < chunks; c += blockDim.x) reduce_add_square(c, ld_mutable(mine + c));
+    } else {
+        for (int c = threadIdx.x; c < chunks; c += blockDim.x) exchange(c);
     }
     for (int d = 16; d >= 1; d >>= 1) sum_sq += __shfl_xor_sync(0xFFFFFFFFu, sum_sq, d);
     if (threadIdx.x % 32 == 0) partial_sums[threadIdx.x / 32] = sum_sq;
@@ -209,27 +202,26 @@ allreduce_add_rmsnorm_kernel(const Peers p, size_t slot_elems, int max_rows, uin
 
 using namespace b200q;
 
-extern "C" int32_t b200q_tp_allreduce_add_rmsnorm(const int64_t* peer_areas, const int64_t* peer_flags,
-                                                  int64_t slot_elems, int64_t max_rows, int32_t world,
-                                                  int32_t rank, void* epoch, void* done, void* error, void* x,
+extern "C" int32_t b200q_tp_allreduce_add_rmsnorm(const int64_t* peer_areas, int64_t slot_words,
+                                                  const void* partial, int32_t world, int32_t rank,
+                                                  void* epoch, void* done, void* error, void* x,
                                                   const void* weight, void* y, int64_t rows, int64_t hidden,
                                                   float eps, void* stream) {
     B200Q_REQUIRE(world >= 2 && world <= kMaxRanks && rank >= 0 && rank < world,
                   "tp_allreduce_add_rmsnorm: 2..8 ranks, got world=%d rank=%d", world, rank);
     B200Q_REQUIRE(rows >= 0 && hidden > 0 && hidden % 8 == 0, "tp_allreduce_add_rmsnorm: hidden must be a multiple of 8");
-    B200Q_REQUIRE(rows <= max_rows && slot_elems >= max_rows * hidden && slot_elems % 8 == 0,
-                  "tp_allreduce_add_rmsnorm: %lld rows do not fit slots of %lld rows", (long long)rows,
-                  (long long)max_rows);
+    B200Q_REQUIRE(slot_words >= rows * (hidden / 2) && slot_words % 2 == 0,
+                  "tp_allreduce_add_rmsnorm: %lld rows of %lld do not fit slots of %lld words", (long long)rows,
+                  (long long)hidden, (long long)slot_words);
     if (rows == 0) return B200Q_OK;
-    B200Q_REQUIRE(peer_areas && peer_flags && epoch && done && error && x && weight && y,
-                  "tp_allreduce_add_rmsnorm: null argument");
+    B200Q_REQUIRE(peer_areas && partial && epoch && done && error && x && weight && y && aligned(partial, 16),
+                  "tp_allreduce_add_rmsnorm: null or misaligned argument");
     Peers p{};
     p.world = world;
     p.rank = rank;
     for (int r = 0; r < world; ++r) {
-        p.recv[r] = reinterpret_cast<uint16_t*>(peer_areas[r]);
-        p.flags[r] = reinterpret_cast<uint32_t*>(peer_flags[r]);
-        B200Q_REQUIRE(p.recv[r] && p.flags[r] && aligned(p.recv[r], 16), "tp_allreduce_add_rmsnorm: bad peer pointer");
+        p.area[r] = reinterpret_cast<uint2*>(peer_areas[r]);
+        B200Q_REQUIRE(p.area[r] && aligned(p.area[r], 16), "tp_allreduce_add_rmsnorm: bad peer pointer");
     }
     const int chunks = int(hidden / 8);
     int threads = ((chunks + 31) / 32) * 32;
@@ -238,9 +230,9 @@ extern "C" int32_t b200q_tp_allreduce_add_rmsnorm(const int64_t* peer_areas, con
     const dim3 grid{unsigned(rows)}, block{unsigned(threads)};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define B200Q_TP_LAUNCH(CPT)                                                                              \
-    launch_overlapped(allreduce_add_rmsnorm_kernel<CPT>, grid, block, 0, s, p, size_t(slot_elems),        \
-                      int(max_rows), static_cast<uint32_t*>(epoch), static_cast<uint32_t*>(done),         \
-                      static_cast<int*>(error), static_cast<uint16_t*>(x),                                \
+    launch_overlapped(allreduce_add_rmsnorm_kernel<CPT>, grid, block, 0, s, p, size_t(slot_words),        \
+                      static_cast<const uint16_t*>(partial), static_cast<uint32_t*>(epoch),               \
+                      static_cast<uint32_t*>(done), static_cast<int*>(error), static_cast<uint16_t*>(x),  \
                       static_cast<const uint16_t*>(weight), static_cast<uint16_t*>(y), int(hidden), eps)
     const cudaError_t err = held <= 1 ? B200Q_TP_LAUNCH(1) : held <= 2 ? B200Q_TP_LAUNCH(2)
                           : held <= 4 ? B200Q_TP_LAUNCH(4) : B200Q_TP_LAUNCH(0);

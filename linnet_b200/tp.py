@@ -8,7 +8,7 @@ symmetric memory when the message is small and through NCCL otherwise
 two ops that always follow it in a decoder layer folded in, and with every wait bounded.
 
 Memory comes from `torch.distributed._symmetric_memory` (one allocation per rank, mapped
-into every peer by `rendezvous`); the kernel uses plain peer loads and stores only.
+into every peer by `rendezvous`); the kernel uses plain peer stores and local loads only.
 """
 
 from __future__ import annotations
@@ -42,31 +42,29 @@ class PeerReduce:
         if not 2 <= self.world <= 8:
             raise ValueError(f"PeerReduce runs on 2..8 ranks, not {self.world}")
         self.sites, self.max_rows, self.hidden, self.device = sites, max_rows, hidden, device
-        # per site: a receive area [source rank][max_rows][hidden] bf16, then flags [source rank][max_rows] u32
-        self.slot_elems = max_rows * hidden
-        self.area_bytes = self.world * self.slot_elems * 2
-        self.flag_bytes = self.world * max_rows * 4
-        total = sites * (self.area_bytes + self.flag_bytes)
-        self.memory = symm.empty(total, dtype=torch.uint8, device=device)
+        # per site: a receive area [source rank][max_rows][hidden / 2] words of (2 bf16, epoch)
+        self.slot_words = max_rows * hidden // 2
+        self.area_bytes = self.world * self.slot_words * 8
+        self.memory = symm.empty(sites * self.area_bytes, dtype=torch.uint8, device=device)
         self.memory.zero_()
         self.handle = symm.rendezvous(self.memory, group=group)
         self.bases = [int(p) for p in self.handle.buffer_ptrs]
+        # this rank's partial sums (local; rewritten before every reduction, in stream order)
+        self.own = torch.empty(max_rows, hidden, dtype=torch.bfloat16, device=device)
         # epoch and done counters per site, one error word
         self.state = torch.zeros(2 * sites + 1, dtype=torch.int32, device=device)
         torch.cuda.synchronize(device)
-        dist.barrier(group=group)  # nobody signals before every rank's flags are zero
+        dist.barrier(group=group)  # nobody stores into an area before every rank has zeroed its own
         int64s = ctypes.c_int64 * self.world
         self._areas = [int64s(*[b + s * self.area_bytes for b in self.bases]) for s in range(sites)]
-        flags0 = sites * self.area_bytes
-        self._flags = [int64s(*[b + flags0 + s * self.flag_bytes for b in self.bases]) for s in range(sites)]
 
     def partial(self, site: int, rows: int) -> torch.Tensor:
-        """This rank's own slot of a call site's receive area, `[rows, hidden]` bf16 (a view of
-        the symmetric memory): where the row-split linear writes its partial sums."""
+        """Where the row-split linear of a call site writes this rank's partial sums, `[rows,
+        hidden]` bf16 (the same local buffer for every site: it is read by the reduction that
+        follows in the stream before the next linear writes it)."""
         if not 0 <= site < self.sites or not 0 < rows <= self.max_rows:
             raise ValueError(f"PeerReduce: site {site} / rows {rows} outside {self.sites} sites of {self.max_rows} rows")
-        start = site * self.area_bytes + self.rank * self.slot_elems * 2
-        return self.memory[start:start + rows * self.hidden * 2].view(torch.bfloat16).view(rows, self.hidden)
+        return self.own[:rows]
 
     def add_rmsnorm(self, site: int, x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
         rows, hidden = x.shape
@@ -77,10 +75,10 @@ class PeerReduce:
         y = torch.empty_like(x)
         state = self.state.data_ptr()
         _lib.check(_lib.load().b200q_tp_allreduce_add_rmsnorm(
-            ctypes.addressof(self._areas[site]), ctypes.addressof(self._flags[site]), self.slot_elems,
-            self.max_rows, self.world, self.rank, state + 4 * site, state + 4 * (self.sites + site),
-            state + 8 * self.sites, x.data_ptr(), weight.contiguous().data_ptr(), y.data_ptr(), rows, hidden,
-            float(eps), torch.cuda.current_stream(self.device).cuda_stream))
+            ctypes.addressof(self._areas[site]), self.slot_words, self.own.data_ptr(), self.world, self.rank,
+            state + 4 * site, state + 4 * (self.sites + site), state + 8 * self.sites, x.data_ptr(),
+            weight.contiguous().data_ptr(), y.data_ptr(), rows, hidden, float(eps),
+            torch.cuda.current_stream(self.device).cuda_stream))
         return y
 
     def error(self) -> int:
