@@ -377,6 +377,8 @@ def main() -> None:
     parser.add_argument("--no-decode", action="store_true")
     parser.add_argument("--single-batch", action="store_true",
                         help="decode: time only --batch, not 1 / 8 / 64 as well (for profiling)")
+    parser.add_argument("--peer-protocol", default=None, choices=["words", "flags"],
+                        help="exchange of the peer reduction (default: words on 2 ranks, flags on more)")
     parser.add_argument("--reduce", default="peer", choices=["peer", "nccl"],
                         help="tensor-parallel decode: one peer-memory kernel per reduction, or NCCL")
     args = parser.parse_args()

@@ -225,6 +225,20 @@ int32_t b200q_tp_allreduce_add_rmsnorm(const int64_t* peer_areas, int64_t slot_w
                                        const void* weight, void* y, int64_t rows, int64_t hidden,
                                        float eps, void* stream);
 
+/* b200q_tp_allreduce_add_rmsnorm with a different exchange: rows pushed as plain bf16, then
+ * one flag per (source rank, row).  peer_areas[r]: rank r's receive area of the call site,
+ * [world][slot_elems] bf16 with slot_elems >= max_rows * hidden; peer_flags[r]: rank r's flag
+ * words of the site, [world][max_rows] uint32, zeroed once.  This rank's partial sums are
+ * written (by its own kernels, earlier in the stream) into slot `rank` of its OWN area.
+ * Same arithmetic, counters, error code and call-site rule.  Faster than the tagged words from
+ * about four ranks up (half the NVLink bytes), slower on two.  No reference counterpart beyond
+ * the all_reduce both replace. */
+int32_t b200q_tp_allreduce_add_rmsnorm_flags(const int64_t* peer_areas, const int64_t* peer_flags,
+                                             int64_t slot_elems, int64_t max_rows, int32_t world,
+                                             int32_t rank, void* epoch, void* done, void* error,
+                                             void* x, const void* weight, void* y, int64_t rows,
+                                             int64_t hidden, float eps, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

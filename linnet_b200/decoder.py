@@ -184,14 +184,14 @@ class Int4Decoder:
             return self._step_fused(tokens, positions)
         return self._step_torch(tokens, positions)
 
-    def enable_peer_reduce(self, max_rows: int) -> None:
+    def enable_peer_reduce(self, max_rows: int, protocol: str | None = None) -> None:
         """Replaces each NCCL all-reduce + residual add + norm of the fused route by one
         peer-memory kernel (`linnet_b200.tp.PeerReduce`); collective: every rank calls it."""
         from .tp import PeerReduce
 
         if self.tp > 1:
             self.peer_reduce = PeerReduce(2 * self.cfg.layers, max_rows, self.cfg.hidden, self.embed.device,
-                                          self.group)
+                                          self.group, protocol)
 
     def _reduce_norm(self, site: int, x: torch.Tensor, inputs: torch.Tensor, weight: Int4,
                      norm: torch.Tensor) -> torch.Tensor:
@@ -316,7 +316,7 @@ def bench(args, rank: int, world: int, device: torch.device, barrier, reduce_max
     route = getattr(args, "reduce", "peer") if world > 1 else "none"
     peer_reduce = None
     if route == "peer":
-        model.enable_peer_reduce(max(batches))
+        model.enable_peer_reduce(max(batches), getattr(args, "peer_protocol", None))
         peer_reduce = model.peer_reduce
     # With the peer route on, the NCCL route is timed beside it (it is the baseline the
     # fused kernel has to beat); the headline numbers are the selected route's.
@@ -405,7 +405,8 @@ def bench(args, rank: int, world: int, device: torch.device, barrier, reduce_max
                      "traffic": None},
         "per_batch": {str(b): results[b] for b in sorted(results)},
         "reduce_route": {"none": "single GPU: no reduction",
-                         "peer": "one peer-memory kernel per row-split layer: all-reduce + residual add + RMSNorm",
+                         "peer": "one peer-memory kernel per row-split layer: all-reduce + residual add + RMSNorm"
+                                 + (f" ({peer_reduce.protocol} exchange)" if peer_reduce is not None else ""),
                          "nccl": "NCCL all-reduce, then the add + RMSNorm kernel"}[route],
         **({"per_batch_nccl_route": {str(b): nccl_results[b] for b in sorted(nccl_results)}}
            if nccl_results else {}),

@@ -48,11 +48,12 @@ def _checks(rank: int, world: int, dev: torch.device) -> dict:
     from linnet_b200 import glue, kernels
     from linnet_b200.tp import PeerReduce
 
-    report: dict = {}
-    if True:
+    report: dict = {"kernel_exact": True, "kernel_error": 0, "decoder_max_diff": 0.0, "replay_equal": True,
+                    "decoder_error": 0}
+    for protocol in ("words", "flags"):  # both exchanges, whatever the default for this group size
         # 1. the kernel alone, three call sites visited round-robin, several epochs
         hidden, rows, sites = 1024, 5, 3
-        reduce = PeerReduce(sites, 8, hidden, dev)
+        reduce = PeerReduce(sites, 8, hidden, dev, protocol=protocol)
         gen = torch.Generator(device=dev).manual_seed(100 + rank)
         shared = torch.Generator(device=dev).manual_seed(7)
         weight = (1 + 0.1 * torch.randn(hidden, device=dev, generator=shared)).to(torch.bfloat16)
@@ -73,8 +74,8 @@ def _checks(rank: int, world: int, dev: torch.device) -> dict:
                 x_ref = x.clone()
                 y_ref = glue.add_rmsnorm(x_ref, total.to(torch.bfloat16), weight, 1e-5)
                 exact &= bool(torch.equal(x_peer, x_ref)) and bool(torch.equal(y_peer, y_ref))
-        report["kernel_exact"] = exact
-        report["kernel_error"] = reduce.error()
+        report["kernel_exact"] &= exact
+        report["kernel_error"] |= reduce.error()
 
         # 2. the decoder: NCCL route and peer route produce the same logits, eagerly and replayed
         cfg = dec.DecoderConfig.tiny()
@@ -83,9 +84,10 @@ def _checks(rank: int, world: int, dev: torch.device) -> dict:
         for route in ("nccl", "peer"):
             model = du.rank_model(cfg, whole, rank, world, kernels.int4_linear, device=dev)
             if route == "peer":
-                model.enable_peer_reduce(4)
+                model.enable_peer_reduce(4, protocol)
             logits[route] = du.run_steps(model, cfg, batch=4, steps=3, device=dev).float()
-        report["decoder_max_diff"] = (logits["nccl"] - logits["peer"]).abs().max().item()
+        report["decoder_max_diff"] = max(report["decoder_max_diff"],
+                                         (logits["nccl"] - logits["peer"]).abs().max().item())
         report["decoder_scale"] = logits["nccl"].abs().max().item()
 
         tokens = torch.tensor([3, 5, 7, 9], device=dev)
@@ -100,9 +102,10 @@ def _checks(rank: int, world: int, dev: torch.device) -> dict:
             for _ in range(5):
                 graph.replay()
             torch.cuda.synchronize()
-        report["replay_equal"] = bool(torch.equal(out, eager))
-        report["decoder_error"] = model.peer_reduce.error()
-        del graph, out
+        report["replay_equal"] &= bool(torch.equal(out, eager))
+        report["decoder_error"] |= model.peer_reduce.error()
+        del graph, out, model, reduce
+        gc.collect()
     return report
 
 
