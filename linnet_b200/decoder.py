@@ -6,7 +6,9 @@ by a `Shards` generic (docs/torch.md:210-220; python/linnet/tests/torch/test_sha
   fused gate|up, and the output head (followed by one all-gather of the logits);
 * row split (whole input groups; cut along axis 1): o_proj and down_proj, each
   followed by ONE all-reduce of the `[batch, hidden]` partial sums
-  (`std.nn.parallel::all_reduce`, stdlib/nn/parallel.linnet:9-11);
+  (`std.nn.parallel::all_reduce`, stdlib/nn/parallel.linnet:9-11): NCCL, or after
+  `enable_peer_reduce()` one peer-memory kernel that also does the residual add and the
+  norm that follow (`linnet_b200.tp`);
 * the KV cache and attention are split by KV heads.
 
 Fusing q|k|v and gate|up is this build's own step at pack time (the reference joins
