@@ -83,6 +83,20 @@ def test_shard_shapes_and_checks():
     assert abs(full.int4_elements() - 7.5046e9) < 1e6
 
 
+def test_attention_split_heuristic():
+    """Pure host logic: a power of two, at least 64 positions a split, about two blocks per SM."""
+    from linnet_b200 import glue
+
+    assert glue.attention_splits(1, 8, 2048) == 32      # the cluster launch caps it at 8
+    assert glue.attention_splits(8, 8, 2048) == 4
+    assert glue.attention_splits(64, 8, 2048) == 1
+    assert glue.attention_splits(1, 1, 2048) == 32
+    assert glue.attention_splits(1, 8, 100) == 1        # fewer than 128 positions: no split
+    for batch, nkv, seq in ((1, 8, 2048), (3, 2, 777), (200, 8, 4096)):
+        splits = glue.attention_splits(batch, nkv, seq)
+        assert splits & (splits - 1) == 0 and (splits == 1 or seq // splits >= 64)
+
+
 def _free_port() -> int:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
