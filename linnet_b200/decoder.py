@@ -317,9 +317,14 @@ def bench(args, rank: int, world: int, device: torch.device, barrier, reduce_max
     e2e = {}
     route = getattr(args, "reduce", "peer") if world > 1 else "none"
     peer_reduce = None
+    peer_unavailable = None
     if route == "peer":
-        model.enable_peer_reduce(max(batches), getattr(args, "peer_protocol", None))
-        peer_reduce = model.peer_reduce
+        try:
+            model.enable_peer_reduce(max(batches), getattr(args, "peer_protocol", None))
+            peer_reduce = model.peer_reduce
+        except Exception as exc:  # no symmetric memory on this box: the NCCL route is the product then
+            peer_unavailable = f"{type(exc).__name__}: {exc}"[:200]
+            route = "nccl"
     # With the peer route on, the NCCL route is timed beside it (it is the baseline the
     # fused kernel has to beat); the headline numbers are the selected route's.
     passes = [(route, batches)] + ([("nccl", sorted(set(batches)))] if route == "peer" else [])
@@ -412,6 +417,7 @@ def bench(args, rank: int, world: int, device: torch.device, barrier, reduce_max
                          "nccl": "NCCL all-reduce, then the add + RMSNorm kernel"}[route],
         **({"per_batch_nccl_route": {str(b): nccl_results[b] for b in sorted(nccl_results)}}
            if nccl_results else {}),
+        **({"peer_reduce_unavailable": peer_unavailable} if peer_unavailable else {}),
         "e2e": e2e,
         "gpu_launches": args.steps * launches_per_step,
         "clocks": clocks.summary() if clocks else None,
