@@ -34,6 +34,28 @@ def test_binding_matches_header():
     assert lib.b200q_abi_version() == 1
 
 
+def test_binding_argument_lists_match_header():
+    """Every ctypes prototype has the header's argument count and the header's kinds of
+    arguments (pointer / 64-bit / 32-bit / float), in order."""
+    from ctypes import c_float, c_int32, c_int64, c_void_p
+
+    from linnet_b200 import _lib
+
+    header = (ROOT / "include" / "b200q.h").read_text()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    kinds = {c_void_p: "pointer", c_int64: "int64", c_int32: "int32", c_float: "float"}
+    for name, argtypes in _lib.PROTOTYPES.items():
+        match = re.search(r"\b" + name + r"\s*\(([^;]*?)\)\s*;", header, flags=re.S)
+        assert match, name
+        text = match.group(1).strip()
+        params = [] if text in ("", "void") else [p.strip() for p in text.split(",")]
+        assert len(params) == len(argtypes), f"{name}: header has {len(params)} arguments, binding {len(argtypes)}"
+        for position, (param, ctype) in enumerate(zip(params, argtypes)):
+            want = ("pointer" if "*" in param else "int64" if param.startswith("int64_t")
+                    else "int32" if param.startswith("int32_t") else "float" if param.startswith("float") else param)
+            assert kinds[ctype] == want, f"{name} argument {position}: header `{param}`, binding {kinds[ctype]}"
+
+
 def test_argument_errors_need_no_gpu():
     """Shape validation happens on the host, before any launch."""
     from linnet_b200 import _lib
