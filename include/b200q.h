@@ -13,7 +13,9 @@
  * dense and row-major; sizes are element counts.  `stream` is a cudaStream_t
  * passed as void*.  Unless an entry says otherwise it allocates nothing, never
  * synchronises and keeps no state between calls, so it can be recorded into a
- * CUDA graph and called from several host threads on different streams.
+ * CUDA graph and called from several host threads on different streams.  (The
+ * library remembers, per kernel and device, that it has raised the kernel's
+ * shared-memory limit: one runtime call on first use, none afterwards.)
  */
 #ifndef B200Q_H
 #define B200Q_H
@@ -82,6 +84,33 @@ int32_t b200q_int4_gemv(const void* x, const uint8_t* packed, const void* scale,
                         const uint8_t* zero, void* y, int64_t rows, int64_t in,
                         int64_t out, int64_t group, int32_t dtype, void* stream);
 
+/* Flags of b200q_int4_gemv_ex / b200q_int4_linear_ex (0: the defaults of the entries
+ * above).
+ *   B200Q_EXACT_WEIGHTS   every weight is (q - zero) * scale computed in f32 and rounded
+ *     once to the 16-bit type before the product: bit for bit the weight the reference's
+ *     torch path multiplies by (python/linnet/src/linnet/torch/native.py:417-424).
+ *     Without the flag, for groups of 128 and up to 16 rows, zero point and scale are
+ *     applied in f32 to each group's sum of exact products instead; that is closer to
+ *     exact arithmetic and differs from the reference by the rounding noise of its
+ *     weights (2^-9 relative per weight: sigma 1.4e-3 per output at K=4096 with weights
+ *     ~N(0, 0.02) and inputs ~N(0, 1), against the 1e-2 tolerance), at half the
+ *     instructions.  The reference selects these kernels under its `fast` numerics
+ *     policy only (src/opt/candidates.cpp:28-33).
+ *   B200Q_EARLY_DEPENDENTS   the kernels after this one in the stream may start (up to
+ *     their own wait on this one's results) as soon as this one has started, instead of
+ *     when its last weights are in: pays when the next kernel is another product that can
+ *     prefetch its weights meanwhile (q, k, v of one input; a chain of products), costs
+ *     when the next kernel only takes room while it waits. */
+enum { B200Q_EXACT_WEIGHTS = 1, B200Q_EARLY_DEPENDENTS = 2 };
+int32_t b200q_int4_gemv_ex(const void* x, const uint8_t* packed, const void* scale,
+                           const uint8_t* zero, void* y, int64_t rows, int64_t in,
+                           int64_t out, int64_t group, int32_t dtype, int32_t flags,
+                           void* stream);
+int32_t b200q_int4_linear_ex(const void* x, const uint8_t* packed, const void* scale,
+                             const uint8_t* zero, void* y, int64_t rows, int64_t in,
+                             int64_t out, int64_t group, int32_t dtype, int32_t flags,
+                             void* stream);
+
 /* The prefill kernel alone: TMA + tcgen05/TMEM dequant-GEMM (bf16; `in` and `group`
  * multiples of 64; any rows and out). */
 int32_t b200q_int4_gemm(const void* x, const uint8_t* packed, const void* scale,
@@ -90,7 +119,8 @@ int32_t b200q_int4_gemm(const void* x, const uint8_t* packed, const void* scale,
 
 /* Synchronises the device and reports whether any b200q_int4_gemm launch on it gave
  * up on one of its bounded waits (B200Q_ERROR, with the waiting role in the message);
- * such a launch leaves its output incomplete but the context usable.  No reference
+ * such a launch leaves its output incomplete but the context usable.  Reporting clears
+ * the condition (until then later launches cut their waits short).  No reference
  * counterpart: the reference's kernels spin without a bound. */
 int32_t b200q_int4_gemm_status(void);
 
@@ -133,7 +163,12 @@ int32_t b200q_add_rmsnorm(void* x, const void* delta, const void* weight, void* 
 /* qkv [batch, (nq + 2 nkv) * head_dim]: rotary embedding (halves rotated) of the
  * query and key heads at positions[batch] (int64); queries go to q_out
  * [batch, nq, head_dim], keys and values to cache_{k,v}[batch, nkv, max_seq,
- * head_dim] at their position. */
+ * head_dim] at their position.
+ * Positions are device data, so they are checked on the device, here and in the
+ * attention entries below: a position outside 0 .. max_seq-1 stores nothing for that
+ * row, forms no address outside the caches, and is recorded for
+ * b200q_decoder_status().  The caches must hold finite values everywhere (fill them
+ * with zeros once): a tile of keys and values is read whole. */
 int32_t b200q_rope_cache(const void* qkv, const int64_t* positions, void* q_out,
                          void* cache_k, void* cache_v, int64_t batch, int64_t nq,
                          int64_t nkv, int64_t head_dim, int64_t max_seq, float theta,
@@ -193,6 +228,12 @@ int32_t b200q_decode_attention_static(const void* q, const void* cache_k, const 
                                       int64_t nq, int64_t nkv, int64_t head_dim, int64_t max_seq,
                                       int64_t splits, void* stream);
 
+/* Synchronises the device and reports (B200Q_ERROR, naming the batch row) whether a
+ * decode-step kernel since the last report met a position outside its cache; reporting
+ * clears the condition.  No reference counterpart (PyTorch's index_put_ raises a
+ * device-side assertion there). */
+int32_t b200q_decoder_status(void);
+
 /* out[rows, inner] = silu(gate_up[:, :inner]) * gate_up[:, inner:], silu rounded to
  * bf16 before the product as the two PyTorch ops round. */
 int32_t b200q_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t inner,
@@ -207,15 +248,17 @@ int32_t b200q_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t inn
  * that follow it in a decoder layer.  bf16 only.
  *   peer_areas: HOST array of `world` device addresses, all mapped into this process
  *     (symmetric / peer memory): rank r's receive area of this call site, [world][slot_words]
- *     words of 8 bytes (two bf16 values + the call's 32-bit epoch), slot_words >= rows *
- *     hidden / 2 and even, 16-byte aligned, zeroed once.
+ *     words of 8 bytes (two bf16 values + the call's 32-bit epoch; each word is stored and
+ *     polled as one 64-bit element, which is what makes values and epoch arrive together),
+ *     slot_words >= rows * hidden / 2 and even, 16-byte aligned, zeroed once.
  *   partial: this rank's partial sums [rows, hidden] (local memory, 16-byte aligned), written
  *     by this rank's own kernels earlier in the stream.  The kernel stores them, each word
  *     tagged with the epoch, into slot `rank` of every peer's area and reads the peers' words
  *     from its own area, polling each until its epoch matches.
  *   epoch, done: this rank's uint32 counters of this call site (zeroed once); error: an int32
- *     the kernel sets to 100+r when rank r's words did not arrive within about a second (the
- *     kernel then returns without reducing; the context stays usable).
+ *     the kernel sets to 100+r when rank r's words did not arrive within the wait limit (the
+ *     kernel then returns without reducing; the context stays usable, and later calls do not
+ *     wait at all until the host has zeroed the word).
  * Every rank must make the same sequence of calls per site; a site may be used again only
  * after a call on a DIFFERENT site has been issued in between (a decoder has 2 per layer).
  * Plain peer stores and local loads only; no barrier, fence or flag between the ranks. */
@@ -238,6 +281,11 @@ int32_t b200q_tp_allreduce_add_rmsnorm_flags(const int64_t* peer_areas, const in
                                              int32_t rank, void* epoch, void* done, void* error,
                                              void* x, const void* weight, void* y, int64_t rows,
                                              int64_t hidden, float eps, void* stream);
+
+/* How long the two tensor-parallel kernels above wait for a peer before they give up:
+ * process-wide, read at launch; one second unless set.  No reference counterpart (the
+ * reference's one-shot all-reduce spins without a bound, kernels.py:1146-1148). */
+int32_t b200q_set_wait_limit_ns(int64_t nanoseconds);
 
 #ifdef __cplusplus
 }

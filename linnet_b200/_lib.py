@@ -12,6 +12,7 @@ LIBRARY = Path(__file__).resolve().parent / "libb200q.so"
 
 OK, ERROR, UNAVAILABLE = 0, 1, 2
 F32, BF16, F16 = 0, 1, 2
+EXACT_WEIGHTS, EARLY_DEPENDENTS = 1, 2
 
 # name -> argument types, exactly the prototypes of include/b200q.h
 PROTOTYPES: dict[str, list] = {
@@ -25,6 +26,10 @@ PROTOTYPES: dict[str, list] = {
                           c_int64, c_int32, c_void_p],
     "b200q_int4_gemv": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                         c_int64, c_int32, c_void_p],
+    "b200q_int4_gemv_ex": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                           c_int64, c_int32, c_int32, c_void_p],
+    "b200q_int4_linear_ex": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                             c_int64, c_int32, c_int32, c_void_p],
     "b200q_int4_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                         c_int64, c_int32, c_void_p],
     "b200q_int4_gemm_status": [],
@@ -48,6 +53,8 @@ PROTOTYPES: dict[str, list] = {
     "b200q_decode_attention_static_scratch_limit": [],
     "b200q_decode_attention_static": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                       c_int64, c_int64, c_int64, c_int64, c_void_p],
+    "b200q_decoder_status": [],
+    "b200q_set_wait_limit_ns": [c_int64],
     "b200q_silu_mul": [c_void_p, c_void_p, c_int64, c_int64, c_void_p],
     "b200q_tp_allreduce_add_rmsnorm_flags": [c_void_p, c_void_p, c_int64, c_int64, c_int32, c_int32, c_void_p,
                                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,

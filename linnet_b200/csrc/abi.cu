@@ -2,6 +2,8 @@
 #include "common.cuh"
 
 #include <cstring>
+#include <mutex>
+#include <vector>
 
 namespace b200q {
 
@@ -57,6 +59,47 @@ int sm_count() {
         cached[device] = count;
     }
     return cached[device];
+}
+
+namespace {
+struct KernelState {
+    const void* kernel;
+    int device;
+    size_t smem;  // dynamic shared memory limit set so far
+};
+std::mutex g_kernel_mutex;
+std::vector<KernelState> g_kernel_states;
+
+// The entry of (kernel, current device), created on first use; `fresh` tells which.
+KernelState& kernel_state(const void* kernel, bool* fresh) {
+    int device = 0;
+    cudaGetDevice(&device);
+    for (KernelState& s : g_kernel_states)
+        if (s.kernel == kernel && s.device == device) {
+            *fresh = false;
+            return s;
+        }
+    g_kernel_states.push_back(KernelState{kernel, device, 48 * 1024});
+    *fresh = true;
+    return g_kernel_states.back();
+}
+}  // namespace
+
+cudaError_t ensure_dynamic_smem(const void* kernel, size_t bytes) {
+    std::lock_guard<std::mutex> lock(g_kernel_mutex);
+    bool fresh = false;
+    KernelState& s = kernel_state(kernel, &fresh);
+    if (bytes <= s.smem) return cudaSuccess;
+    const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes));
+    if (err == cudaSuccess) s.smem = bytes;
+    return err;
+}
+
+bool first_use_on_device(const void* kernel) {
+    std::lock_guard<std::mutex> lock(g_kernel_mutex);
+    bool fresh = false;
+    kernel_state(kernel, &fresh);
+    return fresh;
 }
 
 }  // namespace b200q

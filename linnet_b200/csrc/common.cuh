@@ -37,10 +37,26 @@ int32_t check_int4_args(const char* who, const void* x, const uint8_t* packed, c
 // Multiprocessor count of the current device (cached per device).
 int sm_count();
 
+// Function attributes are set once per (kernel, device), not per launch.
+// ensure_dynamic_smem: makes `bytes` of dynamic shared memory launchable for `kernel` on the
+// current device (a runtime call only when the limit set so far is lower).
+// first_use_on_device: true the first time `kernel` is seen on the current device.
+cudaError_t ensure_dynamic_smem(const void* kernel, size_t bytes);
+bool first_use_on_device(const void* kernel);
+
 #define B200Q_REQUIRE(cond, ...)                 \
     do {                                         \
         if (!(cond)) return ::b200q::fail(__VA_ARGS__); \
     } while (0)
+
+// Device-side status of the decode-step kernels: a kernel that finds a position outside its
+// cache records 1 + the batch row in this word (on the current device) and leaves the caches
+// alone; b200q_decoder_status() reports and clears it.  The word lives in decoder_glue.cu;
+// kernels get its device address as an argument.  nullptr if the address cannot be had.
+int* decoder_error_word();
+__device__ __forceinline__ void record_bad_position(int* word, int row) {
+    if (word != nullptr) atomicCAS(word, 0, 1 + row);
+}
 
 // ---- programmatic dependent launch ------------------------------------------
 // A kernel launched with launch_overlapped() may start while the kernel before it in

@@ -60,7 +60,7 @@ attention_partial_kernel(const uint16_t* q, uint16_t* cache_k,  // q and positio
                          uint16_t* cache_v, const int64_t* positions,
                          const float2* __restrict__ rope, float* __restrict__ partial,
                          uint16_t* __restrict__ out_final, int nq, int nkv, int S, int splits, int stages,
-                         float scale_log2) {
+                         float scale_log2, int* status) {
     static_assert(REP <= 8 && (HD == 64 || HD == 128), "heads of a group sit in rows 0..7 of the MMA");
     constexpr int kRowBytes = HD * 2;
     constexpr int kPieces = kRowBytes / 16;          // 16-byte pieces per row
@@ -80,7 +80,12 @@ attention_partial_kernel(const uint16_t* q, uint16_t* cache_k,  // q and positio
     // key and value into its tile and into the cache.
     const bool fused = rope != nullptr;
     const int q_heads = fused ? nq + 2 * nkv : nq;  // heads per row of q
-    const int keys = int(ld_mutable(positions + b)) + 1;  // attend to positions 0 .. pos
+    // A position outside the cache is recorded and clamped: the row's result means nothing,
+    // but no address outside the caches or the table is formed and nothing is stored for it.
+    const int64_t pos_given = ld_mutable(positions + b);
+    const bool bad = pos_given < 0 || pos_given >= S;
+    if (bad && threadIdx.x == 0 && split == 0 && kvh == 0) record_bad_position(status, b);
+    const int keys = int(bad ? 0 : pos_given) + 1;  // attend to positions 0 .. pos
     const int per_split = (keys + splits - 1) / splits;
     const int k0 = split * per_split, k1 = min(k0 + per_split, keys);
     const int chunks = k1 > k0 ? (k1 - k0 + kAttnChunk - 1) / kAttnChunk : 0;
@@ -94,7 +99,9 @@ attention_partial_kernel(const uint16_t* q, uint16_t* cache_k,  // q and positio
             for (int piece = threadIdx.x; piece < 2 * kStage / 16; piece += kThreads) {
                 const int which = piece / (kStage / 16), within = piece % (kStage / 16);
                 const int row = within / kPieces, col = within % kPieces;
-                const int key = min(first + row, k1 - 1);  // the tail repeats the last key
+                // The tail repeats the last key already in the cache: with the fused rotary step
+                // the row of the current position is written by this very launch.
+                const int key = min(first + row, max(k1 - 1 - int(fused && k1 == keys), 0));
                 const uint16_t* src = (which ? cache_v : cache_k) + base + size_t(key) * HD + col * 8;
                 const uint32_t d = dst + which * kStage + row * kRowBytes + ((col ^ (row & 7)) * 16);
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
@@ -165,10 +172,12 @@ attention_partial_kernel(const uint16_t* q, uint16_t* cache_k,  // q and positio
                 *reinterpret_cast<uint16_t*>(tile + kStage + at_lo) = v_lo;
                 *reinterpret_cast<uint16_t*>(tile + kStage + at_hi) = v_hi;
                 const size_t dst = base + size_t(keys - 1) * HD;
-                cache_k[dst + i] = lo;
-                cache_k[dst + i + half] = hi;
-                cache_v[dst + i] = v_lo;
-                cache_v[dst + i + half] = v_hi;
+                if (!bad) {
+                    cache_k[dst + i] = lo;
+                    cache_k[dst + i + half] = hi;
+                    cache_v[dst + i] = v_lo;
+                    cache_v[dst + i + half] = v_hi;
+                }
             }
             __syncthreads();
         }
@@ -351,15 +360,15 @@ int32_t launch_attention(const char* who, const void* q, const void* cache_k, co
     B200Q_REQUIRE((head_dim == 128 || head_dim == 64) && (rep == 1 || rep == 2 || rep == 4 || rep == 8),
                   "%s: head_dim is 64 or 128 and heads / kv_heads is 1, 2, 4 or 8", who);
     B200Q_REQUIRE(q && cache_k && cache_v && positions && out && (scratch || in_cluster) && aligned(q, 16) &&
-                      aligned(cache_k, 16) && aligned(cache_v, 16) && aligned(scratch, 16),
-                  "%s: tensors must be 16-byte aligned", who);
+                      aligned(cache_k, 16) && aligned(cache_v, 16) && aligned(scratch, 16) && aligned(positions, 8),
+                  "%s: tensors must be 16-byte aligned (positions: int64)", who);
+    B200Q_REQUIRE(max_seq > 0 && max_seq < (int64_t(1) << 30), "%s: bad cache length", who);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const dim3 grid{unsigned(splits), unsigned(nkv), unsigned(batch)};
     const float scale_log2 = 1.4426950408889634f / sqrtf(float(head_dim));  // softmax in base 2
 #define B200Q_ATTN_W(HD, REP, WARPS) do {                                                             \
     const int kSmem = kAttnStages * 2 * (16 * WARPS) * HD * 2;                                        \
-    cudaFuncSetAttribute(attention_partial_kernel<HD, REP, WARPS>,                                    \
-                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);                         \
+    ensure_dynamic_smem(reinterpret_cast<const void*>(attention_partial_kernel<HD, REP, WARPS>), kSmem); \
     cudaLaunchConfig_t config = {};                                                                   \
     config.gridDim = grid;                                                                            \
     config.blockDim = dim3(32 * WARPS);                                                               \
@@ -381,7 +390,7 @@ int32_t launch_attention(const char* who, const void* q, const void* cache_k, co
                       static_cast<const float2*>(rope), in_cluster ? static_cast<float*>(nullptr)     \
                                                                    : static_cast<float*>(scratch),    \
                       static_cast<uint16_t*>(out), int(nq), int(nkv), int(max_seq), int(splits),      \
-                      kAttnStages, scale_log2); } while (0)
+                      kAttnStages, scale_log2, decoder_error_word()); } while (0)
 #define B200Q_ATTN(HD, REP) do { if (few_blocks) B200Q_ATTN_W(HD, REP, 8); else B200Q_ATTN_W(HD, REP, 4); } while (0)
     cudaError_t err = cudaSuccess;
     const bool few_blocks = splits * nkv * batch <= sm_count();

@@ -11,7 +11,26 @@
 // PyTorch ops (f32 math on bf16 values, one rounding where PyTorch rounds).
 #include "common.cuh"
 
+static __device__ int g_decoder_error = 0;
+
 namespace b200q {
+
+int* decoder_error_word() {
+    // In host code the symbol is a handle, not an address: ask once per device.
+    static int* cached[64] = {nullptr};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return nullptr;
+    if (cached[device] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_decoder_error) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        cached[device] = static_cast<int*>(p);
+    }
+    return cached[device];
+}
+
 namespace {
 
 // ---- x (+= delta); y = rms_norm(x) * w --------------------------------------------
@@ -96,12 +115,18 @@ add_rmsnorm_kernel(uint16_t* x, const uint16_t* delta,  // read with ld_mutable(
 __global__ void rope_cache_kernel(const uint16_t* qkv, const int64_t* positions,
                                   uint16_t* __restrict__ q_out, uint16_t* __restrict__ cache_k,
                                   uint16_t* __restrict__ cache_v, int nq, int nkv, int hd, int S,
-                                  float theta) {
+                                  float theta, int* status) {
     pdl_wait();
     pdl_launch_dependents();
     const int b = blockIdx.y, head = blockIdx.x;  // head < nq: q; < nq + nkv: k; else v
     const int half = hd / 2;
-    const int64_t pos = ld_mutable(positions + b);
+    int64_t pos = ld_mutable(positions + b);
+    const bool bad = pos < 0 || pos >= S;  // outside the cache: nothing is written for this row
+    if (bad) {
+        if (threadIdx.x == 0 && head == 0) record_bad_position(status, b);
+        if (head >= nq) return;
+        pos = 0;
+    }
     const uint16_t* src = qkv + (size_t(b) * (nq + 2 * nkv) + head) * hd;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         if (head < nq + nkv) {
@@ -173,13 +198,28 @@ extern "C" int32_t b200q_add_rmsnorm(void* x, const void* delta, const void* wei
 extern "C" int32_t b200q_rope_cache(const void* qkv, const int64_t* positions, void* q_out, void* cache_k,
                                     void* cache_v, int64_t batch, int64_t nq, int64_t nkv, int64_t head_dim,
                                     int64_t max_seq, float theta, void* stream) {
-    B200Q_REQUIRE(batch >= 0 && nq > 0 && nkv > 0 && head_dim % 2 == 0, "rope_cache: bad shape");
+    B200Q_REQUIRE(batch >= 0 && nq > 0 && nkv > 0 && head_dim % 2 == 0 && max_seq > 0, "rope_cache: bad shape");
+    B200Q_REQUIRE(batch == 0 || (qkv && positions && q_out && cache_k && cache_v && aligned(positions, 8)),
+                  "rope_cache: null tensor, or positions not int64");
     if (batch == 0) return B200Q_OK;
     return launch_status("rope_cache", launch_overlapped(
         rope_cache_kernel, dim3(unsigned(nq + 2 * nkv), unsigned(batch)), dim3(64), 0,
         static_cast<cudaStream_t>(stream), static_cast<const uint16_t*>(qkv), positions,
         static_cast<uint16_t*>(q_out), static_cast<uint16_t*>(cache_k), static_cast<uint16_t*>(cache_v), int(nq),
-        int(nkv), int(head_dim), int(max_seq), theta));
+        int(nkv), int(head_dim), int(max_seq), theta, decoder_error_word()));
+}
+
+extern "C" int32_t b200q_decoder_status(void) {
+    int flag = 0;
+    cudaError_t err = cudaMemcpyFromSymbol(&flag, g_decoder_error, sizeof(int));
+    if (err != cudaSuccess) return fail("decoder_status: %s", cudaGetErrorString(err));
+    if (flag != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_decoder_error, &zero, sizeof(int));
+        return fail("decode step: the position of batch row %d lies outside its cache; that row's keys and "
+                    "values were not stored", flag - 1);
+    }
+    return B200Q_OK;
 }
 
 extern "C" int32_t b200q_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t inner, void* stream) {

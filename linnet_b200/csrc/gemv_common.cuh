@@ -68,10 +68,8 @@ __device__ __forceinline__ void reduce_and_store(const float (&total)[NT][MB][4]
 template <typename Kernel, typename Args>
 int32_t launch_clustered(const char* who, Kernel kernel, const Args& args, int tiles, int ksplit,
                          int threads, size_t smem, cudaStream_t stream, bool overlap = false) {
-    if (smem > 48 * 1024) {
-        if (smem > 227 * 1024) return fail("%s: %zu bytes of shared memory needed", who, smem);
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    }
+    if (smem > 227 * 1024) return fail("%s: %zu bytes of shared memory needed", who, smem);
+    ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(unsigned(tiles), unsigned(ksplit), 1);
     config.blockDim = dim3(unsigned(threads), 1, 1);

@@ -460,9 +460,6 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
     }
 }
 
-int g_force_bn = 0;      // measurement hook: B200Q_GEMM_BN=128|256 in the environment
-int g_force_splits = 0;  // measurement hook: B200Q_GEMM_SPLITS=1|2|4|8
-
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no libcuda link).
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -502,14 +499,6 @@ extern "C" int32_t b200q_int4_gemm(const void* x, const uint8_t* packed, const v
                   "int4_gemm: needs bf16, inputs and group multiples of %d (got in=%lld group=%lld)", kBK,
                   (long long)in, (long long)group);
     B200Q_REQUIRE(rows < (int64_t(1) << 30), "int4_gemm: too many rows");
-    static const bool env_read = [] {
-        const char* v = getenv("B200Q_GEMM_BN");
-        if (v != nullptr) g_force_bn = atoi(v);
-        v = getenv("B200Q_GEMM_SPLITS");
-        if (v != nullptr) g_force_splits = atoi(v);
-        return true;
-    }();
-    (void)env_read;
     EncodeTiled encode = encode_tiled();
     if (encode == nullptr) return unavailable("int4_gemm: the driver has no cuTensorMapEncodeTiled");
 
@@ -534,13 +523,12 @@ extern "C" int32_t b200q_int4_gemm(const void* x, const uint8_t* packed, const v
     // leave more than half of the multiprocessors idle (every slice keeps >= 2 steps of 64).
     int k_splits = 1;
     const int ksteps = int(in / kBK);
-    if (rows <= kBM && g_force_splits != 1) {
+    if (rows <= kBM) {
         const int64_t n_tiles = (out + 127) / 128;
         while (k_splits < 8 && n_tiles * k_splits * 2 <= sms && ksteps / (k_splits * 2) >= 2) k_splits *= 2;
-        if (g_force_splits > 1) k_splits = g_force_splits;
         while (k_splits > 1 && (k_splits - 1) * ((ksteps + k_splits - 1) / k_splits) >= ksteps) k_splits /= 2;
     }
-    const bool wide = k_splits == 1 && (g_force_bn == 256 || (g_force_bn != 128 && cost256 <= cost128));
+    const bool wide = k_splits == 1 && cost256 <= cost128;
     GemmArgs a{packed, static_cast<const uint16_t*>(scale), zero, static_cast<uint16_t*>(y),
                int(rows), int(in), int(out), int(group), m_tiles, int(wide ? (out + 255) / 256 : (out + 127) / 128),
                k_splits};
@@ -548,7 +536,7 @@ extern "C" int32_t b200q_int4_gemm(const void* x, const uint8_t* packed, const v
     const int grid = k_splits > 1 ? tiles * k_splits : (tiles < sms ? tiles : sms);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (k_splits > 1) {
-        cudaFuncSetAttribute(int4_gemm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(Shape<128>::kSmem));
+        ensure_dynamic_smem(reinterpret_cast<const void*>(int4_gemm_kernel<128>), Shape<128>::kSmem);
         cudaLaunchConfig_t config = {};
         config.gridDim = dim3(unsigned(grid));
         config.blockDim = dim3(kThreads);
@@ -564,10 +552,10 @@ extern "C" int32_t b200q_int4_gemm(const void* x, const uint8_t* packed, const v
         return launch_status("int4_gemm", cudaLaunchKernelEx(&config, int4_gemm_kernel<128>, x_map, a));
     }
     if (wide) {
-        cudaFuncSetAttribute(int4_gemm_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(Shape<256>::kSmem));
+        ensure_dynamic_smem(reinterpret_cast<const void*>(int4_gemm_kernel<256>), Shape<256>::kSmem);
         int4_gemm_kernel<256><<<grid, kThreads, Shape<256>::kSmem, s>>>(x_map, a);
     } else {
-        cudaFuncSetAttribute(int4_gemm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(Shape<128>::kSmem));
+        ensure_dynamic_smem(reinterpret_cast<const void*>(int4_gemm_kernel<128>), Shape<128>::kSmem);
         int4_gemm_kernel<128><<<grid, kThreads, Shape<128>::kSmem, s>>>(x_map, a);
     }
     return launched("int4_gemm");
@@ -577,6 +565,11 @@ extern "C" int32_t b200q_int4_gemm_status(void) {
     int flag = 0;
     const cudaError_t err = cudaMemcpyFromSymbol(&flag, g_gemm_error, sizeof(int));
     if (err != cudaSuccess) return fail("int4_gemm_status: %s", cudaGetErrorString(err));
-    if (flag != 0) return fail("int4_gemm: a bounded wait expired (role %d)", flag);
+    if (flag != 0) {
+        // Reported once: cleared so that later launches wait their full time again.
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int));
+        return fail("int4_gemm: a bounded wait expired (role %d)", flag);
+    }
     return B200Q_OK;
 }

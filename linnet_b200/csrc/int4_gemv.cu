@@ -27,6 +27,7 @@
 
 #include "gemv_common.cuh"
 #include "int4_gemv_oct.cuh"
+#include "int4_gemv_sm.cuh"
 #include "int4_gemv_rows.cuh"
 
 namespace b200q {
@@ -42,6 +43,7 @@ struct GemvArgs {
     int kblocks;            // K / 128
     int kb_per_cta;         // k-blocks each block of a cluster handles
     int ksplit;             // blocks per cluster (along grid.y)
+    int flags;              // B200Q_EXACT_WEIGHTS | B200Q_EARLY_DEPENDENTS
 };
 
 // How the zero point and scale reach the product.
@@ -51,9 +53,7 @@ struct GemvArgs {
 //                scale and zero point travel with the k-block's weight loads.
 //   kExactWord:  groups of 16, 32 or 64: the same arithmetic, the scale looked up per
 //                8 weights.
-//   kPost:       (tuning builds only) zero point and scale applied in f32 after each
-//                k-block's products; cheaper but not the reference's rounding.
-enum { kExactBlock = 0, kExactWord = 1, kPost = 2 };
+enum { kExactBlock = 0, kExactWord = 1 };
 
 // One k-block of one 16-row tile as loaded: 16 bytes of rows g and g+8, and the
 // (scale bits | zero << 16) words of the group the k-block lies in.
@@ -84,12 +84,9 @@ int4_gemv_kernel(const GemvArgs a) {
     const int nw = wb1 - wb0;
 
     // Shared memory, per warp: activations as B fragments [cap][4 words][M][4 lanes] x
-    // 16 B and (kPost) per-k-block activation sums [cap][16] f32; then the block's
-    // reduction buffer.
+    // 16 B; then the block's reduction buffer [W][NT*16][MB*8].
     uint4* xs = reinterpret_cast<uint4*>(smem) + size_t(warp) * cap * 16 * M;
-    float* xsum_all = reinterpret_cast<float*>(reinterpret_cast<uint4*>(smem) + size_t(W) * cap * 16 * M);
-    float* xsum = xsum_all + size_t(warp) * cap * 16;
-    float* red = xsum_all + (MODE == kPost ? size_t(W) * cap * 16 : 0);  // [W][NT*16][MB*8]
+    float* red = reinterpret_cast<float*>(reinterpret_cast<uint4*>(smem) + size_t(W) * cap * 16 * M);
 
     const uint16_t* scale16 = static_cast<const uint16_t*>(a.scale);
     const uint8_t* rowp[NT][2];
@@ -149,28 +146,17 @@ int4_gemv_kernel(const GemvArgs a) {
                     const int j = rem / 16, c = rem % 16;
                     raw[u] = ld_mutable(xg + (size_t(m) * K + size_t(kb0 + wb0 + j) * 128) / 8 + c);
                     where[u] = ((j * 4 + (c % 4)) * M + m) * 4 + c / 4;
-                    if (MODE == kPost && c == 0) where[u] |= (j * 16 + m) << 16;
                 }
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                if (MODE == kPost) {
-                    const uint4 r = raw[u];
-                    float sum = H::to_float(r.x & 0xFFFF) + H::to_float(r.x >> 16);
-                    sum += H::to_float(r.y & 0xFFFF); sum += H::to_float(r.y >> 16);
-                    sum += H::to_float(r.z & 0xFFFF); sum += H::to_float(r.z >> 16);
-                    sum += H::to_float(r.w & 0xFFFF); sum += H::to_float(r.w >> 16);
-#pragma unroll
-                    for (int d = 8; d >= 1; d >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, d);
-                    if (where[u] >= 0 && (lane % 16) == 0) xsum[where[u] >> 16] = sum;
-                }
                 if (where[u] >= 0) {
                     uint4 out;
                     out.x = __byte_perm(raw[u].x, raw[u].z, 0x5410);  // (x0, x4)
                     out.y = __byte_perm(raw[u].x, raw[u].z, 0x7632);  // (x1, x5)
                     out.z = __byte_perm(raw[u].y, raw[u].w, 0x5410);  // (x2, x6)
                     out.w = __byte_perm(raw[u].y, raw[u].w, 0x7632);  // (x3, x7)
-                    xs[where[u] & 0xFFFF] = out;
+                    xs[where[u]] = out;
                 }
             }
         }
@@ -204,19 +190,8 @@ int4_gemv_kernel(const GemvArgs a) {
                         b[mb][i] = m < M ? xs[(size_t(j * 4 + i) * M + m) * 4 + t]
                                          : make_uint4(0, 0, 0, 0);
                 }
-                float2 xs2[MB];
-                if (MODE == kPost) {
-#pragma unroll
-                    for (int mb = 0; mb < MB; ++mb)
-                        xs2[mb] = *reinterpret_cast<const float2*>(xsum + j * 16 + mb * 8 + 2 * t);
-                }
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                    float acc[MB][4];
-#pragma unroll
-                    for (int mb = 0; mb < MB; ++mb)
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) acc[mb][i] = 0.0f;
                     const uint32_t w0[4] = {cur.q[nt][0].x, cur.q[nt][0].y, cur.q[nt][0].z, cur.q[nt][0].w};
                     const uint32_t w1[4] = {cur.q[nt][1].x, cur.q[nt][1].y, cur.q[nt][1].z, cur.q[nt][1].w};
                     uint32_t bias0 = 0, bias1 = 0, sc0 = 0, sc1 = 0;  // 16-bit pairs (x, x)
@@ -244,37 +219,17 @@ int4_gemv_kernel(const GemvArgs a) {
                             bias0 = H::kMagic + uint32_t(__ldg(a.zero + srow[nt][0] + grp)) * 0x00010001u;
                             bias1 = H::kMagic + uint32_t(__ldg(a.zero + srow[nt][1] + grp)) * 0x00010001u;
                         }
-                        if (MODE != kPost) {
 #pragma unroll
-                            for (int p = 0; p < 4; ++p) {
-                                f0[p] = sub_mul<T>(f0[p], bias0, sc0);
-                                f1[p] = sub_mul<T>(f1[p], bias1, sc1);
-                            }
+                        for (int p = 0; p < 4; ++p) {
+                            f0[p] = sub_mul<T>(f0[p], bias0, sc0);
+                            f1[p] = sub_mul<T>(f1[p], bias1, sc1);
                         }
                         const uint32_t a_lo[4] = {f0[0], f1[0], f0[1], f1[1]};
                         const uint32_t a_hi[4] = {f0[2], f1[2], f0[3], f1[3]};
 #pragma unroll
                         for (int mb = 0; mb < MB; ++mb) {
-                            if (MODE == kPost) {
-                                H::mma(acc[mb], a_lo, b[mb][i].x, b[mb][i].y);
-                                H::mma(acc[mb], a_hi, b[mb][i].z, b[mb][i].w);
-                            } else {
-                                H::mma(total[nt][mb], a_lo, b[mb][i].x, b[mb][i].y);
-                                H::mma(total[nt][mb], a_hi, b[mb][i].z, b[mb][i].w);
-                            }
-                        }
-                    }
-                    if (MODE == kPost) {
-                        const float s0 = H::to_float(cur.sz[nt][0] & 0xFFFF);
-                        const float s1 = H::to_float(cur.sz[nt][1] & 0xFFFF);
-                        const float z0 = H::kBias + float(cur.sz[nt][0] >> 16);
-                        const float z1 = H::kBias + float(cur.sz[nt][1] >> 16);
-#pragma unroll
-                        for (int mb = 0; mb < MB; ++mb) {
-                            total[nt][mb][0] = fmaf(s0, fmaf(-z0, xs2[mb].x, acc[mb][0]), total[nt][mb][0]);
-                            total[nt][mb][1] = fmaf(s0, fmaf(-z0, xs2[mb].y, acc[mb][1]), total[nt][mb][1]);
-                            total[nt][mb][2] = fmaf(s1, fmaf(-z1, xs2[mb].x, acc[mb][2]), total[nt][mb][2]);
-                            total[nt][mb][3] = fmaf(s1, fmaf(-z1, xs2[mb].y, acc[mb][3]), total[nt][mb][3]);
+                            H::mma(total[nt][mb], a_lo, b[mb][i].x, b[mb][i].y);
+                            H::mma(total[nt][mb], a_hi, b[mb][i].z, b[mb][i].w);
                         }
                     }
                 }
@@ -349,8 +304,7 @@ int32_t launch_gemv(const GemvArgs& args, int ksplit, cudaStream_t stream) {
     a.kb_per_cta = (a.kblocks + ksplit - 1) / ksplit;
     const int tiles = (a.N + 16 * NT - 1) / (16 * NT);
     const size_t cap = (a.kb_per_cta + W - 1) / W;  // k-blocks per warp, at most
-    const size_t smem = size_t(W) * cap * 16 * a.M * 16 + (MODE == kPost ? size_t(W) * cap * 16 * 4 : 0) +
-                        size_t(W) * NT * 16 * MB * 8 * 4;
+    const size_t smem = size_t(W) * cap * 16 * a.M * 16 + size_t(W) * NT * 16 * MB * 8 * 4;
     return launch_clustered("int4_gemv", int4_gemv_kernel<T, MODE, MB, NT, W, D>, a, tiles, ksplit,
                             W * 32, smem, stream, true);
 }
@@ -403,9 +357,6 @@ bool run_rows(const GemvArgs& a, cudaStream_t stream, int32_t* status) {
     return true;
 }
 
-// Set by b200q_int4_gemv: this call reads the activations of the previous call of this thread.
-thread_local bool g_same_activations = false;
-
 // The short-run variants (KB = 4 or 2 k-blocks per warp) for up to 8 rows: the most warps
 // per block (of 8, 4, 7, 2, 1) that divide the runs along K with at most 8 blocks per cluster.
 template <typename T, int KB>
@@ -413,8 +364,8 @@ bool run_short(OctArgs o, int G, cudaStream_t stream, int32_t* status) {
     const bool deep = o.M <= 2;  // every weight load of the kernel issued up front (cp.async)
 #define B200Q_SHORT(W)                                                                       \
     if (oct_plan(o.K, G, W, o.scale, o.zero, &o.ksplit, KB)) {                               \
-        *status = deep ? launch_oct<T, 1, 1, W, 0, false, KB>(o, stream)                     \
-                       : launch_oct<T, 1, 1, W, 2, false, KB>(o, stream);                    \
+        *status = deep ? launch_oct<T, 1, 1, W, 0, KB>(o, stream)                            \
+                       : launch_oct<T, 1, 1, W, 2, KB>(o, stream);                           \
         return true;                                                                         \
     }
     B200Q_SHORT(8)
@@ -432,7 +383,8 @@ template <typename T>
 bool run_oct(const GemvArgs& a, cudaStream_t stream, int32_t* status) {
     // Every variant is launched with programmatic stream serialization: its weight
     // prefetch overlaps the tail of the kernel before it.
-    OctArgs o{a.x, a.packed, a.scale, a.zero, a.y, a.M, a.K, a.N, 1, 1};
+    OctArgs o{a.x, a.packed, a.scale, a.zero, a.y, a.M, a.K, a.N, 1, 1,
+              (a.flags & B200Q_EARLY_DEPENDENTS) ? 1 : 0};
     const bool few = a.M <= 8;
     if (few && a.G == 128) {
         // A warp's run through 8 k-blocks takes ~2.7 us however little else the GPU has to
@@ -453,17 +405,11 @@ bool run_oct(const GemvArgs& a, cudaStream_t stream, int32_t* status) {
         if (kb == 2 && a.K % 256 == 0 && run_short<T, 2>(o, a.G, stream, status)) return true;
     }
     if (oct_plan(a.K, a.G, 4, a.scale, a.zero, &o.ksplit)) {
-        // A product that reads the same activations as the one launched before it on this
-        // host thread is part of a fan-out (q, k and v of one input; gate and up; a chain of
-        // products in a benchmark): let the next kernel start early (see EARLY).
-        const bool early = g_same_activations;
         if (a.M <= 2) {
             // One or two rows: every weight load of the kernel is issued up front (cp.async).
-            *status = early ? launch_oct<T, 1, 1, 4, 0, false, 8, true>(o, stream)
-                            : launch_oct<T, 1, 1, 4, 0>(o, stream);
+            *status = launch_oct<T, 1, 1, 4, 0>(o, stream);
         } else if (few) {
-            *status = early ? launch_oct<T, 1, 1, 4, 2, false, 8, true>(o, stream)
-                            : launch_oct<T, 1, 1, 4, 2>(o, stream);
+            *status = launch_oct<T, 1, 1, 4, 2>(o, stream);
         } else {
             *status = launch_oct<T, 2, 1, 4, 2>(o, stream);
         }
@@ -477,6 +423,39 @@ bool run_oct(const GemvArgs& a, cudaStream_t stream, int32_t* status) {
         return false;
     }
     return true;
+}
+
+// The one-block-per-multiprocessor kernel (int4_gemv_sm.cuh) for group 128 and up to 16 rows:
+// the default with post-scaled sums, and with B200Q_EXACT_WEIGHTS where it takes the shape.
+// The ring is as deep as the staged activations (2 KB per row and 1024 inputs) leave room for.
+template <typename T, bool EXACT>
+bool run_sm(const GemvArgs& a, cudaStream_t stream, int32_t* status) {
+    if (a.G != 128 || a.M > 16 || size_t(a.N) * size_t(a.K / 2) >= (size_t(1) << 40)) return false;
+    const int sms = sm_count();
+    SmArgs p{a.x, a.packed, a.scale, a.zero, a.y, a.M, a.K, a.N, (a.N + 15) / 16, 1, 1, 1, 1,
+             (a.flags & B200Q_EARLY_DEPENDENTS) ? 1 : 0};
+    size_t smem = 0;
+#define B200Q_SM(MB, KB, R)                                                       \
+    if (sm_plan<MB, 28, KB, R>(p, a.G, sms, &smem)) {                             \
+        *status = launch_sm<T, MB, 28, KB, R, EXACT>(p, smem, sms, stream);       \
+        return true;                                                              \
+    }
+    if (a.M <= 8) {
+        B200Q_SM(1, 8, 7)
+        B200Q_SM(1, 8, 6)
+        B200Q_SM(1, 8, 5)
+        B200Q_SM(1, 8, 4)
+        B200Q_SM(1, 8, 3)
+        B200Q_SM(1, 4, 4)
+        B200Q_SM(1, 4, 3)
+    } else {
+        B200Q_SM(2, 8, 3)
+        B200Q_SM(2, 8, 2)
+        B200Q_SM(2, 4, 3)
+        B200Q_SM(2, 4, 2)
+    }
+#undef B200Q_SM
+    return false;
 }
 
 template <typename T>
@@ -506,7 +485,9 @@ int32_t run_gemv(GemvArgs a, int64_t rows, cudaStream_t stream) {
             step = 16;
             a.M = 16;
         }
-        if (a.M >= 9 && run_rows<T, 2>(a, stream, &status)) {
+        if (!(a.flags & B200Q_EXACT_WEIGHTS) && run_sm<T, false>(a, stream, &status)) {
+            // post-scaled sums: the default
+        } else if (a.M >= 9 && run_rows<T, 2>(a, stream, &status)) {
             // 9..16 rows: activations staged once per block (15.7 us against 21.7 us at 16
             // rows, K=4096, N=14336; up to 8 rows the per-lane loads are as fast or faster)
         } else if (run_oct<T>(a, stream, &status)) {
@@ -525,78 +506,6 @@ int32_t run_gemv(GemvArgs a, int64_t rows, cudaStream_t stream) {
     }
     return B200Q_OK;
 }
-
-#ifdef B200Q_TUNING
-// Sweep hook (only in tuning builds): runs one named instantiation.
-#define B200Q_VARIANT(id, MB, NT, W, D)                                                   \
-    case id: return launch_gemv<__nv_bfloat16, kExactBlock, MB, NT, W, D>(a, ksplit, stream); \
-    case 100 + id: return launch_gemv<__nv_bfloat16, kPost, MB, NT, W, D>(a, ksplit, stream);
-int32_t tune_gemv(const GemvArgs& a, int variant, int ksplit, cudaStream_t stream) {
-    switch (variant & 0xFFF) {
-        B200Q_VARIANT(0, 1, 1, 4, 3)
-        B200Q_VARIANT(1, 1, 1, 4, 2)
-        B200Q_VARIANT(2, 1, 1, 4, 4)
-        B200Q_VARIANT(3, 1, 1, 4, 6)
-        B200Q_VARIANT(4, 1, 1, 2, 4)
-        B200Q_VARIANT(5, 1, 1, 8, 2)
-        B200Q_VARIANT(6, 1, 1, 8, 4)
-        B200Q_VARIANT(7, 1, 2, 4, 2)
-        B200Q_VARIANT(8, 1, 2, 4, 3)
-        B200Q_VARIANT(9, 1, 2, 8, 2)
-        B200Q_VARIANT(10, 1, 1, 16, 2)
-        B200Q_VARIANT(11, 1, 4, 4, 2)
-        B200Q_VARIANT(20, 2, 1, 4, 2)
-        B200Q_VARIANT(21, 2, 1, 4, 3)
-        B200Q_VARIANT(22, 2, 2, 4, 2)
-        B200Q_VARIANT(23, 2, 2, 8, 2)
-        B200Q_VARIANT(24, 2, 1, 8, 2)
-        B200Q_VARIANT(25, 2, 4, 4, 1)
-        B200Q_VARIANT(26, 2, 2, 4, 1)
-        B200Q_VARIANT(27, 2, 1, 8, 4)
-    }
-    // 200 + ...: the specialised g128 kernel; bit 0x1000 of `variant` asks for
-    // programmatic dependent launch.
-    if ((variant & 0xFFF) >= 400) {
-        const int octs = a.K / 1024;
-        int opc = 1;
-        while (octs % opc != 0 || octs / opc > 8) ++opc;
-        RowsArgs r{a.x, a.packed, a.scale, a.zero, a.y, a.M, a.K, a.N, (a.N + 15) / 16, opc, octs / opc};
-        switch (variant & 0xFFF) {
-            case 400: return launch_rows<__nv_bfloat16, 1, 4, 2>(r, stream);
-            case 401: return launch_rows<__nv_bfloat16, 1, 7, 2>(r, stream);
-            case 402: return launch_rows<__nv_bfloat16, 1, 14, 2>(r, stream);
-            case 403: return launch_rows<__nv_bfloat16, 1, 2, 2>(r, stream);
-            case 404: return launch_rows<__nv_bfloat16, 1, 4, 4>(r, stream);
-            case 405: return launch_rows<__nv_bfloat16, 1, 7, 4>(r, stream);
-            case 420: return launch_rows<__nv_bfloat16, 2, 4, 2>(r, stream);
-            case 421: return launch_rows<__nv_bfloat16, 2, 7, 2>(r, stream);
-            case 422: return launch_rows<__nv_bfloat16, 2, 14, 2>(r, stream);
-            case 423: return launch_rows<__nv_bfloat16, 2, 2, 2>(r, stream);
-            case 424: return launch_rows<__nv_bfloat16, 2, 7, 4>(r, stream);
-        }
-        return fail("no such variant");
-    }
-    OctArgs o{a.x, a.packed, a.scale, a.zero, a.y, a.M, a.K, a.N, 1, (variant & 0x1000) ? 1 : 0};
-#define B200Q_OCT(id, MB, NT, W, D)                                                      \
-    case id:                                                                             \
-        if (!oct_plan(a.K, a.G, W, a.scale, a.zero, &o.ksplit)) return fail("oct: shape"); \
-        return launch_oct<__nv_bfloat16, MB, NT, W, D, false>(o, stream);                \
-    case 100 + id:                                                                       \
-        if (!oct_plan(a.K, a.G, W, a.scale, a.zero, &o.ksplit)) return fail("oct: shape"); \
-        return launch_oct<__nv_bfloat16, MB, NT, W, D, true>(o, stream);
-    switch (variant & 0xFFF) {
-        B200Q_OCT(200, 1, 1, 4, 2)
-        B200Q_OCT(201, 1, 1, 4, 0)
-        B200Q_OCT(203, 1, 2, 4, 2)
-        B200Q_OCT(210, 1, 1, 7, 2)
-        B200Q_OCT(211, 1, 1, 7, 0)
-        B200Q_OCT(220, 2, 1, 4, 2)
-        B200Q_OCT(221, 2, 2, 4, 2)
-        B200Q_OCT(222, 2, 1, 4, 0)
-    }
-    return fail("no such variant");
-}
-#endif
 
 }  // namespace
 
@@ -621,25 +530,20 @@ int32_t check_int4_args(const char* who, const void* x, const uint8_t* packed, c
 
 using namespace b200q;
 
-extern "C" int32_t b200q_int4_gemv(const void* x, const uint8_t* packed, const void* scale,
-                                   const uint8_t* zero, void* y, int64_t rows, int64_t in,
-                                   int64_t out, int64_t group, int32_t dtype, void* stream) {
+extern "C" int32_t b200q_int4_gemv_ex(const void* x, const uint8_t* packed, const void* scale,
+                                      const uint8_t* zero, void* y, int64_t rows, int64_t in,
+                                      int64_t out, int64_t group, int32_t dtype, int32_t flags,
+                                      void* stream) {
     const int32_t ok = check_int4_args("int4_gemv", x, packed, scale, zero, y, rows, in, out, group, dtype);
     if (ok != B200Q_OK || rows == 0) return ok;
-    GemvArgs a{x, packed, scale, zero, y, 0, int(in), int(out), int(group), int(in / 128), 0, 1};
+    B200Q_REQUIRE((flags & ~(B200Q_EXACT_WEIGHTS | B200Q_EARLY_DEPENDENTS)) == 0, "int4_gemv: unknown flag bits %d", flags);
+    GemvArgs a{x, packed, scale, zero, y, 0, int(in), int(out), int(group), int(in / 128), 0, 1, flags};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    static thread_local const void* last_x = nullptr;
-    g_same_activations = x == last_x;
-    last_x = x;
     return dtype == B200Q_BF16 ? run_gemv<__nv_bfloat16>(a, rows, s) : run_gemv<__half>(a, rows, s);
 }
 
-#ifdef B200Q_TUNING
-extern "C" int32_t b200q_tune_int4_gemv(const void* x, const uint8_t* packed, const void* scale,
-                                        const uint8_t* zero, void* y, int64_t rows, int64_t in,
-                                        int64_t out, int64_t group, int32_t variant, int32_t ksplit,
-                                        void* stream) {
-    GemvArgs a{x, packed, scale, zero, y, int(rows), int(in), int(out), int(group), int(in / 128), 0, 1};
-    return tune_gemv(a, variant, ksplit, static_cast<cudaStream_t>(stream));
+extern "C" int32_t b200q_int4_gemv(const void* x, const uint8_t* packed, const void* scale,
+                                   const uint8_t* zero, void* y, int64_t rows, int64_t in,
+                                   int64_t out, int64_t group, int32_t dtype, void* stream) {
+    return b200q_int4_gemv_ex(x, packed, scale, zero, y, rows, in, out, group, dtype, 0, stream);
 }
-#endif

@@ -17,6 +17,7 @@
 // Dequantization is the reference's arithmetic exactly: (magic + q) - (magic + zero)
 // is the integer q - zero, and one multiply by the scale rounds once to the 16-bit
 // type.  Per k-block and 16-row tile that is 56 LOP3/SHF + 64 HSUB2/HMUL2 + 8 MMA.
+// This is the kernel behind B200Q_EXACT_WEIGHTS; int4_gemv_post.cuh is the default.
 #pragma once
 
 #include "gemv_common.cuh"
@@ -32,11 +33,9 @@ struct OctArgs {
     int M, K, N;
     int ksplit;             // blocks per cluster; K == 128 * KB * W * ksplit
     int overlap;            // launched with programmatic stream serialization
+    int early;              // dependents may start as soon as this kernel has started
 };
 
-// w >> S.  With B200Q_SHIFT_BY_MULHI it is computed as the high half of w * 2^(32-S),
-// an integer multiply that runs on the FMA pipe, to take load off the ALU pipe the
-// LOP3s and PRMTs of the dequantization already fill.
 // Waits until at most `pending` of this thread's cp.async groups are in flight
 // (`pending` is a constant once the caller's loop is unrolled).
 __device__ __forceinline__ void cp_async_wait(int pending) {
@@ -51,28 +50,12 @@ __device__ __forceinline__ void cp_async_wait(int pending) {
     }
 }
 
-template <int S>
-__device__ __forceinline__ uint32_t shr(uint32_t w) {
-#ifdef B200Q_SHIFT_BY_MULHI
-    uint32_t r;
-    asm("mul.hi.u32 %0, %1, %2;" : "=r"(r) : "r"(w), "r"(1u << (32 - S)));
-    return r;
-#else
-    return w >> S;
-#endif
-}
-
 // D > 0: a D-deep register pipeline of weight loads.  D == 0 ("deep", NT == 1): the
 // first k-block is loaded into registers and the other seven are requested at once
 // with cp.async into lane-private shared-memory slots (each lane later reads back
 // exactly the 16-byte pieces it asked for, so a wait_group is all the synchronisation
 // needed): the whole weight matrix is in flight from the first cycles of the kernel
 // and the arithmetic never waits on a load it has not long since issued.
-// FAST: zero point and scale are applied in f32 to each k-block's sums,
-//     y += scale * (sum_k x_k (magic + q_k) - (magic + zero) * sum_k x_k),
-// (sum_k x_k comes from a product with a fragment of ones) instead of dequantizing
-// every weight; cheaper, and closer to exact arithmetic, but not the reference's
-// rounding of each weight to the 16-bit type.
 // KB: k-blocks per warp (8 = an oct; 4 or 2 for small problems, where a warp's serial run
 // through 8 k-blocks -- 1,500 instructions, ~2.7 us -- is the whole kernel time and most
 // multiprocessors hold only a few warps: shorter runs, proportionally more warps).
@@ -81,13 +64,14 @@ __device__ __forceinline__ uint32_t shr(uint32_t w) {
 // programmatically inside a CUDA graph, kernels do not get that cache invalidated between
 // them, and a decode step that reuses an address for a new activation tensor was served the
 // old tensor's lines (found by replaying a captured step against its eager result).
-// EARLY: when the kernels that depend on this one may start (programmatic dependent launch).
-//   false: after the last k-block.  Inside a decode step this is the faster order: a
+// OctArgs::early: when the kernels that depend on this one may start (programmatic dependent
+// launch).
+//   0: after the last k-block.  Inside a decode step this is the faster order: a
 //     dependent that starts early (the attention kernel with its 96-192 KB of shared memory,
 //     say) only takes shared memory and warp slots from this kernel while it waits.
-//   true: at once, so that a following product overlaps its weight prefetch with this
+//   1: at once, so that a following product overlaps its weight prefetch with this
 //     kernel's arithmetic (1.4 us per launch in a chain of products on the headline shape).
-template <typename T, int MB, int NT, int W, int D, bool FAST, int KB = 8, bool EARLY = false>
+template <typename T, int MB, int NT, int W, int D, int KB = 8>
 __global__ void __launch_bounds__(W * 32, ((NT == 1 ? 28 : 20) / W) > 0 ? (NT == 1 ? 28 : 20) / W : 1)
 int4_gemv_oct_kernel(const OctArgs a) {
     static_assert(D > 0 || NT == 1, "the deep variant handles one tile per warp");
@@ -168,7 +152,7 @@ int4_gemv_oct_kernel(const OctArgs a) {
             }
         }
     if (a.overlap) {
-        if (EARLY) pdl_launch_dependents();
+        if (a.early) pdl_launch_dependents();
         pdl_wait();  // activations may come from the kernel before this one
     }
 
@@ -212,15 +196,6 @@ int4_gemv_oct_kernel(const OctArgs a) {
             q[0][0] = slots[((j - 1) * 2 + 0) * 32];
             q[0][1] = slots[((j - 1) * 2 + 1) * 32];
         }
-        float kacc[NT][MB][4], xacc[MB][4];  // FAST: this k-block's sums
-#pragma unroll
-        for (int mb = 0; mb < MB; ++mb)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                xacc[mb][e] = 0.0f;
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) kacc[nt][mb][e] = 0.0f;
-            }
         // (scale, scale) and (magic + zero, magic + zero) of rows g and g+8, k-block j.
         uint32_t sc[NT][2], bias[NT][2];
         // bytes [zero, high byte of magic, zero, high byte of magic]
@@ -239,11 +214,7 @@ int4_gemv_oct_kernel(const OctArgs a) {
             uint4 b[MB];  // (x0,x4) (x1,x5) (x2,x6) (x3,x7) of this lane's 8 inputs
 #pragma unroll
             for (int mb = 0; mb < MB; ++mb) {
-#ifndef B200Q_KO_X
                 const uint4 raw = ld_activation_free(xp[mb] + j * 16 + i);
-#else
-                const uint4 raw = make_uint4(lane, j, i, mb);
-#endif
                 b[mb].x = __byte_perm(raw.x, raw.z, 0x5410);
                 b[mb].y = __byte_perm(raw.x, raw.z, 0x7632);
                 b[mb].z = __byte_perm(raw.y, raw.w, 0x5410);
@@ -254,77 +225,31 @@ int4_gemv_oct_kernel(const OctArgs a) {
                 const uint32_t w0 = i == 0 ? q[nt][0].x : i == 1 ? q[nt][0].y : i == 2 ? q[nt][0].z : q[nt][0].w;
                 const uint32_t w1 = i == 0 ? q[nt][1].x : i == 1 ? q[nt][1].y : i == 2 ? q[nt][1].z : q[nt][1].w;
                 uint32_t f0[4], f1[4];  // (k0,k4) (k1,k5) (k2,k6) (k3,k7) of rows g, g+8
-#ifdef B200Q_KO_DEQUANT
-                f0[0] = f0[1] = f0[2] = f0[3] = w0;
-                f1[0] = f1[1] = f1[2] = f1[3] = w1;
-                if (false) {
-#else
-                {
-#endif
                 f0[0] = lop3_and_or(w0, kMask, H::kMagic);
-                f0[1] = lop3_and_or(shr<4>(w0), kMask, H::kMagic);
-                f0[2] = lop3_and_or(shr<8>(w0), kMask, H::kMagic);
-                f0[3] = lop3_and_or(shr<12>(w0), kMask, H::kMagic);
+                f0[1] = lop3_and_or(w0 >> 4, kMask, H::kMagic);
+                f0[2] = lop3_and_or(w0 >> 8, kMask, H::kMagic);
+                f0[3] = lop3_and_or(w0 >> 12, kMask, H::kMagic);
                 f1[0] = lop3_and_or(w1, kMask, H::kMagic);
-                f1[1] = lop3_and_or(shr<4>(w1), kMask, H::kMagic);
-                f1[2] = lop3_and_or(shr<8>(w1), kMask, H::kMagic);
-                f1[3] = lop3_and_or(shr<12>(w1), kMask, H::kMagic);
-                if (!FAST) {
+                f1[1] = lop3_and_or(w1 >> 4, kMask, H::kMagic);
+                f1[2] = lop3_and_or(w1 >> 8, kMask, H::kMagic);
+                f1[3] = lop3_and_or(w1 >> 12, kMask, H::kMagic);
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        f0[e] = sub_mul<T>(f0[e], bias[nt][0], sc[nt][0]);
-                        f1[e] = sub_mul<T>(f1[e], bias[nt][1], sc[nt][1]);
-                    }
-                }
+                for (int e = 0; e < 4; ++e) {
+                    f0[e] = sub_mul<T>(f0[e], bias[nt][0], sc[nt][0]);
+                    f1[e] = sub_mul<T>(f1[e], bias[nt][1], sc[nt][1]);
                 }
                 const uint32_t a_lo[4] = {f0[0], f1[0], f0[1], f1[1]};
                 const uint32_t a_hi[4] = {f0[2], f1[2], f0[3], f1[3]};
 #pragma unroll
                 for (int mb = 0; mb < MB; ++mb) {
-                    if (FAST) {
-                        H::mma(kacc[nt][mb], a_lo, b[mb].x, b[mb].y);
-                        H::mma(kacc[nt][mb], a_hi, b[mb].z, b[mb].w);
-                    } else {
-#ifdef B200Q_KO_MMA
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            acc[nt][mb][0][e] = __uint_as_float(__float_as_uint(acc[nt][mb][0][e]) ^ a_lo[e] ^ b[mb].x ^ b[mb].y);
-                            acc[nt][mb][1][e] = __uint_as_float(__float_as_uint(acc[nt][mb][1][e]) ^ a_hi[e] ^ b[mb].z ^ b[mb].w);
-                        }
-#else
-                        H::mma(acc[nt][mb][0], a_lo, b[mb].x, b[mb].y);
-                        H::mma(acc[nt][mb][1], a_hi, b[mb].z, b[mb].w);
-#endif
-                    }
-                }
-            }
-            if (FAST) {
-                const uint32_t ones[4] = {H::kOnes, H::kOnes, H::kOnes, H::kOnes};
-#pragma unroll
-                for (int mb = 0; mb < MB; ++mb) {
-                    H::mma(xacc[mb], ones, b[mb].x, b[mb].y);
-                    H::mma(xacc[mb], ones, b[mb].z, b[mb].w);
-                }
-            }
-        }
-        if (FAST) {
-            // y += scale * (sums - (magic + zero) * sum of activations), rows g and g+8.
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                const float s0 = H::to_float(sc[nt][0] & 0xFFFFu), s1 = H::to_float(sc[nt][1] & 0xFFFFu);
-                const float z0 = H::to_float(bias[nt][0] & 0xFFFFu), z1 = H::to_float(bias[nt][1] & 0xFFFFu);
-#pragma unroll
-                for (int mb = 0; mb < MB; ++mb) {
-                    acc[nt][mb][0][0] = fmaf(s0, fmaf(-z0, xacc[mb][0], kacc[nt][mb][0]), acc[nt][mb][0][0]);
-                    acc[nt][mb][0][1] = fmaf(s0, fmaf(-z0, xacc[mb][1], kacc[nt][mb][1]), acc[nt][mb][0][1]);
-                    acc[nt][mb][0][2] = fmaf(s1, fmaf(-z1, xacc[mb][2], kacc[nt][mb][2]), acc[nt][mb][0][2]);
-                    acc[nt][mb][0][3] = fmaf(s1, fmaf(-z1, xacc[mb][3], kacc[nt][mb][3]), acc[nt][mb][0][3]);
+                    H::mma(acc[nt][mb][0], a_lo, b[mb].x, b[mb].y);
+                    H::mma(acc[nt][mb][1], a_hi, b[mb].z, b[mb].w);
                 }
             }
         }
     }
 
-    if (a.overlap && !EARLY) pdl_launch_dependents();
+    if (a.overlap && !a.early) pdl_launch_dependents();
     // 4. Sum the two accumulator sets, the warps, the cluster; write y.
     float total[NT][MB][4];
 #pragma unroll
@@ -347,12 +272,13 @@ inline bool oct_plan(int K, int G, int W, const void* scale, const uint8_t* zero
     return true;
 }
 
-template <typename T, int MB, int NT, int W, int D, bool FAST = false, int KB = 8, bool EARLY = false>
+template <typename T, int MB, int NT, int W, int D, int KB = 8>
 int32_t launch_oct(const OctArgs& args, cudaStream_t stream) {
     const int tiles = (args.N + 16 * NT - 1) / (16 * NT);
     const size_t smem = size_t(W) * NT * 16 * MB * 8 * 4 + (D == 0 ? size_t(W) * (KB - 1) * 2 * 32 * 16 : 0);
-    auto kernel = int4_gemv_oct_kernel<T, MB, NT, W, D, FAST, KB, EARLY>;
-    if (D == 0)  // 7 blocks of 30 KB per multiprocessor need the largest carve-out
+    auto kernel = int4_gemv_oct_kernel<T, MB, NT, W, D, KB>;
+    if (D == 0 && first_use_on_device(reinterpret_cast<const void*>(kernel)))
+        // 7 blocks of 30 KB per multiprocessor need the largest carve-out
         cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                              cudaSharedmemCarveoutMaxShared);
     return launch_clustered("int4_gemv", kernel, args, tiles, args.ksplit, W * 32, smem, stream,

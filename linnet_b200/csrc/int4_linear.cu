@@ -1,8 +1,6 @@
 // Row-count dispatch of the int4 linear layer, the counterpart of the generated
 // `_int4_linear` (src/backend/torch_source.cpp:1553-1570): few rows stream the
 // weight once through the decode kernel, many rows go to the tcgen05 dequant-GEMM.
-#include <cstdlib>
-
 #include "common.cuh"
 
 namespace b200q {
@@ -19,18 +17,17 @@ using namespace b200q;
 // pass (98 us) loses to it.
 static constexpr int64_t kGemmRows = 33;
 
-static int64_t gemm_rows() {  // measurement hook: B200Q_GEMM_ROWS in the environment
-    static const int64_t rows = [] {
-        const char* v = getenv("B200Q_GEMM_ROWS");
-        return v != nullptr && atoll(v) > 0 ? int64_t(atoll(v)) : kGemmRows;
-    }();
-    return rows;
+extern "C" int32_t b200q_int4_linear_ex(const void* x, const uint8_t* packed, const void* scale,
+                                        const uint8_t* zero, void* y, int64_t rows, int64_t in,
+                                        int64_t out, int64_t group, int32_t dtype, int32_t flags,
+                                        void* stream) {
+    if (rows >= kGemmRows && int4_gemm_supports(rows, in, out, group, dtype, x, y))
+        return b200q_int4_gemm(x, packed, scale, zero, y, rows, in, out, group, dtype, stream);
+    return b200q_int4_gemv_ex(x, packed, scale, zero, y, rows, in, out, group, dtype, flags, stream);
 }
 
 extern "C" int32_t b200q_int4_linear(const void* x, const uint8_t* packed, const void* scale,
                                      const uint8_t* zero, void* y, int64_t rows, int64_t in,
                                      int64_t out, int64_t group, int32_t dtype, void* stream) {
-    if (rows >= gemm_rows() && int4_gemm_supports(rows, in, out, group, dtype, x, y))
-        return b200q_int4_gemm(x, packed, scale, zero, y, rows, in, out, group, dtype, stream);
-    return b200q_int4_gemv(x, packed, scale, zero, y, rows, in, out, group, dtype, stream);
+    return b200q_int4_linear_ex(x, packed, scale, zero, y, rows, in, out, group, dtype, 0, stream);
 }

@@ -13,8 +13,10 @@
 //   1. every rank has a receive area per call site, [source rank][rows][hidden / 2] words
 //      of 8 bytes: two bf16 values and the site's 32-bit epoch.  One block per row reads
 //      this rank's partial sums and stores them, word by word with the epoch attached,
-//      into its slot of every peer's area (16-byte stores of two words; an aligned 8-byte
-//      word arrives whole, so a word whose epoch matches carries this call's values);
+//      into its slot of every peer's area.  A word is ONE 64-bit element of the store and of
+//      the polling load (st/ld.relaxed.sys.v2.b64): the memory model makes each element of a
+//      vector access single-copy atomic, so a word whose epoch matches carries this call's
+//      values (with 32-bit elements an epoch could be seen before the value beside it);
 //   2. the block then reads the words the peers stored into its own area, polling (with a
 //      bound) each until its epoch matches, adds the rows in rank order (the same order on
 //      every rank, so all ranks get the same bits), rounds the sum to bf16 as an all-reduce
@@ -27,12 +29,13 @@
 // passed the NEXT site, i.e. after it finished reading this one (the caller alternates at
 // least two sites).  Epochs live in device memory and advance once per call (the last
 // block to finish bumps the site's counter), so the kernel replays inside a CUDA graph.  A
-// poll that runs out (about a second) records an error code and lets the kernel finish
+// poll that runs out (a second unless b200q_set_wait_limit_ns says otherwise) records an error code and lets the kernel finish
 // with whatever it has; the context stays usable, and later calls skip their polls until
 // the host clears the code.
 #include "common.cuh"
 
 namespace b200q {
+uint64_t tp_wait_limit_ns();
 namespace {
 
 constexpr int kMaxRanks = 8;
@@ -48,12 +51,20 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
     __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&p);
 }
-__device__ __forceinline__ uint4 ld_words(const uint4* p) {  // two words, straight from L2
-    uint4 v;
-    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
+// Two words of (values, epoch), each one 64-bit element: values in the low half.
+struct Words2 {
+    uint64_t a, b;
+};
+__device__ __forceinline__ Words2 ld_words(const void* p) {
+    Words2 v;
+    asm volatile("ld.relaxed.sys.global.v2.b64 {%0,%1}, [%2];" : "=l"(v.a), "=l"(v.b) : "l"(p) : "memory");
     return v;
+}
+__device__ __forceinline__ void st_words(void* p, uint64_t a, uint64_t b) {
+    asm volatile("st.relaxed.sys.global.v2.b64 [%0], {%1,%2};" ::"l"(p), "l"(a), "l"(b) : "memory");
+}
+__device__ __forceinline__ uint64_t tagged(uint32_t values, uint32_t epoch) {
+    return uint64_t(values) | (uint64_t(epoch) << 32);
 }
 
 // One 16-byte piece (8 bf16) of a row per thread and step; CPT pieces are kept in registers
@@ -63,7 +74,7 @@ __global__ void __launch_bounds__(512)
 allreduce_add_rmsnorm_kernel(const Peers p, size_t slot_words, const uint16_t* partial,
                              uint32_t* __restrict__ epoch, uint32_t* __restrict__ done,
                              int* __restrict__ error, uint16_t* x, const uint16_t* __restrict__ weight,
-                             uint16_t* __restrict__ y, int hidden, float eps) {
+                             uint16_t* __restrict__ y, int hidden, float eps, uint64_t wait_limit_ns) {
     __shared__ float partial_sums[16];
     constexpr int kHeld = CPT > 0 ? CPT : 1;
     const int row = blockIdx.x, chunks = hidden / 8;
@@ -90,12 +101,11 @@ allreduce_add_rmsnorm_kernel(const Peers p, size_t slot_words, const uint16_t* p
     // piece c: push it to every peer, collect the peers' pieces, reduce, add, square
     auto exchange = [&](int c) {
         const uint4 own = ld_mutable(mine + c);
-        const uint4 first = make_uint4(own.x, e, own.y, e), second = make_uint4(own.z, e, own.w, e);
         for (int peer = 0; peer < p.world; ++peer)
             if (peer != p.rank) {
-                uint4* dst = reinterpret_cast<uint4*>(p.area[peer] + size_t(p.rank) * slot_words + row_words + 4 * c);
-                dst[0] = first;
-                dst[1] = second;
+                uint2* dst = p.area[peer] + size_t(p.rank) * slot_words + row_words + 4 * c;
+                st_words(dst, tagged(own.x, e), tagged(own.y, e));
+                st_words(dst + 2, tagged(own.z, e), tagged(own.w, e));
             }
         uint4 t = ld_mutable(xr + c);
         uint4 q[kMaxRanks];
@@ -111,11 +121,11 @@ allreduce_add_rmsnorm_kernel(const Peers p, size_t slot_words, const uint16_t* p
 #pragma unroll
             for (int r = 0; r < kMaxRanks; ++r)
                 if (pending & (1u << r)) {
-                    const uint4* src = reinterpret_cast<const uint4*>(p.area[p.rank] + size_t(r) * slot_words +
-                                                                      row_words + 4 * c);
-                    const uint4 a = ld_words(src), b = ld_words(src + 1);
-                    if (a.y == e && a.w == e && b.y == e && b.w == e) {
-                        q[r] = make_uint4(a.x, a.z, b.x, b.z);
+                    const uint2* src = p.area[p.rank] + size_t(r) * slot_words + row_words + 4 * c;
+                    const Words2 lo = ld_words(src), hi = ld_words(src + 2);
+                    if (uint32_t(lo.a >> 32) == e && uint32_t(lo.b >> 32) == e && uint32_t(hi.a >> 32) == e &&
+                        uint32_t(hi.b >> 32) == e) {
+                        q[r] = make_uint4(uint32_t(lo.a), uint32_t(lo.b), uint32_t(hi.a), uint32_t(hi.b));
                         pending &= ~(1u << r);
                     }
                 }
@@ -123,7 +133,7 @@ allreduce_add_rmsnorm_kernel(const Peers p, size_t slot_words, const uint16_t* p
                 uint64_t now;
                 asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
                 if (start == 0) start = now;
-                if (now - start > 1000000000ull) {  // a peer never arrived: give up, stay usable
+                if (now - start > wait_limit_ns) {  // a peer never arrived: give up, stay usable
                     atomicCAS(error, 0, 100 + (__ffs(int(pending)) - 1));
                     gave_up = true;
                     pending = 0;
@@ -198,9 +208,21 @@ allreduce_add_rmsnorm_kernel(const Peers p, size_t slot_words, const uint16_t* p
 }
 
 }  // namespace
+
+// How long the tensor-parallel kernels wait for a peer before they give up (shared with
+// tp_allreduce_flags.cu).
+static uint64_t g_tp_wait_limit_ns = 1000000000ull;
+uint64_t tp_wait_limit_ns() { return g_tp_wait_limit_ns; }
+
 }  // namespace b200q
 
 using namespace b200q;
+
+extern "C" int32_t b200q_set_wait_limit_ns(int64_t nanoseconds) {
+    B200Q_REQUIRE(nanoseconds > 0 && nanoseconds <= 60000000000ll, "set_wait_limit_ns: between 1 ns and 60 s");
+    g_tp_wait_limit_ns = uint64_t(nanoseconds);
+    return B200Q_OK;
+}
 
 extern "C" int32_t b200q_tp_allreduce_add_rmsnorm(const int64_t* peer_areas, int64_t slot_words,
                                                   const void* partial, int32_t world, int32_t rank,
@@ -233,7 +255,8 @@ extern "C" int32_t b200q_tp_allreduce_add_rmsnorm(const int64_t* peer_areas, int
     launch_overlapped(allreduce_add_rmsnorm_kernel<CPT>, grid, block, 0, s, p, size_t(slot_words),        \
                       static_cast<const uint16_t*>(partial), static_cast<uint32_t*>(epoch),               \
                       static_cast<uint32_t*>(done), static_cast<int*>(error), static_cast<uint16_t*>(x),  \
-                      static_cast<const uint16_t*>(weight), static_cast<uint16_t*>(y), int(hidden), eps)
+                      static_cast<const uint16_t*>(weight), static_cast<uint16_t*>(y), int(hidden), eps,     \
+                      tp_wait_limit_ns())
     const cudaError_t err = held <= 1 ? B200Q_TP_LAUNCH(1) : held <= 2 ? B200Q_TP_LAUNCH(2)
                           : held <= 4 ? B200Q_TP_LAUNCH(4) : B200Q_TP_LAUNCH(0);
 #undef B200Q_TP_LAUNCH

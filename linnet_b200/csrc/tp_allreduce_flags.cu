@@ -17,6 +17,7 @@
 #include "common.cuh"
 
 namespace b200q {
+uint64_t tp_wait_limit_ns();  // tp_allreduce.cu
 namespace {
 
 constexpr int kMaxRanks = 8;
@@ -41,7 +42,7 @@ __global__ void __launch_bounds__(512)
 allreduce_flags_kernel(const Peers p, size_t slot_elems, int max_rows, uint32_t* __restrict__ epoch,
                              uint32_t* __restrict__ done, int* __restrict__ error, uint16_t* x,
                              const uint16_t* __restrict__ weight, uint16_t* __restrict__ y, int hidden,
-                             float eps) {
+                             float eps, uint64_t wait_limit_ns) {
     __shared__ float partial_sums[16];
     __shared__ int gave_up;
     constexpr int kHeld = CPT > 0 ? CPT : 1;
@@ -101,7 +102,7 @@ allreduce_flags_kernel(const Peers p, size_t slot_elems, int max_rows, uint32_t*
                     uint64_t now;
                     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
                     if (start == 0) start = now;
-                    if (now - start > 1000000000ull) {  // a peer never arrived: give up, stay usable
+                    if (now - start > wait_limit_ns) {  // a peer never arrived: give up, stay usable
                         atomicCAS(error, 0, 100 + int(threadIdx.x));
                         gave_up = 1;
                         break;
@@ -228,7 +229,8 @@ extern "C" int32_t b200q_tp_allreduce_add_rmsnorm_flags(const int64_t* peer_area
     launch_overlapped(allreduce_flags_kernel<CPT>, grid, block, 0, s, p, size_t(slot_elems),        \
                       int(max_rows), static_cast<uint32_t*>(epoch), static_cast<uint32_t*>(done),         \
                       static_cast<int*>(error), static_cast<uint16_t*>(x),                                \
-                      static_cast<const uint16_t*>(weight), static_cast<uint16_t*>(y), int(hidden), eps)
+                      static_cast<const uint16_t*>(weight), static_cast<uint16_t*>(y), int(hidden), eps,     \
+                      tp_wait_limit_ns())
     const cudaError_t err = held <= 1 ? B200Q_TP_LAUNCH(1) : held <= 2 ? B200Q_TP_LAUNCH(2)
                           : held <= 4 ? B200Q_TP_LAUNCH(4) : B200Q_TP_LAUNCH(0);
 #undef B200Q_TP_LAUNCH

@@ -58,9 +58,29 @@ class _Device:
 
 # ---- int4 ----------------------------------------------------------------------
 
+_exact_weights = False
+
+
+def set_int4_numerics(mode: str) -> None:
+    """How the decode kernels (up to 16 rows, groups of 128) apply zero point and scale.
+    "fast" (the default; the reference picks these kernels under its `fast` numerics policy
+    only, src/opt/candidates.cpp:28-33): in f32 on each group's sum of exact products.
+    "exact": every weight rounded to the activation type first, bit for bit the weight the
+    reference's torch path multiplies by (python/linnet/src/linnet/torch/native.py:417-424),
+    at about twice the instructions.  Both stay within rtol/atol 1e-2 of that path on
+    weights ~N(0, 0.02)."""
+    global _exact_weights
+    if mode not in ("fast", "exact"):
+        raise ValueError(f"int4 numerics are 'fast' or 'exact', not {mode!r}")
+    _exact_weights = mode == "exact"
+
+
+def int4_numerics() -> str:
+    return "exact" if _exact_weights else "fast"
+
 
 def _int4_linear(x: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor,
-                 zero: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+                 zero: torch.Tensor, out: torch.Tensor | None = None, early: bool = False) -> torch.Tensor:
     rows, depth = x.shape
     width, groups, half = packed.shape
     group = 2 * half
@@ -83,9 +103,10 @@ def _int4_linear(x: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor,
             raise ValueError(f"int4_linear: out must be a contiguous [{rows}, {width}] {x.dtype} tensor on {device}")
         y = out
     with _Device(device):
-        _lib.check(_lib.load().b200q_int4_linear(
+        flags = (_lib.EXACT_WEIGHTS if _exact_weights else 0) | (_lib.EARLY_DEPENDENTS if early else 0)
+        _lib.check(_lib.load().b200q_int4_linear_ex(
             x.data_ptr(), packed.data_ptr(), scale.data_ptr(), zero.data_ptr(), y.data_ptr(),
-            rows, depth, width, group, _code(x.dtype, "int4_linear"), _stream(device)))
+            rows, depth, width, group, _code(x.dtype, "int4_linear"), flags, _stream(device)))
     return y
 
 
@@ -101,16 +122,18 @@ def _(x, packed, scale, zero):
 
 
 def int4_linear(x: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor,
-                zero: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+                zero: torch.Tensor, out: torch.Tensor | None = None, early: bool = False) -> torch.Tensor:
     """`F.linear(x, W)` for `x` [rows, In] (bf16 or f16) and the group-wise 4-bit weight
     of `std.quant::linear_int4_groups`: `packed` [Out, Groups, Group/2] u8 (even value
     low), `scale` and `zero` [Out, Groups].  Any row count: up to 16 rows stream the
     weight once at HBM speed, more go through the tensor-memory GEMM.  `out` (eager
     calls only) receives the result in place of a new tensor, e.g. a buffer in peer-mapped
-    memory that a tensor-parallel reduction reads next."""
-    if out is None and torch.compiler.is_compiling():
+    memory that a tensor-parallel reduction reads next.  `early` (eager calls only): the next
+    kernel in the stream is another product of the same input, which may start prefetching its
+    weights at once (`B200Q_EARLY_DEPENDENTS`)."""
+    if out is None and not early and torch.compiler.is_compiling():
         return _int4_linear_op(x, packed, scale, zero)
-    return _int4_linear(x, packed, scale, zero, out)
+    return _int4_linear(x, packed, scale, zero, out, early)
 
 
 def int4_dequantize(packed: torch.Tensor, scale: torch.Tensor, zero: torch.Tensor) -> torch.Tensor:

@@ -42,6 +42,19 @@ def int4_groups_linear(x, packed, scale, zero, bias=None):
     return y if bias is None else y + bias
 
 
+def int4_groups_linear_f32(x, packed, scale, zero):
+    """The op as `stdlib/quant.linnet:113-175` defines it, before any 16-bit rounding of the
+    weight: `x . ((q - zero) * scale)^T` in f64 (returned as f32), and beside it the most the
+    reference's torch path can differ from that through rounding every weight once to the
+    activation type: `eps * |x| . |w|^T` with eps = 2^-9 (bf16) or 2^-12 (f16)."""
+    rows, groups, half = packed.shape
+    q = unpack_levels(packed)
+    w = ((q.double() - zero.double()[..., None]) * scale.double()[..., None]).reshape(rows, groups * 2 * half)
+    flat = x.reshape(-1, x.shape[-1]).double()
+    eps = 2.0 ** -9 if x.dtype == torch.bfloat16 else 2.0 ** -12
+    return (flat @ w.T).float(), (eps * (flat.abs() @ w.abs().T)).float()
+
+
 def int8_weight(weight: torch.Tensor, scale: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     """`(weight.float() * scale[:, None]).to(dtype)` for a per-row scale `[Out]`, or
     the grouped form for `scale [Out, In/group]`
