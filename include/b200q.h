@@ -141,6 +141,23 @@ int32_t b200q_int8_linear(const void* x, const int8_t* w, const float* scale,
                           void* y, int64_t rows, int64_t in, int64_t out,
                           int64_t group, int32_t dtype, void* stream);
 
+/* ---- int8 activations x int8 weights (W8A8) ----------------------------------
+ * Replaces linnet::rows8 for int8 (python/linnet/src/linnet/torch/kernels.py:669-753):
+ * every row of x [rows, in] (`dtype`) gets scale[row] = max(max|row|, 1e-12) / 127 and
+ * q[row, :] = x / scale rounded half away from zero, clamped to -127..127; IEEE f32
+ * arithmetic.  `in` a multiple of 8. */
+int32_t b200q_int8_rows(const void* x, int8_t* q, float* scale, int64_t rows, int64_t in,
+                        int32_t dtype, void* stream);
+
+/* Replaces linnet::int8_mm (kernels.py:805-915): y[rows, out] in `dtype` =
+ * (xq . w^T summed exactly in int32) * x_scale[row] * w_scale[col], tcgen05 kind::i8 with the
+ * accumulator in tensor memory.  xq [rows, in] and w [out, in] int8, `in` a multiple of
+ * 128, both 16-byte aligned.  A bounded wait that expires is reported by
+ * b200q_int4_gemm_status(). */
+int32_t b200q_int8_mm(const int8_t* xq, const int8_t* w, const float* x_scale,
+                      const float* w_scale, void* y, int64_t rows, int64_t in, int64_t out,
+                      int32_t dtype, void* stream);
+
 /* Replaces dequantize8 (kernels.py:595-666) for int8: weight[out, in] in `dtype`
  * = round(f32(w) * scale). */
 int32_t b200q_int8_dequantize(const int8_t* w, const float* scale, void* weight,

@@ -37,6 +37,9 @@ PROTOTYPES: dict[str, list] = {
                               c_int32, c_void_p],
     "b200q_int8_linear": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                           c_int32, c_void_p],
+    "b200q_int8_rows": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int32, c_void_p],
+    "b200q_int8_mm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int32,
+                      c_void_p],
     "b200q_int8_dequantize": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int32,
                               c_void_p],
     "b200q_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float, c_void_p],

@@ -427,7 +427,8 @@ bool run_oct(const GemvArgs& a, cudaStream_t stream, int32_t* status) {
 
 // The one-block-per-multiprocessor kernel (int4_gemv_sm.cuh) for group 128 and up to 16 rows:
 // the default with post-scaled sums, and with B200Q_EXACT_WEIGHTS where it takes the shape.
-// The ring is as deep as the staged activations (2 KB per row and 1024 inputs) leave room for.
+// Three ring slots a lane keep HBM busy (see int4_gemv_sm.cuh on why not more); two where the
+// staged activations (2 KB per row and 1024 inputs) leave no room for three.
 template <typename T, bool EXACT>
 bool run_sm(const GemvArgs& a, cudaStream_t stream, int32_t* status) {
     if (a.G != 128 || a.M > 16 || size_t(a.N) * size_t(a.K / 2) >= (size_t(1) << 40)) return false;
@@ -441,13 +442,10 @@ bool run_sm(const GemvArgs& a, cudaStream_t stream, int32_t* status) {
         return true;                                                              \
     }
     if (a.M <= 8) {
-        B200Q_SM(1, 8, 7)
-        B200Q_SM(1, 8, 6)
-        B200Q_SM(1, 8, 5)
-        B200Q_SM(1, 8, 4)
         B200Q_SM(1, 8, 3)
-        B200Q_SM(1, 4, 4)
+        B200Q_SM(1, 8, 2)
         B200Q_SM(1, 4, 3)
+        B200Q_SM(1, 4, 2)
     } else {
         B200Q_SM(2, 8, 3)
         B200Q_SM(2, 8, 2)

@@ -29,12 +29,15 @@
 //     of their own: no thread-block cluster, no atomics, no global scratch.
 //
 // Order of the memory requests.  A multiprocessor serves its requests in the order they were
-// made, and its share of the weight stream is some 200 KB: an activation load issued after
-// the ring has been filled arrives after all of that (4 us on the headline shape, measured
-// with per-block timestamps), and the arithmetic then starts when the memory traffic is
-// nearly over instead of running under it.  So a warp first asks for its first k-block only
-// (the part that may run ahead of the previous kernel in the stream), then the block loads
-// the activations, and only then the warps fill their rings.
+// made (its share of the weight stream is some 200 KB, 5 us at its share of the HBM rate), and a
+// warp that asks for more than the memory pipeline has room for stalls at the request itself.
+// Measured with per-block timestamps on the headline shape: activation loads issued behind a
+// full ring arrive 3 to 4 us late, and a warp that fills a deep ring first does not even look
+// at them before that, so the arithmetic starts when the memory traffic is nearly over
+// instead of running under it.  Hence: the activation loads go out first, the ring is filled
+// behind them, and it is only as deep as it takes to keep HBM busy (84 KB a multiprocessor
+// at three slots; bandwidth times latency is about 45 KB), the rest being requested as slots
+// are consumed.  PRE ring slots can still be asked for before the wait on the previous kernel.
 #pragma once
 
 #include "gemv_common.cuh"
@@ -134,7 +137,8 @@ __host__ __device__ inline SmLayout sm_layout(int M, int K, int opc) {
 
 // MB: blocks of 8 activation rows (1 or 2).  WARPS: warps per block.  KB: k-blocks per run
 // (8 or 4).  R: ring slots per lane.  EXACT: dequantize every weight as the reference does.
-template <typename T, int MB, int WARPS, int KB, int R, bool EXACT>
+// PRE: ring slots requested ahead of the wait on the previous kernel and of the activations.
+template <typename T, int MB, int WARPS, int KB, int R, bool EXACT, int PRE = 0>
 __global__ void __launch_bounds__(WARPS * 32, 1)
 int4_gemv_sm_kernel(const SmArgs a) {
     static_assert(KB == 8 || KB == 4, "k-blocks per run");
@@ -182,30 +186,44 @@ int4_gemv_sm_kernel(const SmArgs a) {
         asm volatile("cp.async.commit_group;" ::: "memory");  // one group per step, empty past the end
     };
     // The task's scales ([16 rows][steps] x 2 B) and zero points ([16][steps] x 1 B) -> this
-    // warp's part of shared memory, 4 bytes at a time.
-    auto fetch_sz = [&](int tl) {
+    // warp's part of shared memory, 4 bytes at a time: loads first (up to kSzWords words a
+    // lane in registers), stores later.
+    constexpr int kSzWords = 4;
+    auto sz_word = [&](int tl, int i, bool store, uint32_t& v) {
         const int sw = steps / 2, zw = steps / 4;  // words per row
-        const uint32_t* sg = reinterpret_cast<const uint32_t*>(static_cast<const uint16_t*>(a.scale));
-        const uint32_t* zg = reinterpret_cast<const uint32_t*>(a.zero);
-        for (int i = lane; i < 16 * (sw + zw); i += 32) {
-            const bool is_zero = i >= 16 * sw;
-            const int j = is_zero ? i - 16 * sw : i;
-            const int per = is_zero ? zw : sw;
-            const int row = j / per, word = j % per;
+        if (i >= 16 * (sw + zw)) return;
+        const bool is_zero = i >= 16 * sw;
+        const int j = is_zero ? i - 16 * sw : i;
+        const int per = is_zero ? zw : sw;
+        const int row = j / per, word = j % per;
+        if (!store) {
             const int r = min(tl * 16 + row, N - 1);
             const size_t at = size_t(r) * groups + kbase;  // element index of the row's first group
-            const uint32_t v = is_zero ? __ldg(zg + at / 4 + word) : __ldg(sg + at / 2 + word);
+            v = is_zero ? __ldg(reinterpret_cast<const uint32_t*>(a.zero) + at / 4 + word)
+                        : __ldg(reinterpret_cast<const uint32_t*>(static_cast<const uint16_t*>(a.scale)) + at / 2 + word);
+        } else {
             sts32(my_sz + (is_zero ? 16 * steps * 2 : 0) + j * 4, v);
         }
     };
+    auto fetch_sz = [&](int tl) {  // load and store at once (tasks after the first)
+        for (int i = lane; i < 16 * (steps / 2 + steps / 4); i += 32) {
+            uint32_t v = 0;
+            sz_word(tl, i, false, v);
+            sz_word(tl, i, true, v);
+        }
+    };
+    const bool sz_in_registers = 16 * (steps / 2 + steps / 4) <= 32 * kSzWords;
 
-    // 1. The part that does not depend on the kernel ahead in the stream: the first task's
-    //    scales, zero points and first k-block.
+    // 1. Requests, in the order they should be served: (PRE ring slots, which may run ahead of
+    //    the previous kernel in the stream;) the activations; the first task's scales and zero
+    //    points; the rest of the ring.  Nothing loaded is touched before all of it is asked for.
     const bool has_task = works && tile < t1;
+    uint32_t szr[kSzWords] = {0, 0, 0, 0};
+    constexpr int kPre = R < PRE ? R : PRE;
     if (has_task) {
         set_rows(tile);
-        fetch_sz(tile);
-        request(0, 0);
+#pragma unroll
+        for (int s = 0; s < kPre; ++s) request(s, s);
     }
     if (a.overlap) {
         if (a.early) pdl_launch_dependents();
@@ -213,8 +231,7 @@ int4_gemv_sm_kernel(const SmArgs a) {
     }
 
     // 2. Activations: M * (K / 128) * 16 pieces of 16 bytes, the 16 pieces of a (row, k-block)
-    //    in 16 consecutive lanes, which also add up the k-block's inputs.  With up to two
-    //    pieces a thread the loads are issued before the rings are filled and used after.
+    //    in 16 consecutive lanes, which also add up the k-block's inputs.
     {
         const uint4* xg = below_pdl_wait(static_cast<const uint4*>(a.x));
         const int pieces = M * groups * 16;
@@ -256,23 +273,37 @@ int4_gemv_sm_kernel(const SmArgs a) {
             }
             return raw;
         };
-        const bool few = pieces <= 2 * threads;
-        const int e0 = int(threadIdx.x), e1 = e0 + threads;
-        uint4 raw0 = load(e0), raw1 = make_uint4(0, 0, 0, 0);
-        if (pieces > threads) raw1 = load(e1);
-        if (few && has_task) {  // the rings, behind the activation loads
+        // Up to kFirst pieces a thread are in flight at once (all of them, for up to 16 rows of
+        // 4096 inputs): registers are plentiful before the main loop.
+        constexpr int kFirst = MB == 1 ? 5 : 10;
+        uint4 raw[kFirst];
 #pragma unroll
-            for (int s = 1; s < R; ++s) request(s, s);
-        }
-        stage(e0, raw0);
-        if (pieces > threads) stage(e1, raw1);
-        for (int base = 2 * threads; base < pieces; base += threads) {
-            const int e = base + int(threadIdx.x);
-            stage(e, load(e));
-        }
-        if (!few && has_task) {
+        for (int u = 0; u < kFirst; ++u) raw[u] = load(u * threads + int(threadIdx.x));
+        if (has_task) {
+            if (sz_in_registers) {
 #pragma unroll
-            for (int s = 1; s < R; ++s) request(s, s);
+                for (int u = 0; u < kSzWords; ++u) sz_word(tile, lane + 32 * u, false, szr[u]);
+            }
+#pragma unroll
+            for (int s = kPre; s < R; ++s) request(s, s);  // the (rest of the) ring
+        }
+#pragma unroll
+        for (int u = 0; u < kFirst; ++u)
+            if (u * threads < pieces) stage(u * threads + int(threadIdx.x), raw[u]);
+        for (int base = kFirst * threads; base < pieces; base += 4 * threads) {  // four loads in flight a thread
+            uint4 more[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) more[u] = load(base + u * threads + int(threadIdx.x));
+#pragma unroll
+            for (int u = 0; u < 4; ++u) stage(base + u * threads + int(threadIdx.x), more[u]);
+        }
+        if (has_task) {
+            if (sz_in_registers) {
+#pragma unroll
+                for (int u = 0; u < kSzWords; ++u) sz_word(tile, lane + 32 * u, true, szr[u]);
+            } else {
+                fetch_sz(tile);
+            }
         }
     }
     __syncthreads();
@@ -440,9 +471,9 @@ inline bool sm_plan(SmArgs& a, int G, int sms, size_t* smem) {
     return l.total <= 226 * 1024;
 }
 
-template <typename T, int MB, int WARPS, int KB, int R, bool EXACT>
+template <typename T, int MB, int WARPS, int KB, int R, bool EXACT, int PRE = 0>
 int32_t launch_sm(const SmArgs& a, size_t smem, int sms, cudaStream_t stream) {
-    auto kernel = int4_gemv_sm_kernel<T, MB, WARPS, KB, R, EXACT>;
+    auto kernel = int4_gemv_sm_kernel<T, MB, WARPS, KB, R, EXACT, PRE>;
     const cudaError_t attr_err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
     if (attr_err != cudaSuccess) {
         cudaGetLastError();

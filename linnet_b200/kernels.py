@@ -2,8 +2,9 @@
 
 Same names, arguments and results as the reference's Triton operators
 (python/linnet/src/linnet/torch/kernels.py): `int4_linear` (`linnet::int4_linear`,
-:277-323), `gemv8` (`linnet::gemv8`, :375-434), `w8a16` (`linnet::w8a16`, :526-592)
-and `dequantize8` (:619-666).  Each is a `torch.library` custom op with a fake
+:277-323), `gemv8` (`linnet::gemv8`, :375-434), `w8a16` (`linnet::w8a16`, :526-592),
+`dequantize8` (:619-666), `int8_rows` (`linnet::rows8`, :705-753) and `int8_mm`
+(`linnet::int8_mm`, :856-915).  Each is a `torch.library` custom op with a fake
 implementation, so it is opaque to `torch.compile` and recordable into a CUDA graph;
 outside `torch.compile` the kernel is launched directly (the reference does the same
 to keep the host cost of a decoding step low, kernels.py:43-55).
@@ -234,17 +235,100 @@ def dequantize8(weight: torch.Tensor, scale: torch.Tensor, fp8: bool, group: int
     return out
 
 
+# ---- int8 activations (W8A8) ------------------------------------------------------
+
+
+def _int8_rows(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    rows, depth = x.shape
+    device = _on_gpu("int8_rows", x)
+    if depth % 8:
+        raise ValueError(f"int8_rows: rows of {depth} inputs are not a multiple of 8")
+    x = x.contiguous()
+    q = torch.empty(rows, depth, dtype=torch.int8, device=device)
+    scale = torch.empty(rows, 1, dtype=torch.float32, device=device)
+    with _Device(device):
+        _lib.check(_lib.load().b200q_int8_rows(x.data_ptr(), q.data_ptr(), scale.data_ptr(), rows, depth,
+                                               _code(x.dtype, "int8_rows"), _stream(device)))
+    return q, scale
+
+
+@torch.library.custom_op("linnet::rows8", mutates_args=(), device_types="cuda")
+def _rows8_op(x: torch.Tensor, fp8: bool) -> tuple[torch.Tensor, torch.Tensor]:
+    _no_fp8("rows8", fp8)
+    return _int8_rows(x)
+
+
+@_rows8_op.register_fake
+def _(x, fp8):
+    return x.new_empty(x.shape, dtype=torch.int8), x.new_empty(x.shape[0], 1, dtype=torch.float32)
+
+
+def int8_rows(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Each row of `x` [rows, In] rounded to int8 with a scale of its own (its largest magnitude
+    over 127; levels rounded half away from zero): the rounded rows and the scales ([rows, 1],
+    f32), as `int8_mm` takes them (the reference's `int8_rows`, kernels.py:705-753)."""
+    if torch.compiler.is_compiling():
+        return _rows8_op(x, False)
+    return _int8_rows(x)
+
+
+def int8_mm_available(weight: torch.Tensor) -> bool:
+    """Whether `int8_mm` takes this weight: inputs a multiple of 128 (the reference asks the
+    same, kernels.py:866-868, and outputs a multiple of 16, quantized.py:85-87)."""
+    return weight.is_cuda and weight.shape[1] % 128 == 0 and weight.shape[0] % 16 == 0
+
+
+def _int8_mm(x: torch.Tensor, weight: torch.Tensor, x_scale: torch.Tensor, scale: torch.Tensor,
+             dtype: torch.dtype) -> torch.Tensor:
+    rows, depth = x.shape
+    width = weight.shape[0]
+    if x.dtype != torch.int8 or weight.dtype != torch.int8:
+        raise ValueError("int8_mm: int8 rows and int8 weights expected")
+    if weight.shape[1] != depth or depth % 128:
+        raise ValueError(f"int8_mm: {depth} inputs (a multiple of 128) against a weight of {weight.shape[1]}")
+    device = _on_gpu("int8_mm", x, weight, x_scale, scale)
+    x, weight = x.contiguous(), weight.contiguous()
+    x_scale, scale = x_scale.float().reshape(-1).contiguous(), scale.float().reshape(-1).contiguous()
+    if x_scale.numel() != rows or scale.numel() != width:
+        raise ValueError("int8_mm: one scale a row of x and one a row of the weight")
+    y = torch.empty(rows, width, dtype=dtype, device=device)
+    with _Device(device):
+        _lib.check(_lib.load().b200q_int8_mm(x.data_ptr(), weight.data_ptr(), x_scale.data_ptr(), scale.data_ptr(),
+                                             y.data_ptr(), rows, depth, width, _code(dtype, "int8_mm"),
+                                             _stream(device)))
+    return y
+
+
+@torch.library.custom_op("linnet::int8_mm", mutates_args=(), device_types="cuda")
+def _int8_mm_op(x: torch.Tensor, weight: torch.Tensor, x_scale: torch.Tensor, scale: torch.Tensor,
+                dtype: torch.dtype) -> torch.Tensor:
+    return _int8_mm(x, weight, x_scale, scale, dtype)
+
+
+@_int8_mm_op.register_fake
+def _(x, weight, x_scale, scale, dtype):
+    return x.new_empty(x.shape[0], weight.shape[0], dtype=dtype)
+
+
+def int8_mm(x: torch.Tensor, weight: torch.Tensor, x_scale: torch.Tensor, scale: torch.Tensor,
+            dtype: torch.dtype) -> torch.Tensor:
+    """`(x @ weight.T) * x_scale * scale` in `dtype`, for int8 rows `x` [rows, In] with their
+    scales ([rows, 1] f32, from `int8_rows`) and int8 weights [Out, In] with one scale a row
+    ([Out]); the sum is exact in int32 on the tensor cores (kernels.py:856-915)."""
+    if torch.compiler.is_compiling():
+        return _int8_mm_op(x, weight, x_scale, scale, dtype)
+    return _int8_mm(x, weight, x_scale, scale, dtype)
+
+
 def _outside(name: str):
     def missing(*args: object, **kwargs: object):
         raise NotImplementedError(f"linnet.torch.kernels.{name} is outside this build "
-                                  "(int4 / int8 weight-only layers)")
+                                  "(int4 / int8 layers)")
     missing.__name__ = name
     return missing
 
 
-# Names the reference's `quantized.py` and generated source look up on this module
-# for formats that are not part of this build.
+# Names the reference's `quantized.py` looks up on this module for the FP8 formats, which
+# are not part of this build.
 fp8_rows = _outside("fp8_rows")
 fp8_groups = _outside("fp8_groups")
-int8_rows = _outside("int8_rows")
-int8_mm = _outside("int8_mm")

@@ -5,10 +5,12 @@ is two calls, `*_operands` once per bound weights (run by `prepare`) and `*_line
 per step.  The operand tuples have the reference's members
 (`Int8Operands = (weight, scale_f32, rounded, fast)`, quantized.py:62-66).
 
-Differences, all within this build's scope: the product always reads the weight as it
-is (weight-only) -- `rounded` is carried but the 8-bit-activation route of
-`numerics="fast"` past 32 rows (quantized.py:187-189) is not built; and there is no
-dequantize-and-`F.linear` fallback for CPU tensors.
+Row-count dispatch as the reference's `_weight_only` (quantized.py:90-105): one row goes to
+`gemv8`, up to `TILED_ROWS` rows to `w8a16` (both stream the int8 weight once through the
+decode kernel), more rows dequantize the weight once with `dequantize8` and hand the dense
+product to the library GEMM, which is the reference's own route for that range.  `rounded`
+with more than `FEW_ROWS` rows takes the 8-bit-activation route (`int8_rows` + `int8_mm`,
+quantized.py:187-189).  There is no fallback for CPU tensors.
 """
 
 from __future__ import annotations
@@ -21,6 +23,28 @@ Int8Operands = tuple[torch.Tensor, torch.Tensor, int, int]
 Int8GroupOperands = tuple[torch.Tensor, torch.Tensor, int, int]
 
 _HALF = (torch.bfloat16, torch.float16)
+
+# Where the kernels switch (the reference's constants, python/linnet/src/linnet/quant.py:73-80).
+FEW_ROWS = 32
+TILED_ROWS = 64
+
+
+def _weight_only(flat: torch.Tensor, weight: torch.Tensor, scale: torch.Tensor, group: int = 0) -> torch.Tensor:
+    rows = flat.shape[0]
+    if rows == 1:
+        return kernels.gemv8(flat, weight, scale, False, group, 1)
+    if rows <= TILED_ROWS:
+        return kernels.w8a16(flat, weight, scale, False, group, 1)
+    dequantized = kernels.dequantize8(weight, scale, False, group, 1, flat.dtype)
+    # f32 accumulation all the way: the library may otherwise add split-K partial sums in the
+    # 16-bit type, which alone costs more than the 1e-2 this layer is held to.
+    matmul = torch.backends.cuda.matmul
+    saved = (matmul.allow_bf16_reduced_precision_reduction, matmul.allow_fp16_reduced_precision_reduction)
+    matmul.allow_bf16_reduced_precision_reduction = matmul.allow_fp16_reduced_precision_reduction = False
+    try:
+        return torch.nn.functional.linear(flat, dequantized)
+    finally:
+        matmul.allow_bf16_reduced_precision_reduction, matmul.allow_fp16_reduced_precision_reduction = saved
 
 
 def _finish(x: torch.Tensor, y: torch.Tensor, bias: torch.Tensor | None) -> torch.Tensor:
@@ -41,13 +65,14 @@ def int8_operands(weight: torch.Tensor, scale: torch.Tensor, rounded: int) -> In
 
 
 def int8_linear(x: torch.Tensor, operands: Int8Operands, bias: torch.Tensor | None) -> torch.Tensor:
-    weight, scale, _rounded, _fast = operands
+    weight, scale, rounded, _fast = operands
     _require(x, "int8_linear")
     flat = x.reshape(-1, x.shape[-1])
-    if flat.shape[0] == 1:
-        y = kernels.gemv8(flat, weight, scale, False, 0, 1)
+    if rounded and flat.shape[0] > FEW_ROWS and kernels.int8_mm_available(weight):
+        q, row_scale = kernels.int8_rows(flat)
+        y = kernels.int8_mm(q, weight, row_scale, scale, flat.dtype)
     else:
-        y = kernels.w8a16(flat, weight, scale, False, 0, 1)
+        y = _weight_only(flat, weight, scale)
     return _finish(x, y, bias)
 
 
@@ -64,8 +89,4 @@ def int8_group_linear(x: torch.Tensor, operands: Int8GroupOperands,
     weight, scale, group, _fast = operands
     _require(x, "int8_group_linear")
     flat = x.reshape(-1, x.shape[-1])
-    if flat.shape[0] == 1:
-        y = kernels.gemv8(flat, weight, scale, False, group, 1)
-    else:
-        y = kernels.w8a16(flat, weight, scale, False, group, 1)
-    return _finish(x, y, bias)
+    return _finish(x, _weight_only(flat, weight, scale, group), bias)

@@ -85,6 +85,29 @@ def int8_group_linear(x, weight, scale, bias=None):
     return y if bias is None else y + bias
 
 
+def int8_rows(x: torch.Tensor):
+    """Every row of `x` rounded to int8 with its own scale, as the reference's `int8_rows`
+    defines it (python/linnet/src/linnet/torch/kernels.py:669-693): scale = max(max|row|,
+    1e-12) / 127; level = x / scale, half away from zero (`x + 0.5` or `x - 0.5`, then
+    truncation), clamped to +-127.  IEEE f32 throughout.  Returns (q i8, scale f32 [rows, 1])."""
+    v = x.float()
+    top = v.abs().amax(dim=1, keepdim=True).clamp_min(1e-12)
+    scale = top / torch.tensor(127.0)
+    s = v / scale
+    r = torch.where(s >= 0, s + 0.5, s - 0.5).clamp(-127.0, 127.0)
+    return r.trunc().to(torch.int8), scale
+
+
+def int8_mm(xq: torch.Tensor, weight: torch.Tensor, x_scale: torch.Tensor, scale: torch.Tensor,
+            dtype: torch.dtype) -> torch.Tensor:
+    """`(xq @ weight.T)` exactly in integers, then `* x_scale * scale` in f32 in that order,
+    one rounding to `dtype` (kernels.py:805-836)."""
+    acc = xq.to(torch.int64) @ weight.to(torch.int64).T
+    y = acc.to(torch.float32) * x_scale.float().reshape(-1, 1)
+    y = y * scale.float().reshape(1, -1)
+    return y.to(dtype)
+
+
 def shard_int4(packed, scale, zero, rank: int, shards: int, split: str):
     """One tensor-parallel rank's slice of an int4 layer.
 

@@ -13,6 +13,10 @@ ROOT = Path(__file__).resolve().parents[1]
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
+TESTS = Path(__file__).resolve().parent
+if str(TESTS) not in sys.path:
+    sys.path.insert(0, str(TESTS))  # helper modules beside the tests (checkpoint_cases, decoder_util)
+
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
 

@@ -1,18 +1,17 @@
 """Generates the golden fixtures in this directory by RUNNING THE REFERENCE.
 
-Run once in a container that has the reference checked out and its compiler
-built (neither exists where the GPU tests run, which is why the outputs are
-committed):
+Run where the reference has been built into `oracle/_ref` (`python -m oracle.build_ref`); the
+outputs are committed so that the tests do not depend on it:
 
-    LINNET_REF=/path/to/reference LINNET_BIN=/path/to/linnet \
-    LINNET_HOME=/tmp/linnet-home python tests/golden/make_golden.py
+    python tests/golden/make_golden.py
 
 Everything stored here comes out of the reference's own code:
 `linnet.quant.quantize_int4_groups / quantize_int8_groups / pack_int4_groups`,
 `linnet.weights.to_bf16_bits`, `linnet.torch.native.NATIVE[...]` (interpreter
 implementations), `linnet.torch.quantized.int8_linear / int8_group_linear` (CPU
-branch) and `linnet.torch.load(...)` of small `Int4GroupLinear` / `Int8Linear`
-cards, interpreted and as generated source.  Inputs are stored next to the
+branch), `linnet.torch.load(...)` of small `Int4GroupLinear` / `Int8Linear`
+cards, interpreted and as generated source, and `linnet.quant.quantize_checkpoint /
+import_quantized` on small SafeTensors files.  Inputs are stored next to the
 outputs so the tests never depend on a random generator's implementation.
 """
 
@@ -26,10 +25,18 @@ from pathlib import Path
 import numpy as np
 import torch
 
-REF = Path(os.environ.get("LINNET_REF", "/root/reference"))
-sys.path.insert(0, str(REF / "python/linnet/src"))
-os.environ.setdefault("LINNET_BIN", "/tmp/linnet-build/linnet")
-os.environ.setdefault("LINNET_HOME", "/tmp/linnet-home")
+ROOT = Path(__file__).resolve().parents[2]
+sys.path.insert(0, str(ROOT))
+from oracle import build_ref  # noqa: E402
+
+if not build_ref.available():
+    raise SystemExit("oracle/_ref is missing: run `python -m oracle.build_ref` first")
+REF_HOME = Path(tempfile.mkdtemp(prefix="linnet-home-"))
+for key, value in build_ref.environment(REF_HOME).items():
+    if key.startswith("LINNET_"):
+        os.environ[key] = value
+sys.path.insert(0, str(build_ref.OUT / "python"))
+STD = str(build_ref.OUT / "stdlib")
 
 from linnet import quant as refq  # noqa: E402
 from linnet.weights import to_bf16_bits  # noqa: E402
@@ -138,7 +145,7 @@ def linear_cases() -> dict[str, np.ndarray]:
     from linnet.torch import load
     from linnet.torch import native, quantized
 
-    std = REF / "stdlib"
+    std = STD
     out: dict[str, np.ndarray] = {}
     gen = torch.Generator().manual_seed(0)
     IN, OUT, GROUP = 256, 64, 128
@@ -202,11 +209,33 @@ def linear_cases() -> dict[str, np.ndarray]:
     return out
 
 
+def checkpoint_cases() -> None:
+    """`linnet.quant.quantize_checkpoint` / `import_quantized` on the small checkpoints of
+    tests/checkpoint_cases.py: inputs and the reference's output files, verbatim."""
+    import json
+    import shutil
+
+    sys.path.insert(0, str(ROOT / "tests"))
+    import checkpoint_cases as cc
+
+    target = HERE / "checkpoints"
+    if target.exists():
+        shutil.rmtree(target)
+    target.mkdir()
+    cases = cc.all_cases(target)
+    for name, case in cases.items():
+        paths = cc.convert(refq, case, target, target / f"{name}.expected.safetensors")
+        case["quantized"] = paths
+    (target / "cases.json").write_text(json.dumps(cases, indent=1) + "\n", encoding="utf-8")
+
+
 def main() -> None:
     np.savez_compressed(HERE / "quantizer.npz", **quantizer_cases())
     np.savez_compressed(HERE / "linear.npz", **linear_cases())
-    for name in ("quantizer.npz", "linear.npz"):
-        print(name, (HERE / name).stat().st_size, "bytes")
+    checkpoint_cases()
+    for path in sorted(HERE.rglob("*")):
+        if path.is_file() and path.suffix in (".npz", ".safetensors", ".json"):
+            print(path.relative_to(HERE), path.stat().st_size, "bytes")
 
 
 if __name__ == "__main__":

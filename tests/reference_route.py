@@ -316,7 +316,7 @@ def run_cards(work: Path, device: str, modes: list, out: dict, std: str) -> None
         model = load("llama4", LLAMA_GENERICS, "llama4", mode, source=work / "llama4" / "src" / "lib.linnet")
         tokens = torch.from_numpy(inputs["llama4/tokens"]).to(device)
         for step in range(3):
-            logits = model.run_entry("decode", [tokens[step], torch.tensor(step, dtype=torch.int32)])
+            logits = model.run_entry("decode", [tokens[step], torch.tensor(step, dtype=torch.int32, device=device)])
             out[f"{tag}/llama4/logits{step}"] = bits(logits)
         del model
 

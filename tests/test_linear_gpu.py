@@ -269,7 +269,7 @@ def test_int8_shapes(rows, depth, out, group):
     bias = torch.randn(out, generator=gen).to(torch.bfloat16)
     if group == 0:
         want = lo.int8_linear(x, q, scale.reshape(-1), bias)
-        ops = quantized.int8_operands(q.cuda(), scale.reshape(-1).cuda(), 1)
+        ops = quantized.int8_operands(q.cuda(), scale.reshape(-1).cuda(), 0)  # weight-only: inputs not rounded
         got = quantized.int8_linear(x.cuda(), ops, bias.cuda())
     else:
         want = lo.int8_group_linear(x, q, scale, bias)
