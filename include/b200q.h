@@ -285,6 +285,16 @@ int32_t b200q_tp_allreduce_add_rmsnorm(const int64_t* peer_areas, int64_t slot_w
                                        const void* weight, void* y, int64_t rows, int64_t hidden,
                                        float eps, void* stream);
 
+/* The exchange of b200q_tp_allreduce_add_rmsnorm alone: out[count] = the ranks' in[count]
+ * summed in f32 in rank order and rounded once to `dtype` (bf16 or f16), count a multiple
+ * of 8.  Replaces the reference's one-shot all-reduce for messages up to 128 KiB
+ * (`OneShot.__call__`, python/linnet/src/linnet/torch/collectives.py:86-103; kernel
+ * kernels.py:1107-1156), with every wait bounded.  Same areas, counters, error word and
+ * call-site rule as above (slot_words >= count / 2). */
+int32_t b200q_tp_allreduce(const int64_t* peer_areas, int64_t slot_words, const void* in,
+                           int32_t world, int32_t rank, void* epoch, void* done, void* error,
+                           void* out, int64_t count, int32_t dtype, void* stream);
+
 /* b200q_tp_allreduce_add_rmsnorm with a different exchange: rows pushed as plain bf16, then
  * one flag per (source rank, row).  peer_areas[r]: rank r's receive area of the call site,
  * [world][slot_elems] bf16 with slot_elems >= max_rows * hidden; peer_flags[r]: rank r's flag

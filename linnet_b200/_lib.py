@@ -62,6 +62,8 @@ PROTOTYPES: dict[str, list] = {
     "b200q_tp_allreduce_add_rmsnorm_flags": [c_void_p, c_void_p, c_int64, c_int64, c_int32, c_int32, c_void_p,
                                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                              c_float, c_void_p],
+    "b200q_tp_allreduce": [c_void_p, c_int64, c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p,
+                           c_int64, c_int32, c_void_p],
     "b200q_tp_allreduce_add_rmsnorm": [c_void_p, c_int64, c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float, c_void_p],
 }

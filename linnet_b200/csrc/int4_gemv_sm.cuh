@@ -138,8 +138,11 @@ __host__ __device__ inline SmLayout sm_layout(int M, int K, int opc) {
 // MB: blocks of 8 activation rows (1 or 2).  WARPS: warps per block.  KB: k-blocks per run
 // (8 or 4).  R: ring slots per lane.  EXACT: dequantize every weight as the reference does.
 // PRE: ring slots requested ahead of the wait on the previous kernel and of the activations.
-template <typename T, int MB, int WARPS, int KB, int R, bool EXACT, int PRE = 0>
-__global__ void __launch_bounds__(WARPS * 32, 1)
+// SW: extra warps that do nothing but load and stage the activations, while the WARPS others
+// fill their rings (a warp stalls at a request the memory pipeline has no room for, and could
+// not look at the activations meanwhile); 0: every warp stages its share after its requests.
+template <typename T, int MB, int WARPS, int KB, int R, bool EXACT, int PRE = 0, int SW = 0>
+__global__ void __launch_bounds__((WARPS + SW) * 32, 1)
 int4_gemv_sm_kernel(const SmArgs a) {
     static_assert(KB == 8 || KB == 4, "k-blocks per run");
     using H = Half16<T>;
@@ -235,7 +238,9 @@ int4_gemv_sm_kernel(const SmArgs a) {
     {
         const uint4* xg = below_pdl_wait(static_cast<const uint4*>(a.x));
         const int pieces = M * groups * 16;
-        const int threads = WARPS * 32;
+        const bool stager = SW == 0 || warp >= WARPS;
+        const int threads = SW == 0 ? WARPS * 32 : SW * 32;
+        const int me = SW == 0 ? int(threadIdx.x) : int(threadIdx.x) - WARPS * 32;  // among the staging threads
         auto where = [&](int e, int& m, int& j, int& c) {
             m = e / (groups * 16);
             const int rem = e - m * (groups * 16);
@@ -273,12 +278,14 @@ int4_gemv_sm_kernel(const SmArgs a) {
             }
             return raw;
         };
-        // Up to kFirst pieces a thread are in flight at once (all of them, for up to 16 rows of
-        // 4096 inputs): registers are plentiful before the main loop.
-        constexpr int kFirst = MB == 1 ? 5 : 10;
+        // Up to kFirst pieces a thread are in flight at once: registers are plentiful before the
+        // main loop (and all a staging warp needs).
+        constexpr int kFirst = SW > 0 ? 8 : MB == 1 ? 5 : 10;
         uint4 raw[kFirst];
+        if (stager) {
 #pragma unroll
-        for (int u = 0; u < kFirst; ++u) raw[u] = load(u * threads + int(threadIdx.x));
+            for (int u = 0; u < kFirst; ++u) raw[u] = load(u * threads + me);
+        }
         if (has_task) {
             if (sz_in_registers) {
 #pragma unroll
@@ -287,15 +294,17 @@ int4_gemv_sm_kernel(const SmArgs a) {
 #pragma unroll
             for (int s = kPre; s < R; ++s) request(s, s);  // the (rest of the) ring
         }
+        if (stager) {
 #pragma unroll
-        for (int u = 0; u < kFirst; ++u)
-            if (u * threads < pieces) stage(u * threads + int(threadIdx.x), raw[u]);
-        for (int base = kFirst * threads; base < pieces; base += 4 * threads) {  // four loads in flight a thread
-            uint4 more[4];
+            for (int u = 0; u < kFirst; ++u)
+                if (u * threads < pieces) stage(u * threads + me, raw[u]);
+            for (int base = kFirst * threads; base < pieces; base += 4 * threads) {  // four loads in flight a thread
+                uint4 more[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) more[u] = load(base + u * threads + int(threadIdx.x));
+                for (int u = 0; u < 4; ++u) more[u] = load(base + u * threads + me);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) stage(base + u * threads + int(threadIdx.x), more[u]);
+                for (int u = 0; u < 4; ++u) stage(base + u * threads + me, more[u]);
+            }
         }
         if (has_task) {
             if (sz_in_registers) {
@@ -471,9 +480,9 @@ inline bool sm_plan(SmArgs& a, int G, int sms, size_t* smem) {
     return l.total <= 226 * 1024;
 }
 
-template <typename T, int MB, int WARPS, int KB, int R, bool EXACT, int PRE = 0>
+template <typename T, int MB, int WARPS, int KB, int R, bool EXACT, int PRE = 0, int SW = 0>
 int32_t launch_sm(const SmArgs& a, size_t smem, int sms, cudaStream_t stream) {
-    auto kernel = int4_gemv_sm_kernel<T, MB, WARPS, KB, R, EXACT, PRE>;
+    auto kernel = int4_gemv_sm_kernel<T, MB, WARPS, KB, R, EXACT, PRE, SW>;
     const cudaError_t attr_err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
     if (attr_err != cudaSuccess) {
         cudaGetLastError();
@@ -484,7 +493,7 @@ int32_t launch_sm(const SmArgs& a, size_t smem, int sms, cudaStream_t stream) {
     const int grid = a.tiles < sms ? a.tiles : sms;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(unsigned(grid), 1, 1);
-    config.blockDim = dim3(WARPS * 32, 1, 1);
+    config.blockDim = dim3((WARPS + SW) * 32, 1, 1);
     config.dynamicSmemBytes = smem;
     config.stream = stream;
     cudaLaunchAttribute attr[1];

@@ -207,6 +207,88 @@ allreduce_add_rmsnorm_kernel(const Peers p, size_t slot_words, const uint16_t* p
     }
 }
 
+// The exchange alone: out[i] = round(sum over ranks of in_r[i]), summed in f32 in rank order.
+// One 16-byte piece (8 values) per thread; bf16 or f16.
+template <bool F16>
+__global__ void __launch_bounds__(512)
+allreduce_words_kernel(const Peers p, size_t slot_words, const uint16_t* in, uint32_t* __restrict__ epoch,
+                       uint32_t* __restrict__ done, int* __restrict__ error, uint16_t* __restrict__ out, int pieces,
+                       uint64_t wait_limit_ns) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const uint32_t e = *reinterpret_cast<volatile uint32_t*>(epoch) + 1;
+    bool gave_up = *reinterpret_cast<volatile int*>(error) != 0;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < pieces) {
+        const uint4 own = ld_mutable(reinterpret_cast<const uint4*>(in) + c);
+        for (int peer = 0; peer < p.world; ++peer)
+            if (peer != p.rank) {
+                uint2* dst = p.area[peer] + size_t(p.rank) * slot_words + size_t(4) * c;
+                st_words(dst, tagged(own.x, e), tagged(own.y, e));
+                st_words(dst + 2, tagged(own.z, e), tagged(own.w, e));
+            }
+        uint4 q[kMaxRanks];
+        unsigned pending = 0;
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r) {
+            q[r] = make_uint4(0, 0, 0, 0);
+            if (r < p.world && r != p.rank) pending |= 1u << r;
+        }
+        if (gave_up) pending = 0;
+        uint64_t start = 0;
+        for (uint32_t spins = 0; pending != 0; ++spins) {
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (pending & (1u << r)) {
+                    const uint2* src = p.area[p.rank] + size_t(r) * slot_words + size_t(4) * c;
+                    const Words2 lo = ld_words(src), hi = ld_words(src + 2);
+                    if (uint32_t(lo.a >> 32) == e && uint32_t(lo.b >> 32) == e && uint32_t(hi.a >> 32) == e &&
+                        uint32_t(hi.b >> 32) == e) {
+                        q[r] = make_uint4(uint32_t(lo.a), uint32_t(lo.b), uint32_t(hi.a), uint32_t(hi.b));
+                        pending &= ~(1u << r);
+                    }
+                }
+            if (pending != 0 && (spins & 63u) == 63u) {
+                uint64_t now;
+                asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+                if (start == 0) start = now;
+                if (now - start > wait_limit_ns) {  // a peer never arrived: give up, stay usable
+                    atomicCAS(error, 0, 100 + (__ffs(int(pending)) - 1));
+                    gave_up = true;
+                    pending = 0;
+                }
+            }
+        }
+        if (!gave_up) {
+            auto low = [](uint32_t v) { return F16 ? __half2float(__ushort_as_half(uint16_t(v & 0xFFFFu))) : lo16(v); };
+            auto high = [](uint32_t v) { return F16 ? __half2float(__ushort_as_half(uint16_t(v >> 16))) : hi16(v); };
+            float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r) {
+                if (r >= p.world) break;
+                const uint4 qr = r == p.rank ? own : q[r];
+                s[0] += low(qr.x); s[1] += high(qr.x); s[2] += low(qr.y); s[3] += high(qr.y);
+                s[4] += low(qr.z); s[5] += high(qr.z); s[6] += low(qr.w); s[7] += high(qr.w);
+            }
+            auto pack = [](float a, float b) {
+                if (!F16) return pack16(a, b);
+                __half2 h = __floats2half2_rn(a, b);
+                return *reinterpret_cast<uint32_t*>(&h);
+            };
+            reinterpret_cast<uint4*>(out)[c] = make_uint4(pack(s[0], s[1]), pack(s[2], s[3]), pack(s[4], s[5]), pack(s[6], s[7]));
+        }
+    }
+    // The last block to finish advances the site's epoch (every block has read it by then).
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(done, 1u) == gridDim.x - 1) {
+            *done = 0;
+            *reinterpret_cast<volatile uint32_t*>(epoch) = e;
+        }
+    }
+}
+
 }  // namespace
 
 // How long the tensor-parallel kernels wait for a peer before they give up (shared with
@@ -261,4 +343,38 @@ extern "C" int32_t b200q_tp_allreduce_add_rmsnorm(const int64_t* peer_areas, int
                           : held <= 4 ? B200Q_TP_LAUNCH(4) : B200Q_TP_LAUNCH(0);
 #undef B200Q_TP_LAUNCH
     return launch_status("tp_allreduce_add_rmsnorm", err);
+}
+
+extern "C" int32_t b200q_tp_allreduce(const int64_t* peer_areas, int64_t slot_words, const void* in, int32_t world,
+                                      int32_t rank, void* epoch, void* done, void* error, void* out, int64_t count,
+                                      int32_t dtype, void* stream) {
+    B200Q_REQUIRE(world >= 2 && world <= kMaxRanks && rank >= 0 && rank < world,
+                  "tp_allreduce: 2..8 ranks, got world=%d rank=%d", world, rank);
+    B200Q_REQUIRE(dtype == B200Q_BF16 || dtype == B200Q_F16, "tp_allreduce: bf16 or f16");
+    B200Q_REQUIRE(count >= 0 && count % 8 == 0, "tp_allreduce: a multiple of 8 values, not %lld", (long long)count);
+    B200Q_REQUIRE(slot_words >= count / 2 && slot_words % 2 == 0, "tp_allreduce: %lld values do not fit slots of %lld words",
+                  (long long)count, (long long)slot_words);
+    if (count == 0) return B200Q_OK;
+    B200Q_REQUIRE(peer_areas && in && epoch && done && error && out && aligned(in, 16) && aligned(out, 16),
+                  "tp_allreduce: null or misaligned argument");
+    Peers p{};
+    p.world = world;
+    p.rank = rank;
+    for (int r = 0; r < world; ++r) {
+        p.area[r] = reinterpret_cast<uint2*>(peer_areas[r]);
+        B200Q_REQUIRE(p.area[r] && aligned(p.area[r], 16), "tp_allreduce: bad peer pointer");
+    }
+    const int pieces = int(count / 8);
+    const int threads = pieces < 256 ? ((pieces + 31) / 32) * 32 : 256;
+    const dim3 grid{unsigned((pieces + threads - 1) / threads)}, block{unsigned(threads)};
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const cudaError_t err =
+        dtype == B200Q_F16
+            ? launch_overlapped(allreduce_words_kernel<true>, grid, block, 0, s, p, size_t(slot_words),
+                                static_cast<const uint16_t*>(in), static_cast<uint32_t*>(epoch), static_cast<uint32_t*>(done),
+                                static_cast<int*>(error), static_cast<uint16_t*>(out), pieces, tp_wait_limit_ns())
+            : launch_overlapped(allreduce_words_kernel<false>, grid, block, 0, s, p, size_t(slot_words),
+                                static_cast<const uint16_t*>(in), static_cast<uint32_t*>(epoch), static_cast<uint32_t*>(done),
+                                static_cast<int*>(error), static_cast<uint16_t*>(out), pieces, tp_wait_limit_ns());
+    return launch_status("tp_allreduce", err);
 }

@@ -309,6 +309,7 @@ def bench(args, rank: int, world: int, device: torch.device, barrier, reduce_max
                          quantize=quant.quantize_int4_groups)
     results: dict[int, dict] = {}
     nccl_results: dict[int, dict] = {}
+    kept_logits: dict[tuple[str, int], torch.Tensor] = {}  # one step's logits per route and batch
     clocks = None
     stream = torch.cuda.Stream(device)
     batches = [args.batch]
@@ -344,11 +345,13 @@ def bench(args, rank: int, world: int, device: torch.device, barrier, reduce_max
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 logits = model.step(tokens, positions)
+                sampled = logits.argmax(dim=-1)  # greedy sampling stays on the device, inside the graph
             main = headline and batch == args.batch
             steps = args.steps if main else max(5, args.steps // 4)
             for _ in range(max(3, args.warmup if main else 3)):
                 graph.replay()
             torch.cuda.synchronize()
+            kept_logits[(which, batch)] = logits.float().clone()
             barrier()
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
@@ -371,25 +374,55 @@ def bench(args, rank: int, world: int, device: torch.device, barrier, reduce_max
             (results if headline else nccl_results)[batch] = {"tok_s": batch / (ms_step / 1e3), "ms_per_step": ms_step,
                               "GB_s_per_gpu": decode_bytes(cfg, batch, world) / (ms_step / 1e3) / 1e9}
             if main:
-                # End to end: token ids from pinned host memory in, sampled ids back out.
-                host_out = torch.empty(batch, dtype=torch.long).pin_memory()
+                # End to end, as the reference's serving loop runs a step (python/linnet/src/linnet/
+                # serve/__init__.py:1606-1618, :1657-1681): token ids go in from pinned host memory,
+                # the step and its sampling replay as one graph, the sampled ids are copied to
+                # pinned host memory behind it, and the host reads them one step behind (it waits
+                # for step i - 1's copy while step i runs).
+                host_out = [torch.empty(batch, dtype=torch.long).pin_memory() for _ in range(2)]
+                done = [torch.cuda.Event(), torch.cuda.Event()]
+                checksum = 0
                 barrier()
                 t0 = time.perf_counter()
-                for _ in range(steps):
+                for i in range(steps):
                     tokens.copy_(host_tokens, non_blocking=True)
                     graph.replay()
-                    host_out.copy_(logits.argmax(dim=-1), non_blocking=True)
-                    torch.cuda.current_stream().synchronize()
+                    host_out[i % 2].copy_(sampled, non_blocking=True)
+                    done[i % 2].record()
+                    if i > 0:
+                        done[(i - 1) % 2].synchronize()
+                        checksum += int(host_out[(i - 1) % 2][0])
+                done[(steps - 1) % 2].synchronize()
+                checksum += int(host_out[(steps - 1) % 2][0])
                 ms_e2e = reduce_max((time.perf_counter() - t0) * 1e3) / steps
                 e2e = {"value": batch / (ms_e2e / 1e3), "unit": "tok/s", "ms_per_step": ms_e2e,
-                       "h2d_bytes_per_step": batch * 8, "d2h_bytes_per_step": batch * 8}
-            del graph, logits
+                       "h2d_bytes_per_step": batch * 8, "d2h_bytes_per_step": batch * 8,
+                       "how": "ids from pinned host memory, one graph replay (step + argmax), sampled ids to "
+                              "pinned host memory, read one step behind", "checksum": checksum}
+            del graph, logits, sampled
             model.cache_k, model.cache_v = [], []
             torch.cuda.empty_cache()
     peaks_path = Path(__file__).resolve().parents[1] / "MEASURED_PEAKS.json"
     peak = float(json.loads(peaks_path.read_text())["hbm_gbs"]) if peaks_path.exists() else 6650.0
     if peer_reduce is not None and peer_reduce.error():
         raise RuntimeError(f"peer reduction gave up waiting for a rank (code {peer_reduce.error()})")
+    # The peer route against the NCCL route on the same step (same weights, cache and tokens):
+    # parity of the multi-GPU reduction, carried by every multi-GPU bench line.
+    peer_vs_nccl = None
+    if nccl_results:
+        worst, scale_of = 0.0, 0.0
+        per_batch_diff = {}
+        for batch in sorted(nccl_results):
+            a, b = kept_logits[(route, batch)], kept_logits[("nccl", batch)]
+            diff, top = float((a - b).abs().max()), float(b.abs().max())
+            per_batch_diff[str(batch)] = {"max_abs": diff, "max_logit": top}
+            worst, scale_of = max(worst, diff / max(top, 1e-6)), max(scale_of, top)
+        worst = reduce_max(worst)
+        # bf16 sums taken in two different orders through 32 layers: a few bf16 ulps of the logits
+        peer_vs_nccl = {"peer_vs_nccl_max_abs_over_max_logit": worst, "tolerance": 5e-2, "ok": worst <= 5e-2,
+                        "per_batch": per_batch_diff}
+        if not peer_vs_nccl["ok"]:
+            raise SystemExit(f"peer-memory reduction and NCCL disagree: {peer_vs_nccl}")
     main = results[args.batch]
     # per layer: 4 linears, 2 (reduce +) add + norm, rotary + cache write + attention, silu*mul;
     # then the first norm and the output head
@@ -418,6 +451,7 @@ def bench(args, rank: int, world: int, device: torch.device, barrier, reduce_max
         **({"per_batch_nccl_route": {str(b): nccl_results[b] for b in sorted(nccl_results)}}
            if nccl_results else {}),
         **({"peer_reduce_unavailable": peer_unavailable} if peer_unavailable else {}),
+        **({"peer_vs_nccl": peer_vs_nccl} if peer_vs_nccl else {}),
         "e2e": e2e,
         "gpu_launches": args.steps * launches_per_step,
         "clocks": clocks.summary() if clocks else None,

@@ -20,6 +20,20 @@ def _bf16(*tensors: torch.Tensor) -> None:
             raise RuntimeError("glue kernels take contiguous bf16 CUDA tensors")
 
 
+def _positions(positions: torch.Tensor, batch: int, device: torch.device) -> None:
+    """Positions are read on the device as int64: anything else would be misread."""
+    if (not positions.is_cuda or positions.device != device or positions.dtype != torch.int64
+            or not positions.is_contiguous() or positions.numel() != batch):
+        raise ValueError(f"positions must be a contiguous int64 tensor of {batch} entries on {device}, not "
+                         f"{positions.dtype}{list(positions.shape)} on {positions.device}")
+
+
+def decoder_status() -> None:
+    """Raises if a decode-step kernel met a position outside its cache since the last call
+    (synchronises the device; `b200q_decoder_status`)."""
+    _lib.check(_lib.load().b200q_decoder_status())
+
+
 def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float) -> torch.Tensor:
     """`x += delta` in place (when given), returns `rms_norm(x) * weight`."""
     _bf16(x, weight, *([] if delta is None else [delta]))
@@ -36,6 +50,7 @@ def rope_cache(qkv: torch.Tensor, positions: torch.Tensor, cache_k: torch.Tensor
     [B, nkv, S, D] at `positions` and returns q [B, nq, D]."""
     _bf16(qkv, cache_k, cache_v)
     batch = qkv.shape[0]
+    _positions(positions, batch, qkv.device)
     _, _, max_seq, hd = cache_k.shape
     q = torch.empty(batch, nq, hd, device=qkv.device, dtype=qkv.dtype)
     _lib.check(_lib.load().b200q_rope_cache(qkv.data_ptr(), positions.data_ptr(), q.data_ptr(),
@@ -62,6 +77,7 @@ def decode_attention(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tens
     head are a thread-block cluster); more need a scratch tensor and a second, merging launch."""
     _bf16(q, cache_k, cache_v)
     batch, nq, hd = q.shape
+    _positions(positions, batch, q.device)
     _, nkv, max_seq, _ = cache_k.shape
     if splits is None:
         splits = min(8, attention_splits(batch, nkv, max_seq))
@@ -96,6 +112,7 @@ def rope_attention(qkv: torch.Tensor, positions: torch.Tensor, table: torch.Tens
     positions 0..positions[b]; returns [B, nq * D]."""
     _bf16(qkv, cache_k, cache_v)
     batch, _, max_seq, hd = cache_k.shape
+    _positions(positions, batch, qkv.device)
     if splits is None:
         splits = min(8, attention_splits(batch, nkv, max_seq))
     if table.shape != (max_seq, hd // 2, 2) or table.dtype != torch.float32:

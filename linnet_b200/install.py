@@ -19,7 +19,11 @@ What it replaces (all of it is looked up by name at run time in the reference):
    generated source and the interpreter table `NATIVE` call.
 3. `NATIVE["torch.ops.aten._weight_int4pack_mm"]`, the interpreter's int4 entry
    (python/linnet/src/linnet/torch/native.py:417-424, :557).
-4. The `_int4_pack`, `_int4_weight`, `_int4_linear` helpers that every generated module
+4. `linnet.torch.collectives.OneShot`, the small-message all-reduce behind
+   `std.nn.parallel::all_reduce` (python/linnet/src/linnet/torch/collectives.py:56-167): the
+   class `collectives.prepare` builds per group becomes `linnet_b200.tp.OneShot`, whose sums
+   run `b200q_tp_allreduce` over peer memory with bounded waits.
+5. The `_int4_pack`, `_int4_weight`, `_int4_linear` helpers that every generated module
    defines for itself (text at src/backend/torch_source.cpp:1482-1570): they are
    overwritten in each module right after `CompiledLinnetModule.import_source` imports it
    (python/linnet/src/linnet/torch/compiled.py:1035-1038).
@@ -87,6 +91,12 @@ def install() -> None:
         return int4._int4_linear(x, int4._int4_pack(packed, scale, zero), bias, packed, scale, zero)
 
     native.NATIVE["torch.ops.aten._weight_int4pack_mm"] = int4_native
+
+    import linnet.torch.collectives as collectives
+
+    from . import tp
+
+    collectives.OneShot = tp.OneShot
 
     original = compiled.CompiledLinnetModule.import_source
 

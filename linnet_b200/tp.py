@@ -14,6 +14,7 @@ into every peer by `rendezvous`); the kernel uses plain peer stores and local lo
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
@@ -40,6 +41,8 @@ class PeerReduce:
 
     def __init__(self, sites: int, max_rows: int, hidden: int, device: torch.device,
                  group: "dist.ProcessGroup | None" = None, protocol: str | None = None) -> None:
+        # plain peer stores and local loads only: the allocation needs no NVLink multicast binding
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
 
         if sites < 2:
@@ -115,3 +118,73 @@ class PeerReduce:
     def error(self) -> int:
         """0, or 100 + r when a wait for rank r ran out (synchronises the device)."""
         return int(self.state[2 * self.sites].item())
+
+
+ONE_SHOT_BYTES = 128 * 1024  # the reference's limit (python/linnet/src/linnet/parallel.py:53)
+
+
+class OneShot:
+    """A group's buffers for the small-message all-reduce, with the reference's interface
+    (`OneShot`, python/linnet/src/linnet/torch/collectives.py:56-103): built once per group by
+    `collectives.prepare`, a collective call; `one_shot(x)` returns the sum of `x` over the
+    group's ranks.  `install()` puts this class in the reference's place, so a `Shards` card's
+    `std.nn.parallel::all_reduce` runs `b200q_tp_allreduce` for bf16 / f16 messages up to
+    128 KiB whose length is a multiple of 8, in eager code, compiled code and CUDA graphs;
+    anything else goes to NCCL the way the reference sends what its kernel does not cover
+    (collectives.py:159-167).  Sums are taken in f32 in rank order: every rank gets the same
+    bits.  Every wait on a peer is bounded (`b200q_set_wait_limit_ns`)."""
+
+    def __init__(self, group: "dist.ProcessGroup") -> None:
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+
+        self.group = group
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if not 2 <= self.world <= 8:
+            raise RuntimeError(f"the peer-memory all-reduce runs on 2..8 ranks, not {self.world}")
+        # two call sites that alternate; per site [source rank][slot] words of (2 values, epoch)
+        self.slot_words = ONE_SHOT_BYTES // 2 // 2
+        self.area_bytes = self.world * self.slot_words * 8
+        self.memory = symm.empty(2 * self.area_bytes, dtype=torch.uint8, device=self.device)
+        self.memory.zero_()
+        handle = symm.rendezvous(self.memory, group=group.group_name)
+        bases = [int(p) for p in handle.buffer_ptrs]
+        int64s = ctypes.c_int64 * self.world
+        self._areas = [int64s(*[b + s * self.area_bytes for b in bases]) for s in range(2)]
+        self.state = torch.zeros(5, dtype=torch.int32, device=self.device)  # 2 epochs, 2 done counters, error
+        self.site = 0
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group)  # nobody stores into an area before every rank has zeroed its own
+
+    def covers(self, x: torch.Tensor) -> bool:
+        return (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and x.numel() % 8 == 0
+                and 0 < x.numel() * x.element_size() <= ONE_SHOT_BYTES)
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        if not self.covers(x):
+            return self._library(x)
+        x = x.contiguous()
+        out = torch.empty_like(x)
+        site, self.site = self.site, 1 - self.site
+        state = self.state.data_ptr()
+        _lib.check(_lib.load().b200q_tp_allreduce(
+            ctypes.addressof(self._areas[site]), self.slot_words, x.data_ptr(), self.world, self.rank,
+            state + 4 * site, state + 4 * (2 + site), state + 16, out.data_ptr(), x.numel(),
+            _lib.BF16 if x.dtype == torch.bfloat16 else _lib.F16,
+            torch.cuda.current_stream(self.device).cuda_stream))
+        return out
+
+    def _library(self, x: torch.Tensor) -> torch.Tensor:
+        """f32, odd lengths: the group's own backend, as the reference does past its kernel."""
+        if torch.compiler.is_compiling() or torch.cuda.is_current_stream_capturing():
+            from torch.distributed import _functional_collectives as funcol
+
+            return funcol.all_reduce(x, "sum", self.group)
+        out = x.clone(memory_format=torch.contiguous_format)
+        dist.all_reduce(out, group=self.group)
+        return out
+
+    def error(self) -> int:
+        """0, or 100 + r when a wait for rank r ran out (synchronises the device)."""
+        return int(self.state[4].item())
