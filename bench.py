@@ -34,6 +34,7 @@ import json
 import os
 import statistics
 import subprocess
+import tempfile
 import sys
 import threading
 import time
@@ -159,7 +160,7 @@ def reference_run(what: str, *extra: str, timeout: int = 900) -> dict | None:
 
     if not build_ref.available():
         return None
-    home = ROOT / "gpurun_out" / "linnet-home" if (ROOT / "gpurun_out").is_dir() else Path("/tmp/linnet-home")
+    home = Path(tempfile.mkdtemp(prefix="linnet-home-"))
     env = build_ref.environment(home)
     done = subprocess.run([sys.executable, str(ROOT / "oracle" / "run_reference.py"), what, *extra], env=env,
                           capture_output=True, text=True, timeout=timeout)
@@ -637,8 +638,7 @@ def main() -> None:
         # NCCL's log (when NCCL_DEBUG is set) goes to a file beside the output, not to stdout,
         # which carries the one JSON line.
         if os.environ.get("NCCL_DEBUG") and not os.environ.get("NCCL_DEBUG_FILE"):
-            logs = ROOT / "gpurun_out"
-            os.environ["NCCL_DEBUG_FILE"] = str((logs if logs.is_dir() else Path("/tmp")) / "nccl.%h.%p.log")
+            os.environ["NCCL_DEBUG_FILE"] = str(Path(tempfile.gettempdir()) / "nccl.%h.%p.log")
         # plain peer stores only: no NVLS multicast binding of the symmetric memory
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         dist.init_process_group("nccl", device_id=device)

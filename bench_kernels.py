@@ -1,4 +1,4 @@
-"""Per-kernel timings of the decode step (`bench.py --workload kernels`): each kernel alone,
+"""Per-kernel timings of the decode step (`python bench_kernels.py --case ...`): each kernel alone,
 recorded into a CUDA graph over rotating inputs larger than L2 (so every launch streams
 from HBM, as inside a decode step where each layer has its own weights and cache) and
 replayed back to back with programmatic dependent launch, as the decoder runs them.
@@ -9,9 +9,12 @@ most, one kernel family per case.
 
 from __future__ import annotations
 
+import argparse
+import json
+
 import torch
 
-from . import glue, kernels
+from linnet_b200 import glue, kernels, quant
 
 SHAPES = {"qkv": (4096, 6144), "o": (4096, 4096), "gate_up": (4096, 28672), "down": (14336, 4096)}
 
@@ -109,3 +112,57 @@ def run(device: torch.device, case: str, rows: int | None, batch: int | None, tp
     if case in ("linear", "all"):
         results.update(linear(device, (rows,) if rows else (1, 8, 16, 32, 64, 128), tp=tp))
     return results
+
+
+def quantize(device: torch.device, out: int = 8192, depth: int = 8192) -> dict:
+    """The group quantizers on one bf16 tensor larger than L2 (a few weight sets in turn)."""
+    sets = 4
+    ws = [torch.randn(out, depth, device=device, dtype=torch.bfloat16) * 0.015 for _ in range(sets)]
+    results = {}
+    us = _timed(lambda i: quant.quantize_int4_groups(ws[i], 128, scale_dtype="bf16"), sets)
+    nbytes = out * depth * (2 + 0.5 + 3 / 128)
+    results[f"quantize_int4_g128_{out}x{depth}"] = {"us": us, "GB/s": nbytes / us / 1e3}
+    us = _timed(lambda i: quant.quantize_int8_groups(ws[i], depth, "bf16"), sets)
+    nbytes = out * depth * 3 + out * 2
+    results[f"quantize_int8_channel_{out}x{depth}"] = {"us": us, "GB/s": nbytes / us / 1e3}
+    return results
+
+
+def int8(device: torch.device, rows=(1, 4, 16), shapes=((4096, 4096), (4096, 14336))) -> dict:
+    """`int8_linear` (per-channel scales) at decode row counts over weight sets larger than L2."""
+    gen = torch.Generator(device=device).manual_seed(0)
+    results = {}
+    for depth, width in shapes:
+        sets = max(2, min(64, int(300e6 / (depth * width))))
+        ws = [(torch.randint(-127, 128, (width, depth), device=device, dtype=torch.int8, generator=gen),
+               torch.rand(width, device=device, generator=gen) * 0.01 + 0.001) for _ in range(sets)]
+        for m in rows:
+            x = torch.randn(m, depth, device=device, dtype=torch.bfloat16)
+            fn = kernels.gemv8 if m == 1 else kernels.w8a16
+            us = _timed(lambda i: fn(x, ws[i][0], ws[i][1], False, 0, 1), sets)
+            nbytes = depth * width + width * 4 + m * (depth + width) * 2
+            results[f"int8_linear_K{depth}_N{width}_M{m}"] = {"us": us, "GB/s": nbytes / us / 1e3}
+    return results
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__.splitlines()[0])
+    parser.add_argument("--case", default="all", choices=["attention", "glue", "linear", "quantize", "int8", "all"])
+    parser.add_argument("--rows", type=int, default=None)
+    parser.add_argument("--batch", type=int, default=None)
+    parser.add_argument("--tp", type=int, default=1)
+    args = parser.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench_kernels.py needs a CUDA device")
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    results = run(device, args.case, args.rows, args.batch, args.tp)
+    if args.case in ("quantize", "all"):
+        results.update(quantize(device))
+    if args.case in ("int8", "all"):
+        results.update(int8(device, (args.rows,) if args.rows else (1, 4, 16)))
+    print(json.dumps(results, indent=1))
+
+
+if __name__ == "__main__":
+    main()

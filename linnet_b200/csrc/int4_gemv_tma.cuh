@@ -1,0 +1,584 @@
+// int4-g128 decode kernel, up to 16 activation rows: ONE block per multiprocessor, the weights
+// brought in by the TMA unit, the arithmetic on warps that never issue a weight load.
+//
+//   y[m, n] = sum_g scale[n, g] * ( sum_{k in g} x[m, k] (magic + q[n, k])  -  (magic + zero[n, g]) X[m, g] )
+//   X[m, g] = sum_{k in g} x[m, k]
+//
+// magic + q (128 + q in bf16, 1024 + q in f16) is what one LOP3 makes of a pair of nibbles,
+// and it is exact, so the tensor-core sums are sums of exact products in f32; the zero point
+// costs one multiply-add per k-block with X, which the block computes once in f32 while it
+// stages the activations.  The result differs from the reference's torch path ((q - zero) *
+// scale rounded to the 16-bit type per weight, python/linnet/src/linnet/torch/native.py:417-424)
+// by the rounding noise of its weights only; EXACT = true keeps that rounding, weight for
+// weight, in the same kernel.
+//
+// Layout of the work (weights in the checkpoint layout, nothing repacked):
+//   * W is seen through a 3-D tensor map: 64 bytes of a k-block (128 inputs) innermost, then
+//     the rows (stride K/2 bytes), then the k-blocks of a row (stride 64 bytes).  One box is
+//     an ITEM: 16 rows x KB k-blocks, landing in shared memory as [KB][16 rows][64 bytes], so
+//     that the 16-byte reads of a quarter warp (rows g, g+1 and the four quarters of a k-block)
+//     cover all 32 banks once;
+//   * the grid has one block per multiprocessor; block b owns the 16-row tiles
+//     [b * tiles / grid, (b + 1) * tiles / grid).  WPT warps share a tile, each taking OPC
+//     consecutive items of its K, and TPC = WARPS / WPT tiles are in work at a time;
+//   * one extra warp is the producer: a single thread issues every item's box into a ring of
+//     shared-memory stages, in the order the consumers will want them, as deep as shared
+//     memory allows (the whole share of a multiprocessor, some 200 KB, is in flight from the
+//     first microsecond, ahead even of the wait on the previous kernel: weights are constants);
+//   * the block stages ALL activations once: [rows x K] 16-bit values, permuted to the
+//     (k, k+4) pairing of the A fragments and stored as B fragments of mma.m16n8k16, with the
+//     per-group sums X beside them;
+//   * the warps of a tile add up their partial sums in the stages they have just emptied,
+//     behind a named barrier of their own: no thread-block cluster, no atomics, no global scratch.
+//
+// Every wait on a shared-memory barrier is bounded: after about a second the waiting warp
+// records a code in the device's status word, and it and every other warp finish without
+// further waiting (the output is then incomplete and the status says so).
+#pragma once
+
+#include <cuda.h>
+
+#include "gemv_common.cuh"
+#include "umma.cuh"
+
+namespace b200q {
+
+struct TmaArgs {
+    const void* x;          // [M, K]
+    const void* scale;      // [N, K/128]
+    const uint8_t* zero;    // [N, K/128]
+    void* y;                // [M, N]
+    int M, K, N;
+    int tiles;              // ceil(N / 16)
+    int wpt;                // warps per tile
+    int opc;                // items per warp and tile; K == 128 * KB * opc * wpt
+    int tpc;                // tiles in work at a time per block = WARPS / wpt
+    int stages;             // ring stages of KB KiB
+    int overlap;            // launched with programmatic stream serialization
+    int early;              // dependents may start as soon as this kernel has started
+    int* status;            // device word of expired waits
+};
+
+// Shared memory by its 32-bit address (one register instead of a generic pointer's two).
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float2 lds64f(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float lds32f(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
+    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void sts32f(uint32_t addr, float v) {
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void named_barrier(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// d = a * b (accumulator starts at zero).
+template <typename T>
+__device__ __forceinline__ void mma_first(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma_first<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
+}
+template <>
+__device__ __forceinline__ void mma_first<__half>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                                  uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
+// One box of the weight map -> shared memory; the barrier receives the bytes.
+__device__ __forceinline__ void tma_item(uint32_t dst, const CUtensorMap* map, int row, int kblock, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+        "l"(map), "r"(0), "r"(row), "r"(kblock), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ bool bar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false (and the status word set) after about a second, or as soon as another
+// warp of the device has given up.
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+    if (bar_try_wait(bar, parity)) return true;
+    const uint64_t start = umma::global_timer_ns();
+    for (uint32_t spins = 0;; ++spins) {
+        if (bar_try_wait(bar, parity)) return true;
+        if ((spins & 1023u) == 1023u) {
+            if (*reinterpret_cast<volatile int*>(status) != 0) return false;
+            if (umma::global_timer_ns() - start > 1000000000ull) {
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void bar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void bar_expect(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+// Offsets (bytes) of the shared-memory regions: ring of stages, barriers, per-warp scales
+// and zero points, B fragments of the activations, their group sums.
+struct TmaLayout {
+    uint32_t bars, sz, xs, xsum, total;
+    uint32_t xrow;    // bytes of one activation row in xs (padded so that rows g, g+1 fall on different banks)
+    int xpairs;       // pairs of rows in xsum
+};
+template <int MB, int WARPS, int KB>
+__host__ __device__ inline TmaLayout tma_layout(int M, int K, int stages) {
+    TmaLayout l;
+    const int groups = K / 128;
+    l.bars = uint32_t(stages) * (KB * 1024);
+    l.sz = (l.bars + uint32_t(stages + WARPS) * 8 + 15u) & ~15u;  // 16-byte stores
+    l.xs = (l.sz + WARPS * 16 * KB * 3 + 127u) & ~127u;
+    l.xrow = uint32_t(groups) * 256 + (M > 1 ? 64 : 0);
+    l.xpairs = (M + 1) / 2;
+    l.xsum = l.xs + uint32_t(M) * l.xrow;
+    l.total = l.xsum + uint32_t(l.xpairs) * groups * 8;
+    return l;
+}
+
+// MB: blocks of 8 activation rows (1 or 2).  WARPS: consumer warps (one more is the producer).
+// KB: k-blocks per item (8 or 4).  EXACT: dequantize every weight as the reference does.
+template <typename T, int MB, int WARPS, int KB, bool EXACT>
+__global__ void __launch_bounds__((WARPS + 1) * 32, 1)
+int4_gemv_tma_kernel(const __grid_constant__ CUtensorMap wmap, const TmaArgs a) {
+    static_assert(KB == 8 || KB == 4, "k-blocks per item");
+    using H = Half16<T>;
+    constexpr int MP = MB * 8;
+    constexpr uint32_t kItem = KB * 1024;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+    const int g = lane / 4, t = lane % 4;
+    const int M = a.M, K = a.K, N = a.N;
+    const int groups = K / 128;
+    const int S = a.stages;
+    const TmaLayout lay = tma_layout<MB, WARPS, KB>(M, K, S);
+    const uint32_t smem0 = uint32_t(__cvta_generic_to_shared(smem));
+    // Barriers: empty[s] (a stage has been read; only the producer waits on it, lap after lap)
+    // and ready[w] (the bytes of consumer w's next item have landed; only w waits on it, item
+    // after item).  Each has one waiter that follows its phases in order, so a parity never
+    // stands for the wrong phase.
+    const uint32_t empty0 = smem0 + lay.bars, ready0 = empty0 + uint32_t(S) * 8;
+
+    // This block's tiles; the consumers in use and the rounds they make.
+    const int t0 = int((uint32_t(blockIdx.x) * uint32_t(a.tiles)) / gridDim.x);
+    const int t1 = int((uint32_t(blockIdx.x + 1) * uint32_t(a.tiles)) / gridDim.x);
+    const int active = a.tpc * a.wpt;
+    const int rounds = (t1 - t0 + a.tpc - 1) / a.tpc;
+
+    if (int(threadIdx.x) < S + WARPS) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(empty0 + threadIdx.x * 8));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == WARPS) {
+        // ---- producer: items in the order (round, item of the tile, consumer) ----------------
+        if (lane != 0) return;
+        if (a.overlap) pdl_launch_dependents();  // this thread never waits on the previous kernel: weights are constants
+        int s = 0;
+        uint32_t lap = 0;  // times the ring has been gone round
+        bool ok = true;
+        int n = 0;         // items each consumer has been sent
+        for (int round = 0; round < rounds && ok; ++round) {
+            for (int o = 0; o < a.opc && ok; ++o, ++n) {
+                int w = 0;
+                for (int ts = 0; ts < a.tpc && ok; ++ts) {
+                    const int tile = t0 + round * a.tpc + ts;
+                    for (int part = 0; part < a.wpt; ++part, ++w) {
+                        const uint32_t empty = empty0 + s * 8, ready = ready0 + w * 8;
+                        if (lap > 0) ok = bar_wait(empty, (lap - 1) & 1, a.status, 11);
+                        if (!ok) break;
+                        if (tile < t1) {
+                            // one arrival a phase: the consumer's last item must have landed
+                            if (n > 0) ok = bar_wait(ready, (n - 1) & 1, a.status, 13);
+                            if (!ok) break;
+                            bar_expect(ready, kItem);
+                            tma_item(smem0 + uint32_t(s) * kItem, &wmap, tile * 16, (part * a.opc + o) * KB, ready);
+                        } else {  // nobody takes this one: keep the stage's phases in step
+                            bar_arrive(empty);
+                        }
+                        if (++s == S) {
+                            s = 0;
+                            ++lap;
+                        }
+                    }
+                }
+            }
+        }
+        return;
+    }
+
+    // ---- consumers ---------------------------------------------------------------------------
+    const bool works = warp < active && t0 + warp / a.wpt < t1;
+    const int ts = warp / a.wpt, part = warp % a.wpt;
+    const uint32_t my_sz = smem0 + lay.sz + uint32_t(warp) * (16 * KB * 3);
+    const uint32_t xs = smem0 + lay.xs, xsum = smem0 + lay.xsum;
+
+    // Scales (lanes 0-15: KB x 2 bytes of row `lane`) and zero points (lanes 16-31: KB bytes of
+    // row `lane - 16`) of one item, through registers.
+    auto load_sz = [&](int tile, int item, uint4& v) {
+        const int r = min(tile * 16 + (lane & 15), N - 1);  // ragged tile: clamp
+        const size_t at = size_t(r) * groups + size_t(item) * KB;
+        if (lane < 16) {
+            const uint8_t* p = static_cast<const uint8_t*>(a.scale) + at * 2;
+            if (KB == 8) v = __ldg(reinterpret_cast<const uint4*>(p));
+            else { const uint2 h = __ldg(reinterpret_cast<const uint2*>(p)); v.x = h.x; v.y = h.y; }
+        } else {
+            const uint8_t* p = a.zero + at;
+            if (KB == 8) { const uint2 h = __ldg(reinterpret_cast<const uint2*>(p)); v.x = h.x; v.y = h.y; }
+            else v.x = __ldg(reinterpret_cast<const uint32_t*>(p));
+        }
+    };
+    auto store_sz = [&](const uint4& v) {
+        if (lane < 16) {
+            const uint32_t dst = my_sz + lane * (KB * 2);
+            if (KB == 8) sts128(dst, v);
+            else sts64(dst, v.x, v.y);
+        } else {
+            const uint32_t dst = my_sz + 16 * KB * 2 + (lane - 16) * KB;
+            if (KB == 8) sts64(dst, v.x, v.y);
+            else sts32(dst, v.x);
+        }
+    };
+
+    if (a.overlap) {
+        if (a.early) pdl_launch_dependents();
+        pdl_wait();  // activations may come from the kernel ahead of this one
+    }
+
+    // Activations: M * (K / 128) * 16 pieces of 16 bytes, the 16 pieces of a (row, k-block) in
+    // 16 consecutive lanes, which also add up the k-block's inputs.
+    uint4 szr = make_uint4(0, 0, 0, 0);
+    {
+        const uint4* xg = below_pdl_wait(static_cast<const uint4*>(a.x));
+        const int pieces = M * groups * 16;
+        constexpr int threads = WARPS * 32;
+        const int me = int(threadIdx.x);
+        auto where = [&](int e, int& m, int& j, int& c) {
+            const int r = e >> 4;  // (row, k-block)
+            m = M == 1 ? 0 : r / groups;
+            j = r - m * groups;
+            c = e & 15;  // piece of the k-block: lane t = c/4, word i = c%4
+        };
+        auto stage = [&](int e, const uint4& raw) {
+            const bool live = e < pieces;
+            int m, j, c;
+            where(e, m, j, c);
+            if (!EXACT) {
+                float sum = (H::to_float(raw.x & 0xFFFFu) + H::to_float(raw.x >> 16)) +
+                            (H::to_float(raw.y & 0xFFFFu) + H::to_float(raw.y >> 16));
+                sum += (H::to_float(raw.z & 0xFFFFu) + H::to_float(raw.z >> 16)) +
+                       (H::to_float(raw.w & 0xFFFFu) + H::to_float(raw.w >> 16));
+#pragma unroll
+                for (int d = 8; d >= 1; d >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, d);
+                if (live && c == 0) sts32f(xsum + (uint32_t(m / 2) * groups + j) * 8 + (m % 2) * 4, sum);
+            }
+            if (live) {
+                uint4 out;
+                out.x = __byte_perm(raw.x, raw.z, 0x5410);  // (x0, x4)
+                out.y = __byte_perm(raw.x, raw.z, 0x7632);  // (x1, x5)
+                out.z = __byte_perm(raw.y, raw.w, 0x5410);  // (x2, x6)
+                out.w = __byte_perm(raw.y, raw.w, 0x7632);  // (x3, x7)
+                sts128(xs + uint32_t(m) * lay.xrow + uint32_t(j) * 256 + (c % 4) * 64 + (c / 4) * 16, out);
+            }
+        };
+        auto load = [&](int e) {
+            uint4 raw = make_uint4(0, 0, 0, 0);
+            if (e < pieces) {
+                int m, j, c;
+                where(e, m, j, c);
+                raw = ld_mutable(xg + (size_t(m) * K + size_t(j) * 128) / 8 + c);
+            }
+            return raw;
+        };
+        constexpr int kFirst = MB == 1 ? 4 : 8;  // pieces a thread has in flight at first
+        uint4 raw[kFirst];
+#pragma unroll
+        for (int u = 0; u < kFirst; ++u) raw[u] = load(u * threads + me);
+        if (works) load_sz(t0 + ts, part * a.opc, szr);
+#pragma unroll
+        for (int u = 0; u < kFirst; ++u)
+            if (u * threads < pieces) stage(u * threads + me, raw[u]);
+        for (int base = kFirst * threads; base < pieces; base += 4 * threads) {  // four loads in flight a thread
+            uint4 more[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) more[u] = load(base + u * threads + me);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) stage(base + u * threads + me, more[u]);
+        }
+    }
+    named_barrier(15, WARPS * 32);  // the consumers only: the producer is on its own way
+    if (!works) return;
+
+    // ---- this warp's items --------------------------------------------------------------------
+    const uint32_t kMask = 0x000F000Fu;
+    uint16_t* y = static_cast<uint16_t*>(a.y);
+    const uint32_t wl = uint32_t(g) * 64 + t * 16;                      // this lane's bytes of a k-block's row g
+    const uint32_t x_lane0 = xs + uint32_t(min(g, M - 1)) * lay.xrow + t * 16;
+    const uint32_t x_lane1 = xs + uint32_t(min(8 + g, M - 1)) * lay.xrow + t * 16;  // rows past the last re-read it
+    const uint32_t xsum_lane0 = xsum + uint32_t(min(t, lay.xpairs - 1)) * groups * 8;
+    const uint32_t xsum_lane1 = xsum + uint32_t(min(4 + t, lay.xpairs - 1)) * groups * 8;
+    const uint32_t my_sc = my_sz + g * (KB * 2), my_zp = my_sz + 16 * KB * 2 + g * KB;
+    bool ok = true;
+    int n = 0;                      // items this warp has taken
+    int s = warp % S;               // stage of its next item: (n * active + warp) % S
+    const int s_step = active % S;
+    const uint32_t ready = ready0 + warp * 8;
+    for (int tile = t0 + ts; tile < t1; tile += a.tpc) {
+        float acc[MB][2][4];
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+            for (int s = 0; s < 2; ++s)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[mb][s][i] = 0.0f;
+        uint32_t stage_addr = 0;
+        int s_mine = 0;
+        for (int o = 0; o < a.opc; ++o, ++n) {
+            const int item = part * a.opc + o;
+            // scales and zero points: this item's from the registers, the next one's on their way
+            __syncwarp();
+            store_sz(szr);
+            __syncwarp();
+            {
+                const bool more_here = o + 1 < a.opc;
+                const int next_tile = more_here ? tile : tile + a.tpc;
+                if (next_tile < t1) load_sz(next_tile, more_here ? item + 1 : part * a.opc, szr);
+            }
+            s_mine = s;
+            s += s_step;
+            if (s >= S) s -= S;
+            stage_addr = smem0 + uint32_t(s_mine) * kItem;
+            if (ok) ok = bar_wait(ready, uint32_t(n) & 1, a.status, 12);
+            const uint32_t wq = stage_addr + wl;
+            const uint32_t xq0 = x_lane0 + uint32_t(item) * (KB * 256), xq1 = x_lane1 + uint32_t(item) * (KB * 256);
+            const uint32_t xsq0 = xsum_lane0 + uint32_t(item) * (KB * 8), xsq1 = xsum_lane1 + uint32_t(item) * (KB * 8);
+#pragma unroll
+            for (int j = 0; j < KB; ++j) {
+                const uint4 q0 = lds128(wq + j * 1024), q1 = lds128(wq + j * 1024 + 512);
+                uint32_t sbits[2], zbyte[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(sbits[h]) : "r"(my_sc + (h * 8 * KB + j) * 2));
+                    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(zbyte[h]) : "r"(my_zp + h * 8 * KB + j));
+                }
+                uint32_t sc[2] = {0, 0}, bias[2] = {0, 0};
+                if (EXACT) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        sc[h] = sbits[h] * 0x00010001u;
+                        bias[h] = H::kMagic + zbyte[h] * 0x00010001u;  // (magic + zero, magic + zero)
+                    }
+                }
+                float ka[MB][4];  // !EXACT: this k-block's sums
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    uint4 b[MB];
+                    b[0] = lds128(xq0 + j * 256 + i * 64);
+                    if (MB > 1) b[MB - 1] = lds128(xq1 + j * 256 + i * 64);
+                    const uint32_t w0 = i == 0 ? q0.x : i == 1 ? q0.y : i == 2 ? q0.z : q0.w;
+                    const uint32_t w1 = i == 0 ? q1.x : i == 1 ? q1.y : i == 2 ? q1.z : q1.w;
+                    uint32_t f0[4], f1[4];  // (k0,k4) (k1,k5) (k2,k6) (k3,k7) of rows g, g+8
+                    f0[0] = lop3_and_or(w0, kMask, H::kMagic);
+                    f0[1] = lop3_and_or(w0 >> 4, kMask, H::kMagic);
+                    f0[2] = lop3_and_or(w0 >> 8, kMask, H::kMagic);
+                    f0[3] = lop3_and_or(w0 >> 12, kMask, H::kMagic);
+                    f1[0] = lop3_and_or(w1, kMask, H::kMagic);
+                    f1[1] = lop3_and_or(w1 >> 4, kMask, H::kMagic);
+                    f1[2] = lop3_and_or(w1 >> 8, kMask, H::kMagic);
+                    f1[3] = lop3_and_or(w1 >> 12, kMask, H::kMagic);
+                    if (EXACT) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            f0[e] = sub_mul<T>(f0[e], bias[0], sc[0]);
+                            f1[e] = sub_mul<T>(f1[e], bias[1], sc[1]);
+                        }
+                    }
+                    const uint32_t a_lo[4] = {f0[0], f1[0], f0[1], f1[1]};
+                    const uint32_t a_hi[4] = {f0[2], f1[2], f0[3], f1[3]};
+#pragma unroll
+                    for (int mb = 0; mb < MB; ++mb) {
+                        if (EXACT) {
+                            H::mma(acc[mb][0], a_lo, b[mb].x, b[mb].y);
+                            H::mma(acc[mb][1], a_hi, b[mb].z, b[mb].w);
+                        } else {
+                            if (i == 0) mma_first<T>(ka[mb], a_lo, b[mb].x, b[mb].y);
+                            else H::mma(ka[mb], a_lo, b[mb].x, b[mb].y);
+                            H::mma(ka[mb], a_hi, b[mb].z, b[mb].w);
+                        }
+                    }
+                }
+                if (!EXACT) {
+                    // y += scale * (sums - (magic + zero) * X), rows g (0, 1) and g+8 (2, 3)
+                    float s[2], nz[2];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        s[h] = H::to_float(sbits[h]);
+                        // 2^23 + zero as f32 bits, then (2^23 - magic) - that = -(magic + zero)
+                        nz[h] = (8388608.0f - H::kBias) - __uint_as_float(zbyte[h] | 0x4B000000u);
+                    }
+#pragma unroll
+                    for (int mb = 0; mb < MB; ++mb) {
+                        const float2 X = lds64f((mb == 0 ? xsq0 : xsq1) + j * 8);
+                        acc[mb][0][0] = fmaf(s[0], fmaf(nz[0], X.x, ka[mb][0]), acc[mb][0][0]);
+                        acc[mb][0][1] = fmaf(s[0], fmaf(nz[0], X.y, ka[mb][1]), acc[mb][0][1]);
+                        acc[mb][0][2] = fmaf(s[1], fmaf(nz[1], X.x, ka[mb][2]), acc[mb][0][2]);
+                        acc[mb][0][3] = fmaf(s[1], fmaf(nz[1], X.y, ka[mb][3]), acc[mb][0][3]);
+                    }
+                }
+            }
+            if (o + 1 < a.opc) {  // hand the stage back; the tile's last one carries the partial sums first
+                __syncwarp();
+                if (lane == 0) bar_arrive(empty0 + s_mine * 8);
+            }
+        }
+        const bool last_tile = tile + a.tpc >= t1;
+        if (last_tile && a.overlap && !a.early) pdl_launch_dependents();
+
+        // The tile's partial sums meet in the stages its warps have just read: each warp writes
+        // 16 x MP floats into its own, the tile's first warp adds them up, stores y and hands
+        // all the stages back to the producer.
+        __syncwarp();
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) {
+            const uint32_t dst = stage_addr + (g * MP + mb * 8 + 2 * t) * 4;
+            sts32f(dst, acc[mb][0][0] + (EXACT ? acc[mb][1][0] : 0.0f));
+            sts32f(dst + 4, acc[mb][0][1] + (EXACT ? acc[mb][1][1] : 0.0f));
+            sts32f(dst + 8 * MP * 4, acc[mb][0][2] + (EXACT ? acc[mb][1][2] : 0.0f));
+            sts32f(dst + 8 * MP * 4 + 4, acc[mb][0][3] + (EXACT ? acc[mb][1][3] : 0.0f));
+        }
+        umma::fence_proxy_async();  // these writes come before the TMA unit's next ones to the stage
+        if (a.wpt > 1) named_barrier(1 + ts, a.wpt * 32);
+        else __syncwarp();
+        if (part == 0) {
+            for (int e = lane; e < 16 * M; e += 32) {
+                const int row = e % 16, m = e / 16;
+                float sum = 0.0f;
+                for (int w = 0; w < a.wpt; ++w) {  // the siblings' stages follow this warp's round the ring
+                    const int sw = s_mine + w < S ? s_mine + w : s_mine + w - S;
+                    sum += lds32f(smem0 + uint32_t(sw) * kItem + (row * MP + m) * 4);
+                }
+                const int nrow = tile * 16 + row;
+                if (nrow < N) y[size_t(m) * N + nrow] = H::from_float(sum);
+            }
+            __syncwarp();
+            if (lane < a.wpt) bar_arrive(empty0 + (s_mine + lane < S ? s_mine + lane :
+                                                          s_mine + lane - S) * 8);
+        }
+    }
+}
+
+// Launch geometry; false when the kernel does not take the shape.
+template <int MB, int WARPS, int KB>
+inline bool tma_plan(TmaArgs& a, int G, size_t* smem) {
+    if (G != 128 || a.K % (128 * KB) != 0 || a.M > MB * 8 || a.M < 1) return false;
+    if (!aligned(a.scale, KB * 2) || !aligned(a.zero, KB) || !aligned(a.x, 16)) return false;
+    const int runs = a.K / (128 * KB);
+    // as many warps per tile as there are items, up to the block; else whole items per warp
+    int opc = 1;
+    while (runs % opc != 0 || runs / opc > WARPS) ++opc;
+    a.opc = opc;
+    a.wpt = runs / opc;
+    if (a.wpt > 32) return false;  // the tile's first warp hands one stage back per lane
+    a.tpc = WARPS / a.wpt;
+    if (a.wpt > 1 && a.tpc > 14) a.tpc = 14;  // named barriers 1..14 (15 is the consumers')
+    const TmaLayout fixed = tma_layout<MB, WARPS, KB>(a.M, a.K, 0);
+    const long budget = 226L * 1024 - long(fixed.total);
+    long stages = (budget - WARPS * 8 - 16) / (KB * 1024 + 8);
+    // The stages of a tile's last items go back to the producer together, so the ring must hold
+    // more than one tile's worth of warps; and a shallow ring is another kernel's shape.
+    if (stages < 4 || stages <= a.wpt) return false;
+    if (stages > 96) stages = 96;
+    a.stages = int(stages);
+    *smem = tma_layout<MB, WARPS, KB>(a.M, a.K, a.stages).total;
+    return true;
+}
+
+// The weights [N, K/2] as 64-byte pieces: (byte of the k-block, row, k-block of the row).
+template <int KB>
+inline bool tma_weight_map(CUtensorMap* map, const uint8_t* packed, int N, int K,
+                           CUtensorMapL2promotion promotion = CU_TENSOR_MAP_L2_PROMOTION_NONE) {
+    const umma::EncodeTiled encode = umma::encode_tiled();
+    if (encode == nullptr || !aligned(packed, 16)) return false;
+    const cuuint64_t dims[3] = {64, cuuint64_t(N), cuuint64_t(K / 128)};
+    const cuuint64_t strides[2] = {cuuint64_t(K / 2), 64};
+    const cuuint32_t box[3] = {64, 16, KB};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(packed), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, promotion,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename T, int MB, int WARPS, int KB, bool EXACT>
+int32_t launch_tma(const TmaArgs& a, const uint8_t* packed, size_t smem, int sms, cudaStream_t stream,
+                   CUtensorMapL2promotion promotion = CU_TENSOR_MAP_L2_PROMOTION_NONE) {
+    auto kernel = int4_gemv_tma_kernel<T, MB, WARPS, KB, EXACT>;
+    CUtensorMap map;
+    if (!tma_weight_map<KB>(&map, packed, a.N, a.K, promotion)) return fail("int4_gemv: the weight tensor map was refused");
+    const cudaError_t attr_err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
+    if (attr_err != cudaSuccess) {
+        cudaGetLastError();
+        return fail("int4_gemv: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(attr_err));
+    }
+    // One block per multiprocessor (each takes an equal share of the tiles, several rounds of
+    // `tpc` if need be), fewer when there are fewer tiles than multiprocessors.
+    const int grid = a.tiles < sms ? a.tiles : sms;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(unsigned(grid), 1, 1);
+    config.blockDim = dim3((WARPS + 1) * 32, 1, 1);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attr;
+    config.numAttrs = a.overlap ? 1 : 0;
+    const cudaError_t err = cudaLaunchKernelEx(&config, kernel, map, a);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return fail("int4_gemv: launch failed: %s", cudaGetErrorString(err));
+    }
+    return B200Q_OK;
+}
+
+}  // namespace b200q

@@ -108,6 +108,12 @@ def test_loader_route_on_gpu(reference_run):
             assert got.shape == want.shape, (mode, name)
             if name.startswith("llama4"):
                 assert (got - want).abs().max().item() <= 2e-2 * peak, (mode, name)
+            elif name == "lin8/rows40":
+                # More than 32 rows of a per-channel int8 layer under numerics="fast": on a GPU the
+                # reference rounds the activations to 8 bits too (quantized.py:187-189), which its
+                # CPU run, the one compared with here, never does.  The W8A8 product itself is
+                # pinned bit for bit against the oracle in test_w8a8_gpu.py.
+                assert (got - want).abs().max().item() <= 3e-2 * want.abs().max().item(), (mode, name)
             else:
                 torch.testing.assert_close(got, want, rtol=1e-2, atol=1e-2, msg=lambda m: f"{mode}/{name}: {m}")
             checked += 1
