@@ -16,7 +16,8 @@ import torch
 
 from linnet_b200 import glue, kernels, quant
 
-SHAPES = {"qkv": (4096, 6144), "o": (4096, 4096), "gate_up": (4096, 28672), "down": (14336, 4096)}
+SHAPES = {"qkv": (4096, 6144), "o": (4096, 4096), "gate_up": (4096, 28672), "down": (14336, 4096),
+          "up": (4096, 14336)}  # "up" is the headline shape of bench.py
 
 
 def _timed(fn, sets: int, reps: int = 3) -> float:
@@ -101,7 +102,8 @@ def linear(device: torch.device, rows=(1, 8, 16, 32, 64, 128), shapes=None, tp: 
     return out
 
 
-def run(device: torch.device, case: str, rows: int | None, batch: int | None, tp: int = 1) -> dict:
+def run(device: torch.device, case: str, rows: int | None, batch: int | None, tp: int = 1,
+        shapes=None) -> dict:
     """`case`: attention | glue | linear | all.  `rows` / `batch` narrow the sweep to one size;
     `tp` times the shapes one rank of a tensor-parallel group of that size holds."""
     results: dict = {}
@@ -110,7 +112,7 @@ def run(device: torch.device, case: str, rows: int | None, batch: int | None, tp
     if case in ("glue", "all"):
         results.update(glue_kernels(device, (batch,) if batch else (1, 8, 64)))
     if case in ("linear", "all"):
-        results.update(linear(device, (rows,) if rows else (1, 8, 16, 32, 64, 128), tp=tp))
+        results.update(linear(device, (rows,) if rows else (1, 8, 16, 32, 64, 128), shapes=shapes, tp=tp))
     return results
 
 
@@ -151,12 +153,15 @@ def main() -> None:
     parser.add_argument("--rows", type=int, default=None)
     parser.add_argument("--batch", type=int, default=None)
     parser.add_argument("--tp", type=int, default=1)
+    parser.add_argument("--shape", default=None, choices=sorted(SHAPES), help="one linear shape instead of all")
+    parser.add_argument("--numerics", default="fast", choices=["fast", "exact"])
     args = parser.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("bench_kernels.py needs a CUDA device")
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
-    results = run(device, args.case, args.rows, args.batch, args.tp)
+    kernels.set_int4_numerics(args.numerics)
+    results = run(device, args.case, args.rows, args.batch, args.tp, [args.shape] if args.shape else None)
     if args.case in ("quantize", "all"):
         results.update(quantize(device))
     if args.case in ("int8", "all"):

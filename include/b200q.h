@@ -89,13 +89,15 @@ int32_t b200q_int4_gemv(const void* x, const uint8_t* packed, const void* scale,
  *   B200Q_EXACT_WEIGHTS   every weight is (q - zero) * scale computed in f32 and rounded
  *     once to the 16-bit type before the product: bit for bit the weight the reference's
  *     torch path multiplies by (python/linnet/src/linnet/torch/native.py:417-424).
- *     Without the flag, for groups of 128 and up to 16 rows, zero point and scale are
- *     applied in f32 to each group's sum of exact products instead; that is closer to
- *     exact arithmetic and differs from the reference by the rounding noise of its
- *     weights (2^-9 relative per weight: sigma 1.4e-3 per output at K=4096 with weights
- *     ~N(0, 0.02) and inputs ~N(0, 1), against the 1e-2 tolerance), at half the
- *     instructions.  The reference selects these kernels under its `fast` numerics
- *     policy only (src/opt/candidates.cpp:28-33).
+ *     Without the flag, for groups of 128 and one or two rows (where it is the faster
+ *     kernel), zero point and scale are applied in f32 to each group's sum of exact
+ *     products instead; that is closer to exact arithmetic and differs from the reference
+ *     by the rounding noise of its weights (2^-9 relative per weight: sigma 1.4e-3 per
+ *     output at K=4096 with weights ~N(0, 0.02) and inputs ~N(0, 1), against the 1e-2
+ *     tolerance).  That kernel's weights come through the TMA unit into a ring of
+ *     shared-memory stages; its waits on the ring are bounded, and one that expires is
+ *     reported by b200q_int4_gemm_status().  The reference selects these kernels under
+ *     its `fast` numerics policy only (src/opt/candidates.cpp:28-33).
  *   B200Q_EARLY_DEPENDENTS   the kernels after this one in the stream may start (up to
  *     their own wait on this one's results) as soon as this one has started, instead of
  *     when its last weights are in: pays when the next kernel is another product that can
@@ -117,9 +119,10 @@ int32_t b200q_int4_gemm(const void* x, const uint8_t* packed, const void* scale,
                         const uint8_t* zero, void* y, int64_t rows, int64_t in,
                         int64_t out, int64_t group, int32_t dtype, void* stream);
 
-/* Synchronises the device and reports whether any b200q_int4_gemm launch on it gave
- * up on one of its bounded waits (B200Q_ERROR, with the waiting role in the message);
- * such a launch leaves its output incomplete but the context usable.  Reporting clears
+/* Synchronises the device and reports whether any launch on it of a kernel with a
+ * shared-memory pipeline (b200q_int4_gemm, b200q_int8_mm, the one- and two-row kernel of
+ * b200q_int4_gemv / b200q_int4_linear) gave up on one of its bounded waits (B200Q_ERROR,
+ * with the waiting role in the message); such a launch leaves its output incomplete but the context usable.  Reporting clears
  * the condition (until then later launches cut their waits short).  No reference
  * counterpart: the reference's kernels spin without a bound. */
 int32_t b200q_int4_gemm_status(void);

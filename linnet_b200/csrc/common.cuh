@@ -54,6 +54,10 @@ bool first_use_on_device(const void* kernel);
 // alone; b200q_decoder_status() reports and clears it.  The word lives in decoder_glue.cu;
 // kernels get its device address as an argument.  nullptr if the address cannot be had.
 int* decoder_error_word();
+// Device address of the word that kernels with shared-memory pipelines (the tensor-core GEMMs,
+// the TMA decode kernel) set when one of their bounded waits expires; read and cleared by
+// b200q_int4_gemm_status().  Null when the device cannot be asked.
+int* gemm_error_word();
 __device__ __forceinline__ void record_bad_position(int* word, int row) {
     if (word != nullptr) atomicCAS(word, 0, 1 + row);
 }

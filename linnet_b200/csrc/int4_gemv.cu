@@ -27,7 +27,7 @@
 
 #include "gemv_common.cuh"
 #include "int4_gemv_oct.cuh"
-#include "int4_gemv_sm.cuh"
+#include "int4_gemv_tma.cuh"
 #include "int4_gemv_rows.cuh"
 
 namespace b200q {
@@ -425,34 +425,28 @@ bool run_oct(const GemvArgs& a, cudaStream_t stream, int32_t* status) {
     return true;
 }
 
-// The one-block-per-multiprocessor kernel (int4_gemv_sm.cuh) for group 128 and up to 16 rows:
-// the default with post-scaled sums, and with B200Q_EXACT_WEIGHTS where it takes the shape.
-// Three ring slots a lane keep HBM busy (see int4_gemv_sm.cuh on why not more); two where the
-// staged activations (2 KB per row and 1024 inputs) leave no room for three.
-template <typename T, bool EXACT>
-bool run_sm(const GemvArgs& a, cudaStream_t stream, int32_t* status) {
-    if (a.G != 128 || a.M > 16 || size_t(a.N) * size_t(a.K / 2) >= (size_t(1) << 40)) return false;
-    const int sms = sm_count();
-    SmArgs p{a.x, a.packed, a.scale, a.zero, a.y, a.M, a.K, a.N, (a.N + 15) / 16, 1, 1, 1, 1,
-             (a.flags & B200Q_EARLY_DEPENDENTS) ? 1 : 0};
+// The one-block-per-multiprocessor kernel whose weights come through the TMA unit
+// (int4_gemv_tma.cuh), with post-scaled sums: group 128, one or two activation rows, where it is
+// the fastest of the decode kernels (9.9 us against 12.5 us a launch on the headline shape, in a
+// chain of launches).  From three rows on, staging the activations and their group sums costs
+// more than the post-scaling saves, and the kernels that dequantize every weight take over.
+template <typename T>
+bool run_tma(const GemvArgs& a, cudaStream_t stream, int32_t* status) {
+    if (a.G != 128 || a.M > 2 || size_t(a.N) * size_t(a.K / 2) >= (size_t(1) << 40)) return false;
+    int* word = gemm_error_word();
+    if (word == nullptr) return false;
+    TmaArgs p{a.x, a.scale, a.zero, a.y, a.M, a.K, a.N, (a.N + 15) / 16, 1, 1, 1, 0, 1,
+              (a.flags & B200Q_EARLY_DEPENDENTS) ? 1 : 0, word};
     size_t smem = 0;
-#define B200Q_SM(MB, KB, R)                                                       \
-    if (sm_plan<MB, 28, KB, R>(p, a.G, sms, &smem)) {                             \
-        *status = launch_sm<T, MB, 28, KB, R, EXACT>(p, smem, sms, stream);       \
-        return true;                                                              \
+    const int sms = sm_count();
+    if (tma_plan<1, 16, 8>(p, a.G, &smem)) {
+        *status = launch_tma<T, 1, 16, 8, false>(p, a.packed, smem, sms, stream);
+        return true;
     }
-    if (a.M <= 8) {
-        B200Q_SM(1, 8, 3)
-        B200Q_SM(1, 8, 2)
-        B200Q_SM(1, 4, 3)
-        B200Q_SM(1, 4, 2)
-    } else {
-        B200Q_SM(2, 8, 3)
-        B200Q_SM(2, 8, 2)
-        B200Q_SM(2, 4, 3)
-        B200Q_SM(2, 4, 2)
+    if (tma_plan<1, 16, 4>(p, a.G, &smem)) {
+        *status = launch_tma<T, 1, 16, 4, false>(p, a.packed, smem, sms, stream);
+        return true;
     }
-#undef B200Q_SM
     return false;
 }
 
@@ -483,8 +477,8 @@ int32_t run_gemv(GemvArgs a, int64_t rows, cudaStream_t stream) {
             step = 16;
             a.M = 16;
         }
-        if (!(a.flags & B200Q_EXACT_WEIGHTS) && run_sm<T, false>(a, stream, &status)) {
-            // post-scaled sums: the default
+        if (!(a.flags & B200Q_EXACT_WEIGHTS) && run_tma<T>(a, stream, &status)) {
+            // post-scaled sums through the TMA ring: the default for one or two rows
         } else if (a.M >= 9 && run_rows<T, 2>(a, stream, &status)) {
             // 9..16 rows: activations staged once per block (15.7 us against 21.7 us at 16
             // rows, K=4096, N=14336; up to 8 rows the per-lane loads are as fast or faster)

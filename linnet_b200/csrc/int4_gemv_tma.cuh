@@ -113,6 +113,18 @@ __device__ __forceinline__ void mma_first<__half>(float (&d)[4], const uint32_t 
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
 }
 
+// One of the two 16-bit scales of a word, as f32.
+template <typename T>
+__device__ __forceinline__ float scale_of(uint32_t word, int odd);
+template <>
+__device__ __forceinline__ float scale_of<__nv_bfloat16>(uint32_t word, int odd) {
+    return __uint_as_float(__byte_perm(word, 0, odd ? 0x3244 : 0x1044));
+}
+template <>
+__device__ __forceinline__ float scale_of<__half>(uint32_t word, int odd) {
+    return __half2float(__ushort_as_half(uint16_t(odd ? word >> 16 : word & 0xFFFFu)));
+}
+
 // One box of the weight map -> shared memory; the barrier receives the bytes.
 __device__ __forceinline__ void tma_item(uint32_t dst, const CUtensorMap* map, int row, int kblock, uint32_t bar) {
     asm volatile(
@@ -132,13 +144,26 @@ __device__ __forceinline__ bool bar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ bool bar_test_wait(uint32_t bar, uint32_t parity) {  // does not suspend the thread
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: false (and the status word set) after about a second, or as soon as another
-// warp of the device has given up.
+// warp of the device has given up.  SPIN: poll without suspending (the producer, one thread,
+// which should see a freed stage at once); otherwise the hardware may park the warp a while.
+template <bool SPIN = false>
 __device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
-    if (bar_try_wait(bar, parity)) return true;
+    if (SPIN ? bar_test_wait(bar, parity) : bar_try_wait(bar, parity)) return true;
     const uint64_t start = umma::global_timer_ns();
     for (uint32_t spins = 0;; ++spins) {
-        if (bar_try_wait(bar, parity)) return true;
+        if (SPIN ? bar_test_wait(bar, parity) : bar_try_wait(bar, parity)) return true;
         if ((spins & 1023u) == 1023u) {
             if (*reinterpret_cast<volatile int*>(status) != 0) return false;
             if (umma::global_timer_ns() - start > 1000000000ull) {
@@ -167,7 +192,7 @@ __host__ __device__ inline TmaLayout tma_layout(int M, int K, int stages) {
     TmaLayout l;
     const int groups = K / 128;
     l.bars = uint32_t(stages) * (KB * 1024);
-    l.sz = (l.bars + uint32_t(stages + WARPS) * 8 + 15u) & ~15u;  // 16-byte stores
+    l.sz = (l.bars + uint32_t(stages + 2 * WARPS) * 8 + 15u) & ~15u;  // 16-byte stores
     l.xs = (l.sz + WARPS * 16 * KB * 3 + 127u) & ~127u;
     l.xrow = uint32_t(groups) * 256 + (M > 1 ? 64 : 0);
     l.xpairs = (M + 1) / 2;
@@ -193,11 +218,12 @@ int4_gemv_tma_kernel(const __grid_constant__ CUtensorMap wmap, const TmaArgs a) 
     const int S = a.stages;
     const TmaLayout lay = tma_layout<MB, WARPS, KB>(M, K, S);
     const uint32_t smem0 = uint32_t(__cvta_generic_to_shared(smem));
-    // Barriers: empty[s] (a stage has been read; only the producer waits on it, lap after lap)
-    // and ready[w] (the bytes of consumer w's next item have landed; only w waits on it, item
-    // after item).  Each has one waiter that follows its phases in order, so a parity never
-    // stands for the wrong phase.
-    const uint32_t empty0 = smem0 + lay.bars, ready0 = empty0 + uint32_t(S) * 8;
+    // Barriers: empty[s] (a stage has been read; the producer waits on it, lap after lap),
+    // ready[w] (the bytes of consumer w's next item have landed; w waits on it, item after item)
+    // and taken[w] (w has seen that; the producer waits on it before it sends w another item,
+    // so that ready[w] is never two phases ahead of its waiter: a parity stands for one phase
+    // only while the waiter is at most one behind).
+    const uint32_t empty0 = smem0 + lay.bars, ready0 = empty0 + uint32_t(S) * 8, taken0 = ready0 + WARPS * 8;
 
     // This block's tiles; the consumers in use and the rounds they make.
     const int t0 = int((uint32_t(blockIdx.x) * uint32_t(a.tiles)) / gridDim.x);
@@ -205,9 +231,9 @@ int4_gemv_tma_kernel(const __grid_constant__ CUtensorMap wmap, const TmaArgs a) 
     const int active = a.tpc * a.wpt;
     const int rounds = (t1 - t0 + a.tpc - 1) / a.tpc;
 
-    if (int(threadIdx.x) < S + WARPS) {
+    if (int(threadIdx.x) < S + 2 * WARPS) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(empty0 + threadIdx.x * 8));
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        umma::fence_proxy_async();  // the TMA unit's view of the barriers
     }
     __syncthreads();
 
@@ -220,23 +246,18 @@ int4_gemv_tma_kernel(const __grid_constant__ CUtensorMap wmap, const TmaArgs a) 
         bool ok = true;
         int n = 0;         // items each consumer has been sent
         for (int round = 0; round < rounds && ok; ++round) {
+            const int tiles_here = min(a.tpc, t1 - t0 - round * a.tpc);  // the last round may be short
             for (int o = 0; o < a.opc && ok; ++o, ++n) {
                 int w = 0;
-                for (int ts = 0; ts < a.tpc && ok; ++ts) {
+                for (int ts = 0; ts < tiles_here && ok; ++ts) {
                     const int tile = t0 + round * a.tpc + ts;
                     for (int part = 0; part < a.wpt; ++part, ++w) {
                         const uint32_t empty = empty0 + s * 8, ready = ready0 + w * 8;
-                        if (lap > 0) ok = bar_wait(empty, (lap - 1) & 1, a.status, 11);
+                        if (lap > 0) ok = bar_wait<true>(empty, (lap - 1) & 1, a.status, 11);
+                        if (ok && n > 0) ok = bar_wait<true>(taken0 + w * 8, (n - 1) & 1, a.status, 13);
                         if (!ok) break;
-                        if (tile < t1) {
-                            // one arrival a phase: the consumer's last item must have landed
-                            if (n > 0) ok = bar_wait(ready, (n - 1) & 1, a.status, 13);
-                            if (!ok) break;
-                            bar_expect(ready, kItem);
-                            tma_item(smem0 + uint32_t(s) * kItem, &wmap, tile * 16, (part * a.opc + o) * KB, ready);
-                        } else {  // nobody takes this one: keep the stage's phases in step
-                            bar_arrive(empty);
-                        }
+                        bar_expect(ready, kItem);
+                        tma_item(smem0 + uint32_t(s) * kItem, &wmap, tile * 16, (part * a.opc + o) * KB, ready);
                         if (++s == S) {
                             s = 0;
                             ++lap;
@@ -355,14 +376,15 @@ int4_gemv_tma_kernel(const __grid_constant__ CUtensorMap wmap, const TmaArgs a) 
     uint16_t* y = static_cast<uint16_t*>(a.y);
     const uint32_t wl = uint32_t(g) * 64 + t * 16;                      // this lane's bytes of a k-block's row g
     const uint32_t x_lane0 = xs + uint32_t(min(g, M - 1)) * lay.xrow + t * 16;
-    const uint32_t x_lane1 = xs + uint32_t(min(8 + g, M - 1)) * lay.xrow + t * 16;  // rows past the last re-read it
+    const uint32_t x_lane1 = xs + uint32_t(min(8 + g, M - 1)) * lay.xrow + t * 16;
     const uint32_t xsum_lane0 = xsum + uint32_t(min(t, lay.xpairs - 1)) * groups * 8;
     const uint32_t xsum_lane1 = xsum + uint32_t(min(4 + t, lay.xpairs - 1)) * groups * 8;
     const uint32_t my_sc = my_sz + g * (KB * 2), my_zp = my_sz + 16 * KB * 2 + g * KB;
     bool ok = true;
     int n = 0;                      // items this warp has taken
-    int s = warp % S;               // stage of its next item: (n * active + warp) % S
-    const int s_step = active % S;
+    int s = warp % S;               // stage of its next item: the items before it in the producer's order, modulo S
+    const int s_step = active % S;  // a full round's items between two of this warp's
+    const int s_last = (min(a.tpc, t1 - t0 - (rounds - 1) * a.tpc) * a.wpt) % S;  // the last round's
     const uint32_t ready = ready0 + warp * 8;
     for (int tile = t0 + ts; tile < t1; tile += a.tpc) {
         float acc[MB][2][4];
@@ -386,33 +408,43 @@ int4_gemv_tma_kernel(const __grid_constant__ CUtensorMap wmap, const TmaArgs a) 
                 if (next_tile < t1) load_sz(next_tile, more_here ? item + 1 : part * a.opc, szr);
             }
             s_mine = s;
-            s += s_step;
+            s += tile + a.tpc >= t1 ? s_last : s_step;
             if (s >= S) s -= S;
             stage_addr = smem0 + uint32_t(s_mine) * kItem;
             if (ok) ok = bar_wait(ready, uint32_t(n) & 1, a.status, 12);
+            __syncwarp();  // every lane has seen the phase
+            if (lane == 0) bar_arrive(taken0 + warp * 8);
             const uint32_t wq = stage_addr + wl;
             const uint32_t xq0 = x_lane0 + uint32_t(item) * (KB * 256), xq1 = x_lane1 + uint32_t(item) * (KB * 256);
             const uint32_t xsq0 = xsum_lane0 + uint32_t(item) * (KB * 8), xsq1 = xsum_lane1 + uint32_t(item) * (KB * 8);
+            // the item's scales and zero points of rows g and g+8: KB 16-bit values and KB bytes each
+            uint32_t scw[2][KB / 2], zpw[2][KB / 4];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                if (KB == 8) {
+                    const uint4 sv = lds128(my_sc + h * 8 * KB * 2);
+                    scw[h][0] = sv.x; scw[h][1] = sv.y; scw[h][2 % (KB / 2)] = sv.z; scw[h][3 % (KB / 2)] = sv.w;
+                    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(zpw[h][0]), "=r"(zpw[h][1 % (KB / 4)]) : "r"(my_zp + h * 8 * KB));
+                } else {
+                    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(scw[h][0]), "=r"(scw[h][1]) : "r"(my_sc + h * 8 * KB * 2));
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(zpw[h][0]) : "r"(my_zp + h * 8 * KB));
+                }
+            }
 #pragma unroll
             for (int j = 0; j < KB; ++j) {
                 const uint4 q0 = lds128(wq + j * 1024), q1 = lds128(wq + j * 1024 + 512);
-                uint32_t sbits[2], zbyte[2];
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(sbits[h]) : "r"(my_sc + (h * 8 * KB + j) * 2));
-                    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(zbyte[h]) : "r"(my_zp + h * 8 * KB + j));
-                }
                 uint32_t sc[2] = {0, 0}, bias[2] = {0, 0};
                 if (EXACT) {
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
-                        sc[h] = sbits[h] * 0x00010001u;
-                        bias[h] = H::kMagic + zbyte[h] * 0x00010001u;  // (magic + zero, magic + zero)
+                        sc[h] = __byte_perm(scw[h][j / 2], 0, j % 2 ? 0x3232 : 0x1010);  // (scale, scale)
+                        bias[h] = H::kMagic + __byte_perm(zpw[h][j / 4], 0, 0x4040 | (j % 4) | (j % 4) << 8);  // (magic + zero) x 2
                     }
                 }
-                float ka[MB][4];  // !EXACT: this k-block's sums
+                float ka[MB][4], kb[MB][4];  // !EXACT: this k-block's sums, in two chains of MMAs
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
+                    // rows past the last one re-read the last row: their columns are never stored
                     uint4 b[MB];
                     b[0] = lds128(xq0 + j * 256 + i * 64);
                     if (MB > 1) b[MB - 1] = lds128(xq1 + j * 256 + i * 64);
@@ -441,29 +473,31 @@ int4_gemv_tma_kernel(const __grid_constant__ CUtensorMap wmap, const TmaArgs a) 
                         if (EXACT) {
                             H::mma(acc[mb][0], a_lo, b[mb].x, b[mb].y);
                             H::mma(acc[mb][1], a_hi, b[mb].z, b[mb].w);
+                        } else if (i == 0) {
+                            mma_first<T>(ka[mb], a_lo, b[mb].x, b[mb].y);
+                            mma_first<T>(kb[mb], a_hi, b[mb].z, b[mb].w);
                         } else {
-                            if (i == 0) mma_first<T>(ka[mb], a_lo, b[mb].x, b[mb].y);
-                            else H::mma(ka[mb], a_lo, b[mb].x, b[mb].y);
-                            H::mma(ka[mb], a_hi, b[mb].z, b[mb].w);
+                            H::mma(ka[mb], a_lo, b[mb].x, b[mb].y);
+                            H::mma(kb[mb], a_hi, b[mb].z, b[mb].w);
                         }
                     }
                 }
                 if (!EXACT) {
                     // y += scale * (sums - (magic + zero) * X), rows g (0, 1) and g+8 (2, 3)
-                    float s[2], nz[2];
+                    float sf[2], nz[2];
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
-                        s[h] = H::to_float(sbits[h]);
+                        sf[h] = scale_of<T>(scw[h][j / 2], j % 2);
                         // 2^23 + zero as f32 bits, then (2^23 - magic) - that = -(magic + zero)
-                        nz[h] = (8388608.0f - H::kBias) - __uint_as_float(zbyte[h] | 0x4B000000u);
+                        nz[h] = (8388608.0f - H::kBias) - __uint_as_float(__byte_perm(zpw[h][j / 4], 0x4B000000u, 0x7440 | (j % 4)));
                     }
 #pragma unroll
                     for (int mb = 0; mb < MB; ++mb) {
                         const float2 X = lds64f((mb == 0 ? xsq0 : xsq1) + j * 8);
-                        acc[mb][0][0] = fmaf(s[0], fmaf(nz[0], X.x, ka[mb][0]), acc[mb][0][0]);
-                        acc[mb][0][1] = fmaf(s[0], fmaf(nz[0], X.y, ka[mb][1]), acc[mb][0][1]);
-                        acc[mb][0][2] = fmaf(s[1], fmaf(nz[1], X.x, ka[mb][2]), acc[mb][0][2]);
-                        acc[mb][0][3] = fmaf(s[1], fmaf(nz[1], X.y, ka[mb][3]), acc[mb][0][3]);
+                        acc[mb][0][0] = fmaf(sf[0], fmaf(nz[0], X.x, ka[mb][0] + kb[mb][0]), acc[mb][0][0]);
+                        acc[mb][0][1] = fmaf(sf[0], fmaf(nz[0], X.y, ka[mb][1] + kb[mb][1]), acc[mb][0][1]);
+                        acc[mb][0][2] = fmaf(sf[1], fmaf(nz[1], X.x, ka[mb][2] + kb[mb][2]), acc[mb][0][2]);
+                        acc[mb][0][3] = fmaf(sf[1], fmaf(nz[1], X.y, ka[mb][3] + kb[mb][3]), acc[mb][0][3]);
                     }
                 }
             }
@@ -524,7 +558,7 @@ inline bool tma_plan(TmaArgs& a, int G, size_t* smem) {
     if (a.wpt > 1 && a.tpc > 14) a.tpc = 14;  // named barriers 1..14 (15 is the consumers')
     const TmaLayout fixed = tma_layout<MB, WARPS, KB>(a.M, a.K, 0);
     const long budget = 226L * 1024 - long(fixed.total);
-    long stages = (budget - WARPS * 8 - 16) / (KB * 1024 + 8);
+    long stages = (budget - 2 * WARPS * 8 - 16) / (KB * 1024 + 8);
     // The stages of a tile's last items go back to the producer together, so the ring must hold
     // more than one tile's worth of warps; and a shallow ring is another kernel's shape.
     if (stages < 4 || stages <= a.wpt) return false;
@@ -536,8 +570,7 @@ inline bool tma_plan(TmaArgs& a, int G, size_t* smem) {
 
 // The weights [N, K/2] as 64-byte pieces: (byte of the k-block, row, k-block of the row).
 template <int KB>
-inline bool tma_weight_map(CUtensorMap* map, const uint8_t* packed, int N, int K,
-                           CUtensorMapL2promotion promotion = CU_TENSOR_MAP_L2_PROMOTION_NONE) {
+inline bool tma_weight_map(CUtensorMap* map, const uint8_t* packed, int N, int K) {
     const umma::EncodeTiled encode = umma::encode_tiled();
     if (encode == nullptr || !aligned(packed, 16)) return false;
     const cuuint64_t dims[3] = {64, cuuint64_t(N), cuuint64_t(K / 128)};
@@ -545,16 +578,15 @@ inline bool tma_weight_map(CUtensorMap* map, const uint8_t* packed, int N, int K
     const cuuint32_t box[3] = {64, 16, KB};
     const cuuint32_t elem[3] = {1, 1, 1};
     return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(packed), dims, strides, box, elem,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, promotion,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <typename T, int MB, int WARPS, int KB, bool EXACT>
-int32_t launch_tma(const TmaArgs& a, const uint8_t* packed, size_t smem, int sms, cudaStream_t stream,
-                   CUtensorMapL2promotion promotion = CU_TENSOR_MAP_L2_PROMOTION_NONE) {
+int32_t launch_tma(const TmaArgs& a, const uint8_t* packed, size_t smem, int sms, cudaStream_t stream) {
     auto kernel = int4_gemv_tma_kernel<T, MB, WARPS, KB, EXACT>;
     CUtensorMap map;
-    if (!tma_weight_map<KB>(&map, packed, a.N, a.K, promotion)) return fail("int4_gemv: the weight tensor map was refused");
+    if (!tma_weight_map<KB>(&map, packed, a.N, a.K)) return fail("int4_gemv: the weight tensor map was refused");
     const cudaError_t attr_err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
     if (attr_err != cudaSuccess) {
         cudaGetLastError();

@@ -21,7 +21,6 @@
 
 namespace b200q {
 
-int* gemm_error_word();  // int4_gemm_sm100.cu: device address of the bounded-wait flag
 
 namespace {
 

@@ -6,12 +6,18 @@
 // for NumPy's half-to-even `round`, and no fused multiply-add.  This translation
 // unit must be compiled with -fmad=false -prec-div=true -ftz=false.
 //
-// HBM-bound: 2 B read + 0.52 B written per weight for int4-g128 from bf16,
-// 2 B + 1 B for int8.  Two kernels:
-//   * team kernel  - groups of 16..256 elements: a team of group/8 lanes holds one
-//     group in registers (one 16-byte load per lane for bf16), reduces min/max with
-//     shuffles and writes 4 packed bytes (or 8 int8) per lane; four chunks are in
-//     flight per lane.
+// HBM-bound by its bytes (2 B read + 0.52 B written per weight for int4-g128 from bf16,
+// 2 B + 1 B for int8) but with some twenty instructions a weight when written naively, so
+// the instruction count is what the kernels are built around:
+//   * the common case of round(v / s) is three additions and a multiply-add per weight (the
+//     1.5 * 2^23 trick), with one test per eight weights for the rare near tie, which takes
+//     the true division; levels are packed arithmetically (four nibbles are one f32 sum);
+//   * per-group work (the shuffles of the min/max reduction, two divisions and a reciprocal)
+//     is spread over 32 weights a lane instead of 8.
+// Two kernels:
+//   * team kernel  - groups of 16..256 elements: a team of 1..8 lanes holds one group in
+//     registers, each lane up to four consecutive 8-weight chunks (64 bytes of bf16),
+//     reduces min/max with shuffles and writes its 16 packed bytes (or 32 int8) at once.
 //   * group kernel - any other group size: one warp or one 256-thread block per
 //     group; the group stays in registers (up to 8 chunks per thread) between the
 //     reduction and the rounding, the rest is read again (from L2).
@@ -40,20 +46,50 @@ __device__ __forceinline__ Chunk widen(const uint4& raw) {  // 8 x bf16
     return c;
 }
 
+__device__ __forceinline__ float min3(float a, float b, float c) {
+    float r;
+    asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
 template <typename In>
 struct Raw;  // the bytes of one chunk as loaded
 template <>
 struct Raw<__nv_bfloat16> {
     uint4 a;
-    __device__ __forceinline__ void load(const __nv_bfloat16* p) { a = ldg_stream(p); }
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { a = __ldg(reinterpret_cast<const uint4*>(p)); }
+    __device__ __forceinline__ void clear() { a = make_uint4(0, 0, 0, 0); }
     __device__ __forceinline__ Chunk get() const { return widen(a); }
+    // smallest and largest of the eight values (3-input min / max: four instructions each)
+    __device__ __forceinline__ void range(float& lo, float& hi) const {
+        const Chunk v = get();
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+            lo = min3(lo, v.v[j], v.v[j + 1]);
+            hi = max3(hi, v.v[j], v.v[j + 1]);
+        }
+    }
 };
 template <>
 struct Raw<float> {
     uint4 a, b;
     __device__ __forceinline__ void load(const float* p) {
-        a = ldg_stream(p);
-        b = ldg_stream(p + 4);
+        a = __ldg(reinterpret_cast<const uint4*>(p));
+        b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+    }
+    __device__ __forceinline__ void clear() { a = b = make_uint4(0, 0, 0, 0); }
+    __device__ __forceinline__ void range(float& lo, float& hi) const {
+        const Chunk v = get();
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+            lo = min3(lo, v.v[j], v.v[j + 1]);
+            hi = max3(hi, v.v[j], v.v[j + 1]);
+        }
     }
     __device__ __forceinline__ Chunk get() const {
         Chunk c;
@@ -118,6 +154,11 @@ __device__ __forceinline__ int int8_level(float v, float scale, float inv_scale)
     return int(fminf(fmaxf(q, -127.0f), 127.0f));
 }
 
+// Adding 1.5 * 2^23 to |t| < 2^22 rounds t to an integer, half to even, in the sum's low bits.
+constexpr float kRound = 12582912.0f;
+// A quotient this close to a half-integer (or larger) is rounded by the true division.
+constexpr float kTie = 0.4999f;
+
 __device__ __forceinline__ void store_scale(void* dst, int dtype, int64_t i, float s) {
     if (dst == nullptr) return;
     if (dtype == B200Q_BF16) {
@@ -129,23 +170,59 @@ __device__ __forceinline__ void store_scale(void* dst, int dtype, int64_t i, flo
     }
 }
 
-__device__ __forceinline__ uint32_t pack8_int4(const Chunk& c, float step, float zero) {
-    uint32_t word = 0;
-    const float inv = __frcp_rn(step);
+// Eight levels clip(round(v / step) + zero, 0, 15) as one little-endian word (byte j/2 holds
+// element j low, j+1 high).  t = v * (1/step) + zero is within 1e-5 of the reference's
+// quotient plus zero wherever the clip does not decide the level anyway (|v / step| < 32),
+// so away from half-integers both round alike; zero is an integer, so adding it before the
+// rounding only matters at exact ties, which take the division with every near tie.
+// INSIDE: the group's range straddles zero (low < 0 < high), so its zero point is not clipped
+// and every t lies in [-0.5, 15.5]: away from ties (the only case kept here) it rounds into
+// 0..15 without the clip.
+template <bool INSIDE = false>
+__device__ __forceinline__ uint32_t pack8_int4(const Chunk& c, float step, float zero, float inv) {
+    float q[8];
+    float worst = 0.0f;  // largest distance of a t from its integer
 #pragma unroll
-    for (int j = 0; j < 8; ++j) word |= int4_level(c.v[j], step, inv, zero) << (4 * j);
-    return word;  // little endian: byte j/2 holds element j (even) low, j+1 high
+    for (int j = 0; j < 8; ++j) {
+        const float t = __fmaf_rn(c.v[j], inv, zero);
+        const float r = __fsub_rn(__fadd_rn(t, kRound), kRound);
+        worst = fmaxf(worst, fabsf(__fsub_rn(t, r)));
+        q[j] = INSIDE ? r : fminf(fmaxf(r, 0.0f), 15.0f);
+    }
+    if (!(worst < kTie)) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) q[j] = float(int4_level(c.v[j], step, inv, zero));
+    }
+    // four levels are one exact f32 sum; 2^23 + sum has them in its low 16 bits
+    const float lo = __fmaf_rn(q[3], 4096.0f, __fmaf_rn(q[2], 256.0f, __fmaf_rn(q[1], 16.0f, q[0])));
+    const float hi = __fmaf_rn(q[7], 4096.0f, __fmaf_rn(q[6], 256.0f, __fmaf_rn(q[5], 16.0f, q[4])));
+    return __byte_perm(__float_as_uint(__fadd_rn(lo, 8388608.0f)), __float_as_uint(__fadd_rn(hi, 8388608.0f)), 0x5410);
+}
+__device__ __forceinline__ uint32_t pack8_int4(const Chunk& c, float step, float zero) {
+    return pack8_int4<false>(c, step, zero, __frcp_rn(step));
 }
 
-__device__ __forceinline__ uint2 pack8_int8(const Chunk& c, float scale) {
-    uint32_t lo = 0, hi = 0;
-    const float inv = __frcp_rn(scale);
+// Eight levels clip(round(v / scale), -127, 127) as bytes: kRound + level has the level's
+// two's complement in its low byte.
+__device__ __forceinline__ uint2 pack8_int8(const Chunk& c, float scale, float inv) {
+    uint32_t b[8];
+    float worst = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        lo |= (uint32_t(int8_level(c.v[j], scale, inv)) & 0xFFu) << (8 * j);
-        hi |= (uint32_t(int8_level(c.v[4 + j], scale, inv)) & 0xFFu) << (8 * j);
+    for (int j = 0; j < 8; ++j) {
+        const float t = __fmul_rn(c.v[j], inv);
+        const float s = __fadd_rn(t, kRound);
+        worst = fmaxf(worst, fabsf(__fsub_rn(t, __fsub_rn(s, kRound))));
+        b[j] = __float_as_uint(fminf(fmaxf(s, kRound - 127.0f), kRound + 127.0f));
     }
-    return make_uint2(lo, hi);
+    if (!(worst < kTie)) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) b[j] = uint32_t(int8_level(c.v[j], scale, inv));
+    }
+    return make_uint2(__byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410),
+                      __byte_perm(__byte_perm(b[4], b[5], 0x0040), __byte_perm(b[6], b[7], 0x0040), 0x5410));
+}
+__device__ __forceinline__ uint2 pack8_int8(const Chunk& c, float scale) {
+    return pack8_int8(c, scale, __frcp_rn(scale));
 }
 
 struct Outputs {
@@ -157,68 +234,82 @@ struct Outputs {
 };
 
 // ---- team kernel ------------------------------------------------------------
-// T lanes per group, one 8-element chunk per lane, U chunks in flight per lane.
-template <int MODE, int T, typename In, int U>
-__global__ void __launch_bounds__(256, 4)  // at most 64 registers: 32 warps per multiprocessor
-quantize_team_kernel(const In* __restrict__ w, int64_t chunks, Outputs o) {
+// T lanes per group, C consecutive 8-weight chunks per lane (G == 8 * T * C).
+template <int MODE, int T, int C, typename In>
+__global__ void __launch_bounds__(256)
+quantize_team_kernel(const In* __restrict__ w, int64_t lanes, Outputs o) {
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    const int64_t first = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     const bool leader = (threadIdx.x % T) == 0;
-    for (int64_t base = first; base - threadIdx.x % 32 < chunks; base += U * stride) {
-        Raw<In> raw[U];
-        bool live[U];
+    int64_t l = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    Raw<In> next[C];  // the following iteration's chunks, asked for before this one's arithmetic
+    auto fetch = [&](int64_t at) {
+        if (at < lanes) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int64_t c = base + u * stride;
-            live[u] = c < chunks;  // uniform over a team: chunks % T == 0
-            if (live[u]) raw[u].load(w + c * 8);
+            for (int u = 0; u < C; ++u) next[u].load(w + (at * C + u) * 8);
+        } else {
+#pragma unroll
+            for (int u = 0; u < C; ++u) next[u].clear();
         }
+    };
+    fetch(l);
+    for (; l - threadIdx.x % 32 < lanes; l += stride) {
+        const bool live = l < lanes;  // uniform over a team: lanes % T == 0
+        Raw<In> raw[C];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int64_t c = base + u * stride;
-            Chunk v;
-            if (live[u]) {
-                v = raw[u].get();
+        for (int u = 0; u < C; ++u) raw[u] = next[u];
+        fetch(l + stride);
+        float lo = __int_as_float(0x7F800000), hi = __int_as_float(0xFF800000);
+#pragma unroll
+        for (int u = 0; u < C; ++u) raw[u].range(lo, hi);
+#pragma unroll
+        for (int d = T / 2; d >= 1; d >>= 1) {
+            lo = fminf(lo, __shfl_xor_sync(0xFFFFFFFFu, lo, d));
+            hi = fmaxf(hi, __shfl_xor_sync(0xFFFFFFFFu, hi, d));
+        }
+        if (!live) continue;
+        if (MODE == kInt4) {
+            const float step = int4_step(lo, hi);
+            const float zero = int4_zero(lo, step);
+            const float inv = __frcp_rn(step);
+            uint32_t word[C];
+            if (lo < 0.0f && hi > 0.0f) {
+#pragma unroll
+                for (int u = 0; u < C; ++u) word[u] = pack8_int4<true>(raw[u].get(), step, zero, inv);
             } else {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) v.v[j] = 0.0f;
+                for (int u = 0; u < C; ++u) word[u] = pack8_int4<false>(raw[u].get(), step, zero, inv);
             }
-            if (MODE == kInt4) {
-                float lo = v.v[0], hi = v.v[0];
-#pragma unroll
-                for (int j = 1; j < 8; ++j) {
-                    lo = fminf(lo, v.v[j]);
-                    hi = fmaxf(hi, v.v[j]);
-                }
-#pragma unroll
-                for (int d = T / 2; d >= 1; d >>= 1) {
-                    lo = fminf(lo, __shfl_xor_sync(0xFFFFFFFFu, lo, d));
-                    hi = fmaxf(hi, __shfl_xor_sync(0xFFFFFFFFu, hi, d));
-                }
-                if (live[u]) {
-                    const float step = int4_step(lo, hi);
-                    const float zero = int4_zero(lo, step);
-                    reinterpret_cast<uint32_t*>(o.packed)[c] = pack8_int4(v, step, zero);
-                    if (leader) {
-                        const int64_t g = c / T;
-                        o.scale[g] = step;
-                        o.zero[g] = uint8_t(zero);
-                        store_scale(o.scale_store, o.store_dtype, g, step);
-                    }
-                }
+            uint32_t* dst = reinterpret_cast<uint32_t*>(o.packed) + l * C;
+            if (C == 4) {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(word[0], word[1], word[2], word[3]);
+            } else if (C == 2) {
+                *reinterpret_cast<uint2*>(dst) = make_uint2(word[0], word[1 % C]);
             } else {
-                float top = 0.0f;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) top = fmaxf(top, fabsf(v.v[j]));
-#pragma unroll
-                for (int d = T / 2; d >= 1; d >>= 1)
-                    top = fmaxf(top, __shfl_xor_sync(0xFFFFFFFFu, top, d));
-                if (live[u]) {
-                    const float scale = int8_scale(top, o.store_dtype);
-                    reinterpret_cast<uint2*>(o.packed)[c] = pack8_int8(v, scale);
-                    if (leader) o.scale[c / T] = scale;
-                }
+                for (int u = 0; u < C; ++u) dst[u] = word[u];
             }
+            if (leader) {
+                const int64_t g = l / T;
+                o.scale[g] = step;
+                o.zero[g] = uint8_t(zero);
+                store_scale(o.scale_store, o.store_dtype, g, step);
+            }
+        } else {
+            const float scale = int8_scale(fmaxf(-lo, hi), o.store_dtype);  // the largest magnitude
+            const float inv = __frcp_rn(scale);
+            uint2 pair[C];
+#pragma unroll
+            for (int u = 0; u < C; ++u) pair[u] = pack8_int8(raw[u].get(), scale, inv);
+            uint2* dst = reinterpret_cast<uint2*>(o.packed) + l * C;
+            if (C % 2 == 0) {
+#pragma unroll
+                for (int u = 0; u < C; u += 2)
+                    *reinterpret_cast<uint4*>(dst + u) = make_uint4(pair[u].x, pair[u].y, pair[(u + 1) % C].x, pair[(u + 1) % C].y);
+            } else {
+#pragma unroll
+                for (int u = 0; u < C; ++u) dst[u] = pair[u];
+            }
+            if (leader) o.scale[l / T] = scale;
         }
     }
 }
@@ -358,18 +449,22 @@ int32_t launch_quantize(const In* w, int64_t out, int64_t in, int64_t G, Outputs
     const bool vec = (G % 8 == 0) && aligned(w, 16) &&
                      aligned(o.packed, MODE == kInt4 ? 4 : 8);
     const int sms = sm_count();
-    if (vec && (G == 16 || G == 32 || G == 64 || G == 128 || G == 256)) {
-        constexpr int U = 4;
-        const int64_t chunks = total / 8;
-        int64_t blocks = (chunks + 256 * U - 1) / (256 * U);
-        if (blocks > (int64_t(1) << 30)) blocks = int64_t(1) << 30;
+    const bool wide = aligned(o.packed, 16);  // a lane's 16 (int4) or 32 (int8) output bytes in one or two stores
+    if (vec && wide && (G == 16 || G == 32 || G == 64 || G == 128 || G == 256)) {
+        // a lane holds up to four consecutive chunks (64 bytes of bf16): lanes at a 64-byte
+        // stride read half a sector per load, the other half is the next load's (L1 keeps it)
+        const int C = G >= 32 ? 4 : 2;
+        const int64_t lanes = total / (8 * C);
+        int64_t blocks = (lanes + 255) / 256;
+        const int64_t cap = int64_t(sms) * 32;
+        if (blocks > cap) blocks = cap;
         const dim3 grid{unsigned(blocks)};
         switch (G) {
-            case 16: quantize_team_kernel<MODE, 2, In, U><<<grid, 256, 0, stream>>>(w, chunks, o); break;
-            case 32: quantize_team_kernel<MODE, 4, In, U><<<grid, 256, 0, stream>>>(w, chunks, o); break;
-            case 64: quantize_team_kernel<MODE, 8, In, U><<<grid, 256, 0, stream>>>(w, chunks, o); break;
-            case 128: quantize_team_kernel<MODE, 16, In, U><<<grid, 256, 0, stream>>>(w, chunks, o); break;
-            default: quantize_team_kernel<MODE, 32, In, U><<<grid, 256, 0, stream>>>(w, chunks, o); break;
+            case 16: quantize_team_kernel<MODE, 1, 2, In><<<grid, 256, 0, stream>>>(w, lanes, o); break;
+            case 32: quantize_team_kernel<MODE, 1, 4, In><<<grid, 256, 0, stream>>>(w, lanes, o); break;
+            case 64: quantize_team_kernel<MODE, 2, 4, In><<<grid, 256, 0, stream>>>(w, lanes, o); break;
+            case 128: quantize_team_kernel<MODE, 4, 4, In><<<grid, 256, 0, stream>>>(w, lanes, o); break;
+            default: quantize_team_kernel<MODE, 8, 4, In><<<grid, 256, 0, stream>>>(w, lanes, o); break;
         }
         return launched("quantize (team kernel)");
     }

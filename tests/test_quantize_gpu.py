@@ -82,6 +82,57 @@ def test_int8_matches_oracle(shape, group, dtype):
     assert np.array_equal(_bits(s.cpu().numpy()), _bits(want_s))
 
 
+def _adversarial(rows: int, group: int, groups: int) -> np.ndarray:
+    """Groups whose quotients land on exact half-integers (with even and odd zero points), sit
+    one ulp either side of them, are clipped, are huge, or do not vary at all."""
+    rng = np.random.default_rng(group)
+    w = np.zeros((rows, groups, group), dtype=np.float32)
+    for r in range(rows):
+        for g in range(groups):
+            kind = (r * groups + g) % 8
+            halves = rng.integers(0, 31, size=group).astype(np.float32) * 0.5   # 0, 0.5, ... 15
+            if kind == 0:      # step 1, zero 0: ties everywhere
+                v = halves.copy(); v[0], v[1] = 0.0, 15.0
+            elif kind == 1:    # step 1, zero 4 (from -3.5, itself a tie)
+                v = halves - 3.5; v[0], v[1] = -3.5, 11.5
+            elif kind == 2:    # step 1, zero 7: the zero's parity differs from kind 1's
+                v = halves - 7.0; v[0], v[1] = -7.0, 8.0
+            elif kind == 3:    # one ulp either side of the ties, odd step
+                v = (halves * np.float32(0.3)).astype(np.float32)
+                v = np.nextafter(v, np.where(rng.integers(0, 2, size=group) == 0, -np.inf, np.inf).astype(np.float32))
+                v[0], v[1] = 0.0, np.float32(4.5)
+            elif kind == 4:    # all positive and far from zero: the zero point clips, the levels clip
+                v = (1000.0 + rng.random(group) * 0.01).astype(np.float32)
+            elif kind == 5:    # huge magnitudes
+                v = (rng.standard_normal(group) * 1e30).astype(np.float32)
+            elif kind == 6:    # no variation: the step is replaced by 1
+                v = np.full(group, -2.5 if r % 2 else 0.0, dtype=np.float32)
+            else:              # ordinary weights
+                v = (rng.standard_normal(group) * 0.015).astype(np.float32)
+            w[r, g] = v
+    return w.reshape(rows, groups * group)
+
+
+@pytest.mark.parametrize("group,groups", [(128, 16), (64, 8), (32, 8), (16, 8), (256, 4), (24, 8), (4096, 2)])
+def test_ties_clips_and_extremes(group, groups):
+    from linnet_b200 import quant
+
+    w = _adversarial(16, group, groups)
+    want = qo.quantize_int4_groups(w, group)
+    got = quant.quantize_int4_groups(torch.from_numpy(w), group)
+    for g, e in zip(got, want):
+        assert np.array_equal(g.cpu().numpy().view(np.uint8), e.view(np.uint8))
+    # int8: make the largest magnitude of every group 127 * 2^k so that halves are ties there too
+    w8 = w.copy().reshape(16, groups, group)
+    w8[:, :, 2] = np.where(np.abs(w8).max(axis=2) < 127, 127.0, w8[:, :, 2])
+    w8 = w8.reshape(16, groups * group)
+    for dtype in ("f32", "bf16"):
+        want_q, want_s = qo.quantize_int8_groups(w8, group, dtype)
+        q, s = quant.quantize_int8_groups(torch.from_numpy(w8), group, dtype)
+        assert np.array_equal(q.cpu().numpy(), want_q)
+        assert np.array_equal(_bits(s.cpu().numpy()), _bits(want_s))
+
+
 def test_empty_and_bad_arguments():
     from linnet_b200 import quant
 
