@@ -267,6 +267,21 @@ def run_gemv(args, rank: int, world: int, device: torch.device, barrier, reduce_
         results["early"] = time_replays(graph, args.steps, 3, barrier, reduce_max)
         del graph
 
+        # One launch at a time with the stream drained in between: no overlap with a neighbour,
+        # launch latency and the kernel's own ramp-up and drain all inside the number.
+        alone = []
+        for i in range(3 * WEIGHT_SETS + 3):
+            p, s, z = sets[i % WEIGHT_SETS]
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            stream.synchronize()
+            start.record(stream)
+            kernels.int4_linear(xs[args.rows], p, s, z)
+            stop.record(stream)
+            stop.synchronize()
+            if i >= 3:
+                alone.append(start.elapsed_time(stop) * 1e3)
+        isolated_us = reduce_max(statistics.median(alone))
+
         # End to end through the operator with HOST buffers: per step the activations come
         # from pinned host memory and the last result goes back to the host, all of it (copies
         # and the 64 products) one CUDA-graph replay followed by a wait for the result.
@@ -332,6 +347,9 @@ def run_gemv(args, rank: int, world: int, device: torch.device, barrier, reduce_
                      "traffic_source": traffic["source"] if traffic else None},
         "per_rows": {str(m): rate(results[str(m)]["ms_per_step"], m) for m in (1, 4, 16)},
         "chained_early": rate(results["early"]["ms_per_step"], args.rows),
+        "isolated": {"us_per_launch": isolated_us, "GB/s": gemv_bytes(args.rows) / isolated_us / 1e3,
+                     "how": "one launch between two events, the stream drained before each; median over "
+                            f"{3 * WEIGHT_SETS} launches visiting the weight sets in turn"},
         "e2e": {"value": gemv_bytes(rows) * LAUNCHES_PER_STEP / (e2e_ms / 1e3) / 1e9 * world,
                 "unit": "GB/s", "ms_per_step": e2e_ms, "trials_ms_per_step": e2e_trials,
                 "h2d_bytes_per_step": rows * K_IN * 2, "d2h_bytes_per_step": rows * N_OUT * 2,
@@ -529,6 +547,41 @@ def run_quantize(args, rank: int, world: int, device: torch.device, barrier, red
         return start.elapsed_time(stop) / 4
     ms4 = alone(lambda w: quant.quantize_int4_groups(w, GROUP, scale_dtype="bf16"))
     ms8 = alone(lambda w: quant.quantize_int8_groups(w, w.shape[1], "bf16"))
+
+    # End to end with HOST buffers: per step one layer's bf16 shard comes from pinned host memory,
+    # is quantized to both formats, and everything a checkpoint stores (packed int4, bf16 scales,
+    # zero points; int8 levels, their scales) goes back to pinned host memory.
+    host_in = [w.to("cpu").pin_memory() for w in layers[0]]
+    host_out = None
+    e2e_steps = max(1, min(args.steps, 3))
+
+    def e2e_step() -> None:
+        nonlocal host_out
+        outs = []
+        for src in host_in:
+            w = src.to(device, non_blocking=True)
+            packed, _scale, zero, stored = quant.quantize_int4_groups(w, GROUP, scale_dtype="bf16")
+            q8, s8 = quant.quantize_int8_groups(w, w.shape[1], "bf16")
+            outs.append((packed, stored, zero, q8, s8))
+        if host_out is None:
+            host_out = [[torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in group] for group in outs]
+        for group, dst in zip(outs, host_out):
+            for t, d in zip(group, dst):
+                d.copy_(t, non_blocking=True)
+        torch.cuda.synchronize()
+
+    e2e_step()
+    e2e_trials = []
+    for _ in range(3):
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e2e_trials.append(reduce_max((time.perf_counter() - t0) * 1e3) / e2e_steps)
+    e2e_ms = statistics.median(e2e_trials)
+    h2d = sum(t.numel() * 2 for t in host_in)
+    d2h = sum(d.numel() * d.element_size() for group in host_out for d in group)
+    del host_in, host_out
     elements_layer = sum(out * depth for _n, out, depth in LAYER_70B)
     line = {
         "metric": "bulk quantize/pack GB/s (Llama-3-70B shapes, int4-g128 + int8 per-channel)",
@@ -548,7 +601,11 @@ def run_quantize(args, rank: int, world: int, device: torch.device, barrier, red
                      "int8_channel": {"GB/s": b8 / (ms8 / 1e3) / 1e9, "frac": b8 / (ms8 / 1e3) / 1e9 / hbm},
                      "traffic": None},
         "parity": checked,
-        "e2e": None,
+        "e2e": {"value": (b4 + b8) / (e2e_ms / 1e3) / 1e9 * world, "unit": "GB/s", "ms_per_step": e2e_ms,
+                "trials_ms_per_step": e2e_trials, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "how": f"{e2e_steps} step(s) a trial: the layer's shard from pinned host memory to the device, both "
+                       "quantizers, all results back to pinned host memory, then a wait; the same algorithmic "
+                       "bytes as `value` over that time (the host link, not HBM, bounds it)"},
         "gpu_launches": args.steps * TRIALS * 2 * len(shard),
         "clocks": clocks.summary(),
     }

@@ -144,6 +144,19 @@ int32_t b200q_int8_linear(const void* x, const int8_t* w, const float* scale,
                           void* y, int64_t rows, int64_t in, int64_t out,
                           int64_t group, int32_t dtype, void* stream);
 
+/* The same with the flags of b200q_int4_gemv_ex (b200q_int8_linear passes 0).
+ *   B200Q_EXACT_WEIGHTS   every weight is w * scale computed in f32 and rounded once to the
+ *     16-bit type before the product: the weight the reference's CPU route multiplies by
+ *     (python/linnet/src/linnet/torch/quantized.py:193).  Without the flag, for one scale a
+ *     row and one or two rows of x, the scale multiplies the finished f32 sum instead, as the
+ *     reference's own GPU kernel does (kernels.py:352-371); that kernel's weights come through
+ *     the TMA unit, and a bounded wait of it that expires is reported by
+ *     b200q_int4_gemm_status().
+ *   B200Q_EARLY_DEPENDENTS   as for b200q_int4_gemv_ex. */
+int32_t b200q_int8_linear_ex(const void* x, const int8_t* w, const float* scale,
+                             void* y, int64_t rows, int64_t in, int64_t out,
+                             int64_t group, int32_t dtype, int32_t flags, void* stream);
+
 /* ---- int8 activations x int8 weights (W8A8) ----------------------------------
  * Replaces linnet::rows8 for int8 (python/linnet/src/linnet/torch/kernels.py:669-753):
  * every row of x [rows, in] (`dtype`) gets scale[row] = max(max|row|, 1e-12) / 127 and

@@ -37,6 +37,8 @@ PROTOTYPES: dict[str, list] = {
                               c_int32, c_void_p],
     "b200q_int8_linear": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                           c_int32, c_void_p],
+    "b200q_int8_linear_ex": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                          c_int32, c_int32, c_void_p],
     "b200q_int8_rows": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int32, c_void_p],
     "b200q_int8_mm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int32,
                       c_void_p],

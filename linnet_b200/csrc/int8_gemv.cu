@@ -16,6 +16,7 @@
 // per-group scale (G a multiple of 64) to each k-block's sum, both in f32; smaller
 // groups scale each weight in f32 before the one rounding to the 16-bit type.
 #include "gemv_common.cuh"
+#include "int8_gemv_tma.cuh"
 
 namespace b200q {
 namespace {
@@ -31,6 +32,7 @@ struct Gemv8Args {
     int kblocks;         // K / 64
     int kb_per_cta;
     int ksplit;
+    int flags;           // B200Q_EXACT_WEIGHTS | B200Q_EARLY_DEPENDENTS
 };
 
 template <int NT>
@@ -261,6 +263,30 @@ int32_t dispatch_gemv8(const Gemv8Args& a, cudaStream_t stream) {
     return launch_gemv8<T, MODE, 2, 2, 4, 2>(a, ksplit, stream);
 }
 
+// One scale a row, one or two activation rows, and no request for the per-weight rounding:
+// the kernel of int8_gemv_tma.cuh, which applies the scale to the finished sum as the
+// reference's own GPU kernel does (python/linnet/src/linnet/torch/kernels.py:352-371).
+template <typename T>
+bool run_tma8(const Gemv8Args& a, cudaStream_t stream, int32_t* status) {
+    if ((a.G != 0 && a.G != a.K) || a.M > 2 || (a.flags & B200Q_EXACT_WEIGHTS)) return false;
+    if (size_t(a.N) * size_t(a.K) >= (size_t(1) << 40)) return false;
+    int* word = gemm_error_word();
+    if (word == nullptr) return false;
+    Tma8Args p{a.x, a.scale, a.y, a.M, a.K, a.N, (a.N + 15) / 16, 1, 1, 1, 0, 1,
+               (a.flags & B200Q_EARLY_DEPENDENTS) ? 1 : 0, word};
+    size_t smem = 0;
+    const int sms = sm_count();
+    if (tma8_plan<16, 8>(p, &smem)) {
+        *status = launch_tma8<T, 16, 8>(p, a.w, smem, sms, stream);
+        return true;
+    }
+    if (tma8_plan<16, 4>(p, &smem)) {
+        *status = launch_tma8<T, 16, 4>(p, a.w, smem, sms, stream);
+        return true;
+    }
+    return false;
+}
+
 template <typename T>
 int32_t run_gemv8(Gemv8Args a, int64_t rows, cudaStream_t stream) {
     const uint8_t* x = static_cast<const uint8_t*>(a.x);
@@ -269,8 +295,10 @@ int32_t run_gemv8(Gemv8Args a, int64_t rows, cudaStream_t stream) {
         a.M = int(rows - m0 < 16 ? rows - m0 : 16);
         a.x = x + size_t(m0) * a.K * 2;
         a.y = y + size_t(m0) * a.N * 2;
-        int32_t status;
-        if (a.K % 64 == 0 && (a.G == 0 || a.G % 16 == 0)) {
+        int32_t status = B200Q_OK;
+        if (run_tma8<T>(a, stream, &status)) {
+            // scale applied to the sum
+        } else if (a.K % 64 == 0 && (a.G == 0 || a.G % 16 == 0)) {
             // Every weight is scaled in f32 and rounded once to the 16-bit type before the
             // product, which is the reference's arithmetic ((w.float() * scale).to(dtype),
             // python/linnet/src/linnet/torch/quantized.py:193); applying the scale to the
@@ -293,9 +321,10 @@ int32_t run_gemv8(Gemv8Args a, int64_t rows, cudaStream_t stream) {
 
 using namespace b200q;
 
-extern "C" int32_t b200q_int8_linear(const void* x, const int8_t* w, const float* scale, void* y,
-                                     int64_t rows, int64_t in, int64_t out, int64_t group,
-                                     int32_t dtype, void* stream) {
+extern "C" int32_t b200q_int8_linear_ex(const void* x, const int8_t* w, const float* scale, void* y,
+                                        int64_t rows, int64_t in, int64_t out, int64_t group,
+                                        int32_t dtype, int32_t flags, void* stream) {
+    B200Q_REQUIRE((flags & ~(B200Q_EXACT_WEIGHTS | B200Q_EARLY_DEPENDENTS)) == 0, "int8_linear: unknown flag bits %d", flags);
     B200Q_REQUIRE(dtype == B200Q_BF16 || dtype == B200Q_F16, "int8_linear: activations are bf16 or f16");
     B200Q_REQUIRE(rows >= 0 && in > 0 && out > 0, "int8_linear: bad shape rows=%lld in=%lld out=%lld",
                   (long long)rows, (long long)in, (long long)out);
@@ -306,7 +335,13 @@ extern "C" int32_t b200q_int8_linear(const void* x, const int8_t* w, const float
     B200Q_REQUIRE(x && w && scale && y, "int8_linear: null tensor");
     B200Q_REQUIRE(aligned(x, 16) && aligned(w, 16) && aligned(scale, 4) && aligned(y, 2),
                   "int8_linear: x and w must be 16-byte aligned");
-    Gemv8Args a{x, w, scale, y, 0, int(in), int(out), int(group), int(in / 64), 0, 1};
+    Gemv8Args a{x, w, scale, y, 0, int(in), int(out), int(group), int(in / 64), 0, 1, flags};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return dtype == B200Q_BF16 ? run_gemv8<__nv_bfloat16>(a, rows, s) : run_gemv8<__half>(a, rows, s);
+}
+
+extern "C" int32_t b200q_int8_linear(const void* x, const int8_t* w, const float* scale, void* y,
+                                     int64_t rows, int64_t in, int64_t out, int64_t group,
+                                     int32_t dtype, void* stream) {
+    return b200q_int8_linear_ex(x, w, scale, y, rows, in, out, group, dtype, 0, stream);
 }

@@ -63,7 +63,8 @@ _exact_weights = False
 
 
 def set_int4_numerics(mode: str) -> None:
-    """How the decode kernels (up to 16 rows, groups of 128) apply zero point and scale.
+    """How the decode kernels apply zero point and scale (int4, groups of 128) or the per-row
+    scale (int8), for one and two rows.
     "fast" (the default; the reference picks these kernels under its `fast` numerics policy
     only, src/opt/candidates.cpp:28-33): in f32 on each group's sum of exact products.
     "exact": every weight rounded to the activation type first, bit for bit the weight the
@@ -175,9 +176,9 @@ def _eight_bit(who: str, x: torch.Tensor, weight: torch.Tensor, scale: torch.Ten
     scale = scale.float().contiguous()
     y = torch.empty(rows, width, dtype=x.dtype, device=device)
     with _Device(device):
-        _lib.check(_lib.load().b200q_int8_linear(
+        _lib.check(_lib.load().b200q_int8_linear_ex(
             x.data_ptr(), weight.data_ptr(), scale.data_ptr(), y.data_ptr(), rows, depth, width,
-            group, _code(x.dtype, who), _stream(device)))
+            group, _code(x.dtype, who), _lib.EXACT_WEIGHTS if _exact_weights else 0, _stream(device)))
     return y
 
 

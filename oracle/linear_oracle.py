@@ -68,6 +68,17 @@ def int8_weight(weight: torch.Tensor, scale: torch.Tensor, dtype: torch.dtype) -
     return (g * scale[:, :, None]).reshape(rows, cols).to(dtype)
 
 
+def int8_linear_f32(x, weight, scale):
+    """`std.quant::linear_int8` as `stdlib/quant.linnet:13-97` defines it, before any 16-bit
+    rounding of the weight: `x . (w * scale)^T` in f64 (returned as f32), and the most the
+    reference's CPU route can differ from that through rounding every weight once to the
+    activation type (as `int4_groups_linear_f32`)."""
+    w = weight.double() * scale.double().reshape(-1, 1)
+    flat = x.reshape(-1, x.shape[-1]).double()
+    eps = 2.0 ** -9 if x.dtype == torch.bfloat16 else 2.0 ** -12
+    return (flat @ w.T).float(), (eps * (flat.abs() @ w.abs().T)).float()
+
+
 def int8_linear(x, weight, scale, bias=None):
     """`std.quant::linear_int8` on a CPU (`int8_linear`, quantized.py:183-194)."""
     flat = x.reshape(-1, x.shape[-1])

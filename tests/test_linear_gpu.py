@@ -33,8 +33,6 @@ RTOL, ATOL = 1e-2, 1e-2
 def numerics(request):
     from linnet_b200 import kernels
 
-    if request.param == "exact" and "int8" in request.node.name:
-        pytest.skip("the numerics mode only concerns the int4 kernels")
     kernels.set_int4_numerics(request.param)
     yield request.param
     kernels.set_int4_numerics("fast")
@@ -253,13 +251,26 @@ def test_int8_reference_fixture(golden_linear, rows):
     close(quantized.int8_group_linear(x, gops, None), _bf16(g[f"rows{rows}"]["y_groups_bits"]), "groups")
 
 
-@pytest.mark.parametrize("rows", [1, 3, 8, 16, 17, 64])
+def close_int8(got, x, q, scale, what, bias=None):
+    """One scale a row under fast numerics (the scale multiplies the f32 sum, as the
+    reference's GPU kernel does): within the usual tolerance of the reference's CPU route once
+    that route's own weight-rounding noise is allowed for, and as close to the definition."""
+    want = lo.int8_linear(x, q, scale, bias)
+    true, noise = lo.int8_linear_f32(x, q, scale)
+    true, noise = true.reshape(want.shape), noise.reshape(want.shape)
+    if bias is not None:
+        true = true + bias.float()
+    close(got, want, what, noise=noise)
+    close(got, true, what + " (definition)", noise=noise)
+
+
+@pytest.mark.parametrize("rows", [1, 2, 3, 8, 16, 17, 64])
 @pytest.mark.parametrize(("depth", "out", "group"), [
     (4096, 4096, 0), (512, 72, 0), (256, 17, 128), (1024, 48, 64), (256, 24, 16), (96, 10, 32),
     (100, 7, 0), (14336, 32, 0),
 ])
 def test_int8_shapes(rows, depth, out, group):
-    from linnet_b200 import quantized
+    from linnet_b200 import kernels, quantized
 
     gen = torch.Generator().manual_seed(rows + depth + out)
     w = torch.randn(out, depth, generator=gen) * 0.02
@@ -271,11 +282,43 @@ def test_int8_shapes(rows, depth, out, group):
         want = lo.int8_linear(x, q, scale.reshape(-1), bias)
         ops = quantized.int8_operands(q.cuda(), scale.reshape(-1).cuda(), 0)  # weight-only: inputs not rounded
         got = quantized.int8_linear(x.cuda(), ops, bias.cuda())
+        if kernels.int4_numerics() == "fast":  # passes of one or two rows take the sum-scaled kernel
+            close_int8(got, x, q, scale.reshape(-1), f"int8 rows={rows} depth={depth} out={out}", bias)
+            return
     else:
         want = lo.int8_group_linear(x, q, scale, bias)
         ops = quantized.int8_group_operands(q.cuda(), scale.cuda())
         got = quantized.int8_group_linear(x.cuda(), ops, bias.cuda())
     close(got, want, f"int8 rows={rows} depth={depth} out={out} group={group}")
+
+
+@pytest.mark.parametrize("rows", [1, 2])
+@pytest.mark.parametrize(("depth", "out"), [(4096, 14344), (1024, 4096), (8192, 1000), (14336, 4096), (512, 16)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_int8_one_and_two_rows(rows, depth, out, dtype):
+    """The shapes the two-plane TMA kernel takes under fast numerics (several rounds of tiles,
+    a ragged last tile, more items than ring stages, K of one item) and, under exact numerics,
+    the kernel that rounds every weight: both against the reference's CPU arithmetic."""
+    from linnet_b200 import kernels
+
+    gen = torch.Generator().manual_seed(rows + depth + out)
+    w = torch.randn(out, depth, generator=gen) * 0.02
+    q, scale = qo.quantize_int8_groups(w.numpy(), depth, "f32")
+    q, scale = torch.from_numpy(q), torch.from_numpy(scale).reshape(-1)
+    x = torch.randn(rows, depth, generator=gen).to(dtype)
+    fn = kernels.gemv8 if rows == 1 else kernels.w8a16
+    got = fn(x.cuda(), q.cuda(), scale.cuda(), False, 0, 1)
+    if kernels.int4_numerics() == "fast":
+        close_int8(got, x, q, scale, f"int8 rows={rows} depth={depth} out={out} {dtype}")
+    else:
+        close(got, lo.int8_linear(x, q, scale), f"int8 rows={rows} depth={depth} out={out} {dtype}")
+    # linear in x: twice the input, twice the output, exactly (a power of two), except where an
+    # f16 output is subnormal and doubling it cannot bring back the bits its rounding dropped
+    twice = fn((x * 2).cuda(), q.cuda(), scale.cuda(), False, 0, 1)
+    normal = got.abs() >= 1e-3
+    assert torch.equal(twice[normal], (got * 2)[normal])
+    from linnet_b200 import _lib
+    _lib.check(_lib.load().b200q_int4_gemm_status())
 
 
 def test_int8_config_one():
