@@ -666,6 +666,12 @@ def main() -> None:
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-other-configs", action="store_true")
     parser.add_argument("--no-decode", action="store_true")
+    parser.add_argument("--fold-swiglu", action="store_true",
+                        help="decode: the down projection forms silu(gate) * up itself where it can (one launch fewer a layer)")
+    parser.add_argument("--no-fold-norm", action="store_true",
+                        help="decode: residual add + RMS norm as kernels of their own even where the products can form them")
+    parser.add_argument("--early", action="store_true",
+                        help="decode: the products let their dependents start as soon as they have started")
     parser.add_argument("--single-batch", action="store_true",
                         help="decode: time only --batch, not 1 / 8 / 64 as well (for profiling)")
     parser.add_argument("--peer-protocol", default=None, choices=["words", "flags"],

@@ -102,8 +102,14 @@ int32_t b200q_int4_gemv(const void* x, const uint8_t* packed, const void* scale,
  *     their own wait on this one's results) as soon as this one has started, instead of
  *     when its last weights are in: pays when the next kernel is another product that can
  *     prefetch its weights meanwhile (q, k, v of one input; a chain of products), costs
- *     when the next kernel only takes room while it waits. */
-enum { B200Q_EXACT_WEIGHTS = 1, B200Q_EARLY_DEPENDENTS = 2 };
+ *     when the next kernel only takes room while it waits.
+ *   B200Q_SWIGLU_INPUT   x is [rows, 2 in]: the product's input is silu(x[:, :in]) * x[:, in:]
+ *     (silu rounded to the 16-bit type, then the product rounded, as the two PyTorch ops of the
+ *     reference's generated source do), formed while the kernel stages its activations: the
+ *     SwiGLU of a decoder layer without a launch of its own.  Taken for one or two rows,
+ *     groups of 128 and the default numerics; B200Q_UNAVAILABLE otherwise (the caller then
+ *     forms the input itself).  No counterpart in the reference. */
+enum { B200Q_EXACT_WEIGHTS = 1, B200Q_EARLY_DEPENDENTS = 2, B200Q_SWIGLU_INPUT = 4 };
 int32_t b200q_int4_gemv_ex(const void* x, const uint8_t* packed, const void* scale,
                            const uint8_t* zero, void* y, int64_t rows, int64_t in,
                            int64_t out, int64_t group, int32_t dtype, int32_t flags,
@@ -118,6 +124,19 @@ int32_t b200q_int4_linear_ex(const void* x, const uint8_t* packed, const void* s
 int32_t b200q_int4_gemm(const void* x, const uint8_t* packed, const void* scale,
                         const uint8_t* zero, void* y, int64_t rows, int64_t in,
                         int64_t out, int64_t group, int32_t dtype, void* stream);
+
+/* A decoder layer's residual add, RMS norm and the product that follows, in one launch:
+ *   r = x + delta (delta may be null: r = x);   y = (rms_norm(r, eps) * norm_weight) . W^T
+ * with W the int4 weight of b200q_int4_gemv and the arithmetic of b200q_add_rmsnorm followed
+ * by b200q_int4_gemv (bit for bit, for up to 4096 inputs).  r is stored to x_out (by one block;
+ * not when delta is null), which must not be x: every block reads x.  Taken for bf16, one or
+ * two rows, groups of 128, up to 8192 inputs and the default numerics; B200Q_UNAVAILABLE
+ * otherwise (the caller then runs the two calls).  flags: B200Q_EARLY_DEPENDENTS or 0.  No
+ * counterpart in the reference, whose generated source runs the three ops one after another. */
+int32_t b200q_int4_gemv_norm(const void* x, const void* delta, const void* norm_weight, float eps,
+                             void* x_out, const uint8_t* packed, const void* scale,
+                             const uint8_t* zero, void* y, int64_t rows, int64_t in, int64_t out,
+                             int64_t group, int32_t dtype, int32_t flags, void* stream);
 
 /* Synchronises the device and reports whether any launch on it of a kernel with a
  * shared-memory pipeline (b200q_int4_gemm, b200q_int8_mm, the one- and two-row kernel of

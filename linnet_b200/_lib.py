@@ -12,7 +12,7 @@ LIBRARY = Path(__file__).resolve().parent / "libb200q.so"
 
 OK, ERROR, UNAVAILABLE = 0, 1, 2
 F32, BF16, F16 = 0, 1, 2
-EXACT_WEIGHTS, EARLY_DEPENDENTS = 1, 2
+EXACT_WEIGHTS, EARLY_DEPENDENTS, SWIGLU_INPUT = 1, 2, 4
 
 # name -> argument types, exactly the prototypes of include/b200q.h
 PROTOTYPES: dict[str, list] = {
@@ -35,6 +35,8 @@ PROTOTYPES: dict[str, list] = {
     "b200q_int4_gemm_status": [],
     "b200q_int4_dequantize": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                               c_int32, c_void_p],
+    "b200q_int4_gemv_norm": [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_int64, c_int64, c_int64, c_int64, c_int32, c_int32, c_void_p],
     "b200q_int8_linear": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                           c_int32, c_void_p],
     "b200q_int8_linear_ex": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,

@@ -69,8 +69,8 @@ attention_partial_kernel(const uint16_t* q, uint16_t* cache_k,  // q and positio
     constexpr int kThreads = 32 * kAttnWarps;
     constexpr float kLn2 = 0.6931471805599453f;
     extern __shared__ __align__(128) uint8_t attn_smem[];  // [stages][K chunk | V chunk]
+    pdl_launch_dependents();  // the next kernel may start its own prologue (a product: its weight fetch) at once
     pdl_wait();
-    pdl_launch_dependents();
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
     const int g = lane / 4, t = lane % 4;
@@ -316,8 +316,8 @@ attention_partial_kernel(const uint16_t* q, uint16_t* cache_k,  // q and positio
 template <int HD>
 __global__ void attention_merge_kernel(const float* partial, uint16_t* __restrict__ out,
                                        int splits) {
+    pdl_launch_dependents();  // the next kernel may start its own prologue (a product: its weight fetch) at once
     pdl_wait();
-    pdl_launch_dependents();
     const size_t head = blockIdx.x;  // b * nq + query head
     const float* p = partial + head * splits * (HD + 2);
     float m_all = -INFINITY;

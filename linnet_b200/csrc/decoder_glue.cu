@@ -55,8 +55,8 @@ add_rmsnorm_kernel(uint16_t* x, const uint16_t* delta,  // read with ld_mutable(
             g[u] = c < chunks ? __ldg(wr + c) : make_uint4(0, 0, 0, 0);
         }
     }
+    pdl_launch_dependents();  // the next kernel may start its own prologue (a product: its weight fetch) at once
     pdl_wait();
-    pdl_launch_dependents();
     uint4* xr = reinterpret_cast<uint4*>(x + size_t(row) * hidden);
     const uint4* dr = delta ? reinterpret_cast<const uint4*>(delta + size_t(row) * hidden) : nullptr;
     float sum = 0.0f;
@@ -116,8 +116,8 @@ __global__ void rope_cache_kernel(const uint16_t* qkv, const int64_t* positions,
                                   uint16_t* __restrict__ q_out, uint16_t* __restrict__ cache_k,
                                   uint16_t* __restrict__ cache_v, int nq, int nkv, int hd, int S,
                                   float theta, int* status) {
+    pdl_launch_dependents();  // the next kernel may start its own prologue (a product: its weight fetch) at once
     pdl_wait();
-    pdl_launch_dependents();
     const int b = blockIdx.y, head = blockIdx.x;  // head < nq: q; < nq + nkv: k; else v
     const int half = hd / 2;
     int64_t pos = ld_mutable(positions + b);
@@ -153,8 +153,8 @@ __global__ void rope_cache_kernel(const uint16_t* qkv, const int64_t* positions,
 // PyTorch ops do.
 __global__ void silu_mul_kernel(const uint16_t* gate_up, uint16_t* __restrict__ out,
                                 int inner, int64_t total) {
+    pdl_launch_dependents();  // the next kernel may start its own prologue (a product: its weight fetch) at once
     pdl_wait();
-    pdl_launch_dependents();
     for (int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
          e += int64_t(gridDim.x) * blockDim.x) {
         const int64_t row = e / inner, col = e % inner;

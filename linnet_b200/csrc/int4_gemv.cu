@@ -430,13 +430,22 @@ bool run_oct(const GemvArgs& a, cudaStream_t stream, int32_t* status) {
 // the fastest of the decode kernels (9.9 us against 12.5 us a launch on the headline shape, in a
 // chain of launches).  From three rows on, staging the activations and their group sums costs
 // more than the post-scaling saves, and the kernels that dequantize every weight take over.
+struct NormInput {  // the input of the product is rms_norm(x + delta) * weight
+    const void* delta;   // or null
+    const void* weight;
+    void* x_out;         // x + delta, stored by the product when delta != null
+    float eps;
+};
+
 template <typename T>
-bool run_tma(const GemvArgs& a, cudaStream_t stream, int32_t* status) {
+bool run_tma(const GemvArgs& a, cudaStream_t stream, int32_t* status, const NormInput* norm = nullptr) {
     if (a.G != 128 || a.M > 2 || size_t(a.N) * size_t(a.K / 2) >= (size_t(1) << 40)) return false;
     int* word = gemm_error_word();
     if (word == nullptr) return false;
     TmaArgs p{a.x, a.scale, a.zero, a.y, a.M, a.K, a.N, (a.N + 15) / 16, 1, 1, 1, 0, 1,
-              (a.flags & B200Q_EARLY_DEPENDENTS) ? 1 : 0, word};
+              (a.flags & B200Q_EARLY_DEPENDENTS) ? 1 : 0, (a.flags & B200Q_SWIGLU_INPUT) ? 1 : 0,
+              norm ? norm->delta : nullptr, norm ? norm->weight : nullptr, norm ? norm->x_out : nullptr,
+              norm ? norm->eps : 0.0f, word};
     size_t smem = 0;
     const int sms = sm_count();
     if (tma_plan<1, 16, 8>(p, a.G, &smem)) {
@@ -528,10 +537,42 @@ extern "C" int32_t b200q_int4_gemv_ex(const void* x, const uint8_t* packed, cons
                                       void* stream) {
     const int32_t ok = check_int4_args("int4_gemv", x, packed, scale, zero, y, rows, in, out, group, dtype);
     if (ok != B200Q_OK || rows == 0) return ok;
-    B200Q_REQUIRE((flags & ~(B200Q_EXACT_WEIGHTS | B200Q_EARLY_DEPENDENTS)) == 0, "int4_gemv: unknown flag bits %d", flags);
+    B200Q_REQUIRE((flags & ~(B200Q_EXACT_WEIGHTS | B200Q_EARLY_DEPENDENTS | B200Q_SWIGLU_INPUT)) == 0,
+                  "int4_gemv: unknown flag bits %d", flags);
     GemvArgs a{x, packed, scale, zero, y, 0, int(in), int(out), int(group), int(in / 128), 0, 1, flags};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (flags & B200Q_SWIGLU_INPUT) {
+        // only the kernel that stages the activations once per block forms them on the way
+        a.M = int(rows);
+        int32_t status = B200Q_OK;
+        const bool taken = rows <= 2 && !(flags & B200Q_EXACT_WEIGHTS) &&
+                           (dtype == B200Q_BF16 ? run_tma<__nv_bfloat16>(a, s, &status) : run_tma<__half>(a, s, &status));
+        if (!taken)
+            return unavailable("int4_gemv: B200Q_SWIGLU_INPUT is taken for one or two rows, groups of 128 and the "
+                               "default numerics");
+        return status;
+    }
     return dtype == B200Q_BF16 ? run_gemv<__nv_bfloat16>(a, rows, s) : run_gemv<__half>(a, rows, s);
+}
+
+extern "C" int32_t b200q_int4_gemv_norm(const void* x, const void* delta, const void* norm_weight, float eps,
+                                        void* x_out, const uint8_t* packed, const void* scale,
+                                        const uint8_t* zero, void* y, int64_t rows, int64_t in, int64_t out,
+                                        int64_t group, int32_t dtype, int32_t flags, void* stream) {
+    const int32_t ok = check_int4_args("int4_gemv_norm", x, packed, scale, zero, y, rows, in, out, group, dtype);
+    if (ok != B200Q_OK || rows == 0) return ok;
+    B200Q_REQUIRE((flags & ~B200Q_EARLY_DEPENDENTS) == 0, "int4_gemv_norm: unknown flag bits %d", flags);
+    B200Q_REQUIRE(norm_weight && aligned(norm_weight, 16) && (!delta || (aligned(delta, 16) && x_out && aligned(x_out, 16))),
+                  "int4_gemv_norm: norm weights (and delta with x_out) must be given, 16-byte aligned");
+    B200Q_REQUIRE(!delta || x_out != x, "int4_gemv_norm: x_out must not be x (every block reads x)");
+    if (dtype != B200Q_BF16 || rows > 2 || group != 128 || in > 8192)
+        return unavailable("int4_gemv_norm: taken for bf16, one or two rows, groups of 128, up to 8192 inputs");
+    GemvArgs a{x, packed, scale, zero, y, int(rows), int(in), int(out), int(group), int(in / 128), 0, 1, flags};
+    NormInput norm{delta, norm_weight, x_out, eps};
+    int32_t status = B200Q_OK;
+    if (!run_tma<__nv_bfloat16>(a, static_cast<cudaStream_t>(stream), &status, &norm))
+        return unavailable("int4_gemv_norm: the shape is not one the kernel that stages its input once takes");
+    return status;
 }
 
 extern "C" int32_t b200q_int4_gemv(const void* x, const uint8_t* packed, const void* scale,

@@ -55,6 +55,13 @@ struct TmaArgs {
     int stages;             // ring stages of KB KiB
     int overlap;            // launched with programmatic stream serialization
     int early;              // dependents may start as soon as this kernel has started
+    int swiglu;             // x is [M, 2 K]: the input is silu(x[:, :K]) * x[:, K:], formed while staging
+    // norm != null (bf16 only): the input is rms_norm(x + delta) * norm, formed while staging; the
+    // first block also stores x + delta to x_out (delta may be null: then nothing is stored)
+    const void* delta;      // [M, K] or null
+    const void* norm;       // [K] or null
+    void* x_out;            // [M, K]
+    float eps;
     int* status;            // device word of expired waits
 };
 
@@ -75,7 +82,7 @@ __host__ __device__ inline TmaLayout tma_layout(int M, int K, int stages) {
     l.xrow = uint32_t(groups) * 256 + (M > 1 ? 64 : 0);
     l.xpairs = (M + 1) / 2;
     l.xsum = l.xs + uint32_t(M) * l.xrow;
-    l.total = l.xsum + uint32_t(l.xpairs) * groups * 8;
+    l.total = l.xsum + uint32_t(l.xpairs) * groups * 8 + 128;  // + the sums of squares of the fused norm
     return l;
 }
 
@@ -199,8 +206,7 @@ int4_gemv_tma_kernel(const __grid_constant__ CUtensorMap wmap, const TmaArgs a) 
             j = r - m * groups;
             c = e & 15;  // piece of the k-block: lane t = c/4, word i = c%4
         };
-        auto stage = [&](int e, const uint4& raw) {
-            const bool live = e < pieces;
+        auto stage = [&](int e, const uint4& raw, bool live) {
             int m, j, c;
             where(e, m, j, c);
             if (!EXACT) {
@@ -221,29 +227,111 @@ int4_gemv_tma_kernel(const __grid_constant__ CUtensorMap wmap, const TmaArgs a) 
                 sts128(xs + uint32_t(m) * lay.xrow + uint32_t(j) * 256 + (c % 4) * 64 + (c / 4) * 16, out);
             }
         };
+        // silu(g) rounded to the 16-bit type, times u, rounded again: what the two PyTorch ops
+        // (and the stand-alone silu_mul kernel of the decode step) make of a pair of words
+        auto swiglu2 = [&](uint32_t gw, uint32_t uw) {
+            uint32_t out = 0;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const float gv = H::to_float((gw >> (16 * h)) & 0xFFFFu), uv = H::to_float((uw >> (16 * h)) & 0xFFFFu);
+                const float sv = H::to_float(H::from_float(gv / (1.0f + expf(-gv))));
+                out |= uint32_t(H::from_float(sv * uv)) << (16 * h);
+            }
+            return out;
+        };
         auto load = [&](int e) {
             uint4 raw = make_uint4(0, 0, 0, 0);
             if (e < pieces) {
                 int m, j, c;
                 where(e, m, j, c);
-                raw = ld_mutable(xg + (size_t(m) * K + size_t(j) * 128) / 8 + c);
+                if (!a.swiglu) {
+                    raw = ld_mutable(xg + (size_t(m) * K + size_t(j) * 128) / 8 + c);
+                } else {
+                    const uint4 gq = ld_mutable(xg + (size_t(m) * 2 * K + size_t(j) * 128) / 8 + c);
+                    const uint4 uq = ld_mutable(xg + (size_t(m) * 2 * K + K + size_t(j) * 128) / 8 + c);
+                    raw = make_uint4(swiglu2(gq.x, uq.x), swiglu2(gq.y, uq.y), swiglu2(gq.z, uq.z), swiglu2(gq.w, uq.w));
+                }
             }
             return raw;
         };
         constexpr int kFirst = MB == 1 ? 4 : 8;  // pieces a thread has in flight at first
-        uint4 raw[kFirst];
+        if (MB == 1 && a.norm != nullptr) {
+            // x + delta, its RMS norm times the norm weights, with the arithmetic and the order of
+            // sums of the stand-alone kernel of the decode step (decoder_glue.cu): thread c takes
+            // the pieces c, c + 512, ... of every row; up to two rows of up to 1024 pieces.
+            constexpr int kHeld = 2;
+            const int chunks = groups * 16;
+            const uint4* dg = below_pdl_wait(static_cast<const uint4*>(a.delta));
+            const uint4* ng = static_cast<const uint4*>(a.norm);
+            uint4* xo = static_cast<uint4*>(a.x_out);
+            const uint32_t squares = xsum + uint32_t(lay.xpairs) * groups * 8;  // [2 rows][16 warps] f32
+            uint4 v[2][kHeld], gw[kHeld];
 #pragma unroll
-        for (int u = 0; u < kFirst; ++u) raw[u] = load(u * threads + me);
-        if (works) load_sz(t0 + ts, part * a.opc, szr);
+            for (int u = 0; u < kHeld; ++u) {
+                const int c = me + u * threads;
+                gw[u] = c < chunks ? __ldg(ng + c) : make_uint4(0, 0, 0, 0);
+            }
+            if (works) load_sz(t0 + ts, part * a.opc, szr);
 #pragma unroll
-        for (int u = 0; u < kFirst; ++u)
-            if (u * threads < pieces) stage(u * threads + me, raw[u]);
-        for (int base = kFirst * threads; base < pieces; base += 4 * threads) {  // four loads in flight a thread
-            uint4 more[4];
+            for (int m = 0; m < 2; ++m) {
+                float sum = 0.0f;
 #pragma unroll
-            for (int u = 0; u < 4; ++u) more[u] = load(base + u * threads + me);
+                for (int u = 0; u < kHeld; ++u) {
+                    const int c = me + u * threads;
+                    uint4 tv = make_uint4(0, 0, 0, 0);
+                    if (m < M && c < chunks) {
+                        tv = ld_mutable(xg + size_t(m) * chunks + c);
+                        if (dg != nullptr) {
+                            const uint4 d = ld_mutable(dg + size_t(m) * chunks + c);
+                            tv.x = bf16_pack(bf16_lo(tv.x) + bf16_lo(d.x), bf16_hi(tv.x) + bf16_hi(d.x));
+                            tv.y = bf16_pack(bf16_lo(tv.y) + bf16_lo(d.y), bf16_hi(tv.y) + bf16_hi(d.y));
+                            tv.z = bf16_pack(bf16_lo(tv.z) + bf16_lo(d.z), bf16_hi(tv.z) + bf16_hi(d.z));
+                            tv.w = bf16_pack(bf16_lo(tv.w) + bf16_lo(d.w), bf16_hi(tv.w) + bf16_hi(d.w));
+                            if (blockIdx.x == 0) xo[size_t(m) * chunks + c] = tv;
+                        }
+                        const uint32_t e4[4] = {tv.x, tv.y, tv.z, tv.w};
 #pragma unroll
-            for (int u = 0; u < 4; ++u) stage(base + u * threads + me, more[u]);
+                        for (int i = 0; i < 4; ++i) sum += bf16_lo(e4[i]) * bf16_lo(e4[i]) + bf16_hi(e4[i]) * bf16_hi(e4[i]);
+                    }
+                    v[m][u] = tv;
+                }
+                for (int d = 16; d >= 1; d >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, d);
+                if (lane == 0) sts32f(squares + (m * 16 + warp) * 4, sum);
+            }
+            named_barrier(15, WARPS * 32);
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+                float total = 0.0f;
+                for (int i = 0; i < WARPS; ++i) total += lds32f(squares + (m * 16 + i) * 4);
+                const float rstd = rsqrtf(total / float(K) + a.eps);
+#pragma unroll
+                for (int u = 0; u < kHeld; ++u) {
+                    const int c = me + u * threads;
+                    if (u * threads >= chunks || m >= M) continue;  // uniform over the block
+                    const uint4 tv = v[m][u];
+                    uint4 o;
+                    o.x = bf16_pack(bf16_lo(tv.x) * rstd * bf16_lo(gw[u].x), bf16_hi(tv.x) * rstd * bf16_hi(gw[u].x));
+                    o.y = bf16_pack(bf16_lo(tv.y) * rstd * bf16_lo(gw[u].y), bf16_hi(tv.y) * rstd * bf16_hi(gw[u].y));
+                    o.z = bf16_pack(bf16_lo(tv.z) * rstd * bf16_lo(gw[u].z), bf16_hi(tv.z) * rstd * bf16_hi(gw[u].z));
+                    o.w = bf16_pack(bf16_lo(tv.w) * rstd * bf16_lo(gw[u].w), bf16_hi(tv.w) * rstd * bf16_hi(gw[u].w));
+                    stage(m * chunks + c, o, c < chunks);
+                }
+            }
+        } else {
+            uint4 raw[kFirst];
+#pragma unroll
+            for (int u = 0; u < kFirst; ++u) raw[u] = load(u * threads + me);
+            if (works) load_sz(t0 + ts, part * a.opc, szr);
+#pragma unroll
+            for (int u = 0; u < kFirst; ++u)
+                if (u * threads < pieces) stage(u * threads + me, raw[u], u * threads + me < pieces);
+            for (int base = kFirst * threads; base < pieces; base += 4 * threads) {  // four loads in flight a thread
+                uint4 more[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) more[u] = load(base + u * threads + me);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) stage(base + u * threads + me, more[u], base + u * threads + me < pieces);
+            }
         }
     }
     named_barrier(15, WARPS * 32);  // the consumers only: the producer is on its own way

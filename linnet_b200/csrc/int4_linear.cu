@@ -21,7 +21,7 @@ extern "C" int32_t b200q_int4_linear_ex(const void* x, const uint8_t* packed, co
                                         const uint8_t* zero, void* y, int64_t rows, int64_t in,
                                         int64_t out, int64_t group, int32_t dtype, int32_t flags,
                                         void* stream) {
-    if (rows >= kGemmRows && int4_gemm_supports(rows, in, out, group, dtype, x, y))
+    if (rows >= kGemmRows && !(flags & B200Q_SWIGLU_INPUT) && int4_gemm_supports(rows, in, out, group, dtype, x, y))
         return b200q_int4_gemm(x, packed, scale, zero, y, rows, in, out, group, dtype, stream);
     return b200q_int4_gemv_ex(x, packed, scale, zero, y, rows, in, out, group, dtype, flags, stream);
 }

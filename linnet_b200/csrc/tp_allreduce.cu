@@ -87,8 +87,8 @@ allreduce_add_rmsnorm_kernel(const Peers p, size_t slot_words, const uint16_t* p
             g[u] = c < chunks ? __ldg(wr + c) : make_uint4(0, 0, 0, 0);
         }
     }
+    pdl_launch_dependents();  // the next kernel may start its own prologue (a product: its weight fetch) at once
     pdl_wait();  // this rank's partial sums come from the kernel before this one
-    pdl_launch_dependents();
     const uint32_t e = *reinterpret_cast<volatile uint32_t*>(epoch) + 1;
     // After one poll has run out every later call returns at once instead of waiting again.
     bool gave_up = *reinterpret_cast<volatile int*>(error) != 0;
@@ -214,8 +214,8 @@ __global__ void __launch_bounds__(512)
 allreduce_words_kernel(const Peers p, size_t slot_words, const uint16_t* in, uint32_t* __restrict__ epoch,
                        uint32_t* __restrict__ done, int* __restrict__ error, uint16_t* __restrict__ out, int pieces,
                        uint64_t wait_limit_ns) {
+    pdl_launch_dependents();  // the next kernel may start its own prologue (a product: its weight fetch) at once
     pdl_wait();
-    pdl_launch_dependents();
     const uint32_t e = *reinterpret_cast<volatile uint32_t*>(epoch) + 1;
     bool gave_up = *reinterpret_cast<volatile int*>(error) != 0;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;

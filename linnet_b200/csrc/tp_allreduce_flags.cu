@@ -56,8 +56,8 @@ allreduce_flags_kernel(const Peers p, size_t slot_elems, int max_rows, uint32_t*
             g[u] = c < chunks ? __ldg(wr + c) : make_uint4(0, 0, 0, 0);
         }
     }
+    pdl_launch_dependents();  // the next kernel may start its own prologue (a product: its weight fetch) at once
     pdl_wait();  // this rank's partial sums come from the kernel before this one
-    pdl_launch_dependents();
     const uint32_t e = *reinterpret_cast<volatile uint32_t*>(epoch) + 1;
     // After one wait has run out every later call returns at once instead of waiting again.
     if (threadIdx.x == 0) gave_up = *reinterpret_cast<volatile int*>(error) != 0;

@@ -82,8 +82,11 @@ def int4_numerics() -> str:
 
 
 def _int4_linear(x: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor,
-                 zero: torch.Tensor, out: torch.Tensor | None = None, early: bool = False) -> torch.Tensor:
+                 zero: torch.Tensor, out: torch.Tensor | None = None, early: bool = False,
+                 swiglu: bool = False) -> torch.Tensor:
     rows, depth = x.shape
+    if swiglu:
+        depth //= 2
     width, groups, half = packed.shape
     group = 2 * half
     block_k = min(group, 128)
@@ -106,7 +109,24 @@ def _int4_linear(x: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor,
         y = out
     with _Device(device):
         flags = (_lib.EXACT_WEIGHTS if _exact_weights else 0) | (_lib.EARLY_DEPENDENTS if early else 0)
-        _lib.check(_lib.load().b200q_int4_linear_ex(
+        lib = _lib.load()
+        if swiglu:
+            # the kernel that forms silu(gate) * up while it stages its input, where it takes the
+            # call; else the stand-alone kernel first
+            status = lib.b200q_int4_linear_ex(
+                x.data_ptr(), packed.data_ptr(), scale.data_ptr(), zero.data_ptr(), y.data_ptr(),
+                rows, depth, width, group, _code(x.dtype, "int4_linear"), flags | _lib.SWIGLU_INPUT, _stream(device))
+            if status == _lib.OK:
+                return y
+            if status != _lib.UNAVAILABLE:
+                _lib.check(status)
+            if x.dtype == torch.bfloat16:
+                from . import glue
+
+                x = glue.silu_mul(x)
+            else:
+                x = torch.nn.functional.silu(x[:, :depth]) * x[:, depth:]
+        _lib.check(lib.b200q_int4_linear_ex(
             x.data_ptr(), packed.data_ptr(), scale.data_ptr(), zero.data_ptr(), y.data_ptr(),
             rows, depth, width, group, _code(x.dtype, "int4_linear"), flags, _stream(device)))
     return y
@@ -124,7 +144,8 @@ def _(x, packed, scale, zero):
 
 
 def int4_linear(x: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor,
-                zero: torch.Tensor, out: torch.Tensor | None = None, early: bool = False) -> torch.Tensor:
+                zero: torch.Tensor, out: torch.Tensor | None = None, early: bool = False,
+                swiglu: bool = False) -> torch.Tensor:
     """`F.linear(x, W)` for `x` [rows, In] (bf16 or f16) and the group-wise 4-bit weight
     of `std.quant::linear_int4_groups`: `packed` [Out, Groups, Group/2] u8 (even value
     low), `scale` and `zero` [Out, Groups].  Any row count: up to 16 rows stream the
@@ -132,10 +153,42 @@ def int4_linear(x: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor,
     calls only) receives the result in place of a new tensor, e.g. a buffer in peer-mapped
     memory that a tensor-parallel reduction reads next.  `early` (eager calls only): the next
     kernel in the stream is another product of the same input, which may start prefetching its
-    weights at once (`B200Q_EARLY_DEPENDENTS`)."""
-    if out is None and not early and torch.compiler.is_compiling():
+    weights at once (`B200Q_EARLY_DEPENDENTS`).  `swiglu` (eager calls only): `x` is
+    [rows, 2 In] and the product's input is `silu(x[:, :In]) * x[:, In:]`, formed inside the
+    product for one and two rows (`B200Q_SWIGLU_INPUT`) and by `glue.silu_mul` otherwise."""
+    if out is None and not early and not swiglu and torch.compiler.is_compiling():
         return _int4_linear_op(x, packed, scale, zero)
-    return _int4_linear(x, packed, scale, zero, out, early)
+    return _int4_linear(x, packed, scale, zero, out, early, swiglu)
+
+
+def int4_linear_norm(x: torch.Tensor, delta: torch.Tensor | None, norm_weight: torch.Tensor, eps: float,
+                     x_out: torch.Tensor | None, packed: torch.Tensor, scale: torch.Tensor,
+                     zero: torch.Tensor) -> torch.Tensor | None:
+    """A decoder layer's residual add, RMS norm and the product that follows as one launch
+    (`b200q_int4_gemv_norm`): returns `F.linear(rms_norm(x + delta) * norm_weight, W)` and stores
+    `x + delta` to `x_out` (a buffer other than `x`; unused when `delta` is None), or None where
+    that kernel does not take the call (more than two rows, exact numerics, another dtype or
+    group): the caller then runs `glue.add_rmsnorm` and `int4_linear`.  Eager calls only."""
+    rows, depth = x.shape
+    width, groups, half = packed.shape
+    if _exact_weights or rows > 2 or 2 * half != 128 or x.dtype != torch.bfloat16 or depth != groups * 128:
+        return None
+    if scale.dtype != x.dtype or packed.dtype != torch.uint8 or zero.dtype != torch.uint8:
+        raise ValueError("int4_linear_norm: bf16 scales, uint8 weights and zero points")
+    device = _on_gpu("int4_linear_norm", x, norm_weight, packed, scale, zero)
+    for t in (x, norm_weight, packed, scale, zero) + ((delta, x_out) if delta is not None else ()):
+        if t is None or not t.is_contiguous():
+            raise ValueError("int4_linear_norm: contiguous tensors (and x_out with delta)")
+    y = torch.empty(rows, width, dtype=x.dtype, device=device)
+    with _Device(device):
+        status = _lib.load().b200q_int4_gemv_norm(
+            x.data_ptr(), None if delta is None else delta.data_ptr(), norm_weight.data_ptr(), float(eps),
+            None if delta is None else x_out.data_ptr(), packed.data_ptr(), scale.data_ptr(), zero.data_ptr(),
+            y.data_ptr(), rows, depth, width, 128, _lib.BF16, 0, _stream(device))
+    if status == _lib.UNAVAILABLE:
+        return None
+    _lib.check(status)
+    return y
 
 
 def int4_dequantize(packed: torch.Tensor, scale: torch.Tensor, zero: torch.Tensor) -> torch.Tensor:

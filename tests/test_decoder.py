@@ -211,6 +211,47 @@ def test_fused_and_torch_steps_agree():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("batch", [1, 2, 3])
+def test_folded_step_equals_unfolded_step(batch):
+    """Residual add + RMS norm inside the products and silu(gate) * up inside the down projection
+    (five launches a layer) give the logits and the caches of the step that runs them as kernels
+    of their own, bit for bit, eagerly and replayed from a graph; three rows run unfolded either way."""
+    from linnet_b200 import _lib, kernels, quant
+
+    cfg = dec.DecoderConfig(layers=3, hidden=1024, heads=8, kv_heads=2, head_dim=128, mlp=2048, vocab=1024, max_seq=64)
+    dev = torch.device("cuda", 0)
+    model = dec.build_random(cfg, dev, rank=0, tp=1, seed=3, linear=kernels.int4_linear,
+                             quantize=quant.quantize_int4_groups)
+    tokens = torch.arange(5, 5 + batch, device=dev)
+    results = {}
+    for folded in (False, True):
+        model.fold_norm = model.fold_swiglu = folded
+        model.allocate_cache(batch, torch.Generator(device=dev).manual_seed(4))
+        logits = []
+        for step in range(3):
+            positions = torch.full((batch,), 10 + step, device=dev, dtype=torch.long)
+            logits.append(model.step(tokens + step, positions).clone())
+        graph = torch.cuda.CUDAGraph()
+        positions = torch.full((batch,), 13, device=dev, dtype=torch.long)
+        eager = model.step(tokens, positions).clone()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph):
+            out = model.step(tokens, positions)
+        for _ in range(5):
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(out, eager)
+        results[folded] = (logits, [c.clone() for c in model.cache_k], [c.clone() for c in model.cache_v])
+        del graph, out
+    for a, b in zip(results[False][0], results[True][0]):
+        assert torch.equal(a, b)
+    for which in (1, 2):
+        for a, b in zip(results[False][which], results[True][which]):
+            assert torch.equal(a, b)
+    _lib.check(_lib.load().b200q_int4_gemm_status())
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("shape", ["tiny", "wide"])
 def test_gpu_decoder_graph_replay(shape):
     """A captured step replays to the eager result, every time: inside a graph the kernels

@@ -206,6 +206,27 @@ def test_int4_down_shape_and_linearity():
     torch.testing.assert_close(both, parts, rtol=2e-2, atol=2e-2 * parts.abs().max().item())
 
 
+@pytest.mark.parametrize("rows", [1, 2, 5])
+@pytest.mark.parametrize(("depth", "out"), [(14336, 4096), (1024, 72)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_int4_swiglu_input(rows, depth, out, dtype):
+    """`swiglu=True` (the product forms silu(gate) * up while it stages its input, for one and
+    two rows) gives the bits of the stand-alone kernel followed by the product, and both follow
+    the two PyTorch ops."""
+    from linnet_b200 import glue, kernels
+
+    packed, scale, zero, gen = random_int4(out, depth, 128, dtype, rows + depth)
+    gate_up = (torch.randn(rows, 2 * depth, generator=gen) * 1.5).to(dtype).cuda()
+    # what the two PyTorch ops make of it (silu rounded to the type, then the product)
+    act = torch.nn.functional.silu(gate_up[:, :depth]) * gate_up[:, depth:]
+    if dtype == torch.bfloat16:
+        assert torch.equal(glue.silu_mul(gate_up), act)
+    separate = kernels.int4_linear(act, packed.cuda(), scale.cuda(), zero.cuda())
+    folded = kernels.int4_linear(gate_up, packed.cuda(), scale.cuda(), zero.cuda(), swiglu=True)
+    assert torch.equal(folded, separate)
+    close_int4(folded, act.cpu(), packed, scale, zero, f"swiglu rows={rows} depth={depth}")
+
+
 def test_int4_dequantize_is_exact():
     """`_int4_weight`: bit-for-bit the reference's arithmetic
     (python/linnet/tests/test_quant_groups.py:151-162)."""
