@@ -445,6 +445,24 @@ def other_configs(device: torch.device, with_cpu: bool) -> dict:
                                          "frac_hbm": gemv_bytes(64, 4096, 28672) / us / 1e3 / hbm}
     del x, xk, packed, scale, zero
     torch.cuda.empty_cache()
+    # W8A8 (the reference's many-row route of int8 layers under numerics="fast"): rows of x to int8,
+    # then the int8 x int8 product on the tensor cores, M = 2048, K = 4096, N = 14336
+    x8 = torch.randn(2048, 4096, device=device, generator=gen).to(torch.bfloat16)
+    w8 = torch.empty(14336, 4096, device=device).normal_(0, 0.02, generator=gen)
+    q8, s8 = quant.quantize_int8_groups(w8, 4096, "f32")
+    s8 = s8.reshape(-1).contiguous()
+    del w8
+    if kernels.int8_mm_available(q8):
+        xq, xs = kernels.int8_rows(x8)
+        us_rows = _time_us(lambda: kernels.int8_rows(x8), 20)
+        us_mm = _time_us(lambda: kernels.int8_mm(xq, q8, xs, s8, torch.bfloat16), 10)
+        tops = 2.0 * 2048 * 14336 * 4096 / us_mm / 1e6
+        us_w8a16 = _time_us(lambda: torch.matmul(x8, kernels.dequantize8(q8, s8, False, 0, 1, torch.bfloat16).T), 10)
+        out["w8a8_M2048_K4096_N14336"] = {"int8_rows_us": us_rows, "int8_mm_us": us_mm, "TOP/s": tops,
+                                          "frac_of_2x_bf16_peak": tops / (2 * bf16_peak),
+                                          "comparator_dequantize_plus_library_gemm_us": us_w8a16}
+    del x8, q8, s8
+    torch.cuda.empty_cache()
     # bulk quantize/pack, one Llama-3-70B-shaped tensor (gate/up: 28672 x 8192, bf16 N(0, 0.015))
     w = torch.empty(28672, 8192, device=device, dtype=torch.bfloat16).normal_(0, 0.015, generator=gen)
     n = w.numel()
