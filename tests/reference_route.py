@@ -386,7 +386,10 @@ def stub_kernels() -> None:
     from linnet_b200 import int4, kernels, quantized
     from oracle import linear_oracle as lo
 
-    def int4_linear(x, packed, scale, zero, out=None, early=False):
+    def int4_linear(x, packed, scale, zero, out=None, early=False, swiglu=False):
+        if swiglu:
+            half = x.shape[-1] // 2
+            x = torch.nn.functional.silu(x[..., :half]) * x[..., half:]
         y = lo.int4_groups_linear(x, packed, scale, zero)
         return y if out is None else out.copy_(y)
 
