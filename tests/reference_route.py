@@ -321,6 +321,57 @@ def run_cards(work: Path, device: str, modes: list, out: dict, std: str) -> None
         del model
 
 
+def run_plans(work: Path, device: str, out: dict, std: str, any_device: bool) -> None:
+    """The same cards through the reference's planner with `linnet_b200.backend.B200Quant` as
+    the only backend (docs/backends.md): `plan_for(..., measure=False)` gives it every region it
+    matches, `plan.run` runs them, `conform` compares each region with the generated source."""
+    import linnet.torch as lt
+
+    from linnet_b200 import backend as plug
+
+    inputs = np.load(work / "inputs.npz")
+    executed = {"count": 0}
+    inner = plug._QuantLinear.execute
+
+    def counted(self, *args, **kwargs):
+        executed["count"] += 1
+        return inner(self, *args, **kwargs)
+
+    plug._QuantLinear.execute = counted
+    backend = plug.B200Quant(any_device=any_device)
+
+    def load(card: str, generics: dict, weights: str, source: Path | None = None):
+        return lt.load(source or work / f"{card}.linnet", generics=generics, std_root=std,
+                       weights=work / f"{weights}.safetensors", device=device, compile=True)
+
+    def through_plan(model, entry: str, args: list, name: str) -> None:
+        plan = model.plan_for(entry, args, backends=[backend], measure=False)
+        made = plan.run(args, model.context_for(plan))
+        out[f"plan/{name}"] = bits(made[0])
+        findings = list(model.conform(entry, args, backend))
+        out[f"plan/{name}/regions"] = np.array([len(findings)])
+        out[f"plan/{name}/conform"] = np.array([bool(f.passed) for f in findings])
+
+    model = load("lin4", LIN4_GENERICS, "lin4")
+    for rows in (1, 16):
+        through_plan(model, "forward", [bf16(inputs[f"lin4/x{rows}"], device)], f"lin4/y{rows}")
+    del model
+    model = load("lin8", LIN8_GENERICS, "lin8")
+    through_plan(model, "by_rows", [bf16(inputs["lin8/x1"], device)], "lin8/rows1")
+    through_plan(model, "by_groups", [bf16(inputs["lin8/x5"], device)], "lin8/groups5")
+    del model
+    model = load("llama4", LLAMA_GENERICS, "llama4", source=work / "llama4" / "src" / "lib.linnet")
+    tokens = torch.from_numpy(inputs["llama4/tokens"]).to(device)
+    first = [tokens[0], torch.tensor(0, dtype=torch.int32, device=device)]
+    plan = model.plan_for("decode", first, backends=[backend], measure=False)
+    context = model.context_for(plan)
+    for step in range(3):
+        logits = plan.run([tokens[step], torch.tensor(step, dtype=torch.int32, device=device)], context)[0]
+        out[f"plan/llama4/logits{step}"] = bits(logits)
+    out["plan/executed"] = np.array([executed["count"]])
+    plug._QuantLinear.execute = inner
+
+
 def run_decoder(work: Path, device: str, out: dict, linear, fused: bool | None) -> None:
     """The same Llama checkpoint through `linnet_b200.decoder.Int4Decoder`."""
     from safetensors.torch import load_file
@@ -432,6 +483,7 @@ def main() -> None:
     else:
         modes = [False, True, "cudagraphs"]
     run_cards(args.work, args.device, modes, out, std)
+    run_plans(args.work, args.device, out, std, any_device=args.stub)
     linear = kernels.int4_linear
     run_decoder(args.work, args.device, out, linear, fused=None if not args.stub else False)
     for name, count in CALLS.items():

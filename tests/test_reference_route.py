@@ -80,6 +80,7 @@ def test_loader_hooks_on_cpu(reference_run):
     for key in ref.files:
         assert key in ours.files, key
         assert np.array_equal(ours[key], ref[key]), key
+    _plans_agree(ours, ref, exact=True)
     # weights replaced in place: the second call computes with the new ones
     assert not np.array_equal(ours["source/refresh/before"], ours["source/refresh/after"])
     assert np.array_equal(ours["source/refresh/after"], ours["source/refresh/other"])
@@ -87,6 +88,25 @@ def test_loader_hooks_on_cpu(reference_run):
     for step in range(3):
         got, want = _values(ours[f"decoder/llama4/logits{step}"]), _values(ref[f"source/llama4/logits{step}"])
         assert (got - want).abs().max().item() <= 2e-2 * peak, step
+
+
+def _plans_agree(ours, ref, exact: bool) -> None:
+    """The B2 plug-in (`linnet_b200.backend.B200Quant`) under the reference's planner: every card's
+    quantized linears were taken, ran, conform to the generated source, and the plan's outputs
+    are the reference's."""
+    assert int(ours["plan/executed"][0]) > 0
+    peak = max(_values(ref[f"source/llama4/logits{s}"]).abs().max().item() for s in range(3))
+    for name in ("lin4/y1", "lin4/y16", "lin8/rows1", "lin8/groups5"):
+        assert int(ours[f"plan/{name}/regions"][0]) >= 1, name
+        assert bool(ours[f"plan/{name}/conform"].all()), name
+        got, want = _values(ours[f"plan/{name}"]), _values(ref[f"source/{name}"])
+        if exact:
+            assert torch.equal(got, want), name
+        else:
+            torch.testing.assert_close(got, want, rtol=1e-2, atol=1e-2, msg=lambda m: f"plan/{name}: {m}")
+    for step in range(3):
+        got, want = _values(ours[f"plan/llama4/logits{step}"]), _values(ref[f"source/llama4/logits{step}"])
+        assert (got - want).abs().max().item() <= (0 if exact else 2e-2 * peak), step
 
 
 @pytest.mark.gpu
@@ -97,6 +117,7 @@ def test_loader_route_on_gpu(reference_run):
     for name in ENTRY_POINTS + ("_eight_bit",):
         assert int(ours[f"calls/{name}"][0]) > 0, f"{name} was never reached through linnet.torch.load"
     assert int(ours["calls/_int4_linear"][0]) > 0
+    _plans_agree(ours, ref, exact=False)
     peak = max(_values(ref[f"source/llama4/logits{s}"]).abs().max().item() for s in range(3))
     checked = 0
     for mode in ("interp", "source", "cudagraphs"):
