@@ -236,7 +236,7 @@ struct Outputs {
 // ---- team kernel ------------------------------------------------------------
 // T lanes per group, C consecutive 8-weight chunks per lane (G == 8 * T * C).
 template <int MODE, int T, int C, typename In>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)  // at most 64 registers: 32 warps per multiprocessor
 quantize_team_kernel(const In* __restrict__ w, int64_t lanes, Outputs o) {
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     const bool leader = (threadIdx.x % T) == 0;
