@@ -65,14 +65,14 @@ struct Raw<__nv_bfloat16> {
     __device__ __forceinline__ void load(const __nv_bfloat16* p) { a = __ldg(reinterpret_cast<const uint4*>(p)); }
     __device__ __forceinline__ void clear() { a = make_uint4(0, 0, 0, 0); }
     __device__ __forceinline__ Chunk get() const { return widen(a); }
-    // smallest and largest of the eight values (3-input min / max: four instructions each)
+    // smallest and largest of the eight values, two at a time in the 16-bit type (exact: min and
+    // max only select), which keeps the eight f32 values out of the registers until the second pass
     __device__ __forceinline__ void range(float& lo, float& hi) const {
-        const Chunk v = get();
-#pragma unroll
-        for (int j = 0; j < 8; j += 2) {
-            lo = min3(lo, v.v[j], v.v[j + 1]);
-            hi = max3(hi, v.v[j], v.v[j + 1]);
-        }
+        const __nv_bfloat162* v = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162 l = __hmin2(__hmin2(v[0], v[1]), __hmin2(v[2], v[3]));
+        const __nv_bfloat162 h = __hmax2(__hmax2(v[0], v[1]), __hmax2(v[2], v[3]));
+        lo = min3(lo, __low2float(l), __high2float(l));
+        hi = max3(hi, __low2float(h), __high2float(h));
     }
 };
 template <>
