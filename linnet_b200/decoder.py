@@ -471,8 +471,14 @@ def bench(args, rank: int, world: int, device: torch.device, barrier, reduce_max
             per_batch_diff[str(batch)] = {"max_abs": diff, "max_logit": top}
             worst, scale_of = max(worst, diff / max(top, 1e-6)), max(scale_of, top)
         worst = reduce_max(worst)
-        # bf16 sums taken in two different orders through 32 layers: a few bf16 ulps of the logits
-        peer_vs_nccl = {"peer_vs_nccl_max_abs_over_max_logit": worst, "tolerance": 5e-2, "ok": worst <= 5e-2,
+        # On 2 ranks both routes add the same two numbers (difference 0).  From 3 ranks on NCCL rounds
+        # its partial sums to bf16 in an order of its own while the kernel sums in f32 in rank order
+        # and rounds once; through 32 layers of a random network that grows to a few percent of the
+        # largest logit (0.054 measured on 4 ranks).  The bound catches a broken reduction (missing
+        # or doubled rank: O(1)), not rounding; bit-exactness of the kernel itself is a test
+        # (tests/test_tp_peer_reduce.py).
+        tolerance = 0.25
+        peer_vs_nccl = {"peer_vs_nccl_max_abs_over_max_logit": worst, "tolerance": tolerance, "ok": worst <= tolerance,
                         "per_batch": per_batch_diff}
         if not peer_vs_nccl["ok"]:
             raise SystemExit(f"peer-memory reduction and NCCL disagree: {peer_vs_nccl}")
