@@ -22,7 +22,6 @@
 //     group; the group stays in registers (up to 8 chunks per thread) between the
 //     reduction and the rounding, the rest is read again (from L2).
 #include "common.cuh"
-#include <cstdlib>
 
 namespace b200q {
 namespace {
@@ -236,7 +235,7 @@ struct Outputs {
 
 // ---- team kernel ------------------------------------------------------------
 // T lanes per group, C consecutive 8-weight chunks per lane (G == 8 * T * C).
-template <int MODE, int T, int C, typename In, bool PREFETCH = true>
+template <int MODE, int T, int C, typename In>
 __global__ void __launch_bounds__(256, 4)  // at most 64 registers: 32 warps per multiprocessor
 quantize_team_kernel(const In* __restrict__ w, int64_t lanes, Outputs o) {
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
@@ -252,14 +251,13 @@ quantize_team_kernel(const In* __restrict__ w, int64_t lanes, Outputs o) {
             for (int u = 0; u < C; ++u) next[u].clear();
         }
     };
-    if (PREFETCH) fetch(l);
+    fetch(l);
     for (; l - threadIdx.x % 32 < lanes; l += stride) {
         const bool live = l < lanes;  // uniform over a team: lanes % T == 0
         Raw<In> raw[C];
-        if (!PREFETCH) fetch(l);
 #pragma unroll
         for (int u = 0; u < C; ++u) raw[u] = next[u];
-        if (PREFETCH) fetch(l + stride);
+        fetch(l + stride);
         float lo = __int_as_float(0x7F800000), hi = __int_as_float(0xFF800000);
 #pragma unroll
         for (int u = 0; u < C; ++u) raw[u].range(lo, hi);
@@ -282,10 +280,8 @@ quantize_team_kernel(const In* __restrict__ w, int64_t lanes, Outputs o) {
                 for (int u = 0; u < C; ++u) word[u] = pack8_int4<false>(raw[u].get(), step, zero, inv);
             }
             uint32_t* dst = reinterpret_cast<uint32_t*>(o.packed) + l * C;
-            if (C % 4 == 0) {
-#pragma unroll
-                for (int u = 0; u < C; u += 4)
-                    *reinterpret_cast<uint4*>(dst + u) = make_uint4(word[u], word[(u + 1) % C], word[(u + 2) % C], word[(u + 3) % C]);
+            if (C == 4) {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(word[0], word[1], word[2], word[3]);
             } else if (C == 2) {
                 *reinterpret_cast<uint2*>(dst) = make_uint2(word[0], word[1 % C]);
             } else {
@@ -457,9 +453,7 @@ int32_t launch_quantize(const In* w, int64_t out, int64_t in, int64_t G, Outputs
     if (vec && wide && (G == 16 || G == 32 || G == 64 || G == 128 || G == 256)) {
         // a lane holds up to four consecutive chunks (64 bytes of bf16): lanes at a 64-byte
         // stride read half a sector per load, the other half is the next load's (L1 keeps it)
-        const char* qv = getenv("B200Q_QV");
-        const int variant = qv ? atoi(qv) : 0;
-        const int C = (G == 128 && variant == 2) ? 8 : G >= 32 ? 4 : 2;
+        const int C = G >= 32 ? 4 : 2;
         const int64_t lanes = total / (8 * C);
         int64_t blocks = (lanes + 255) / 256;
         const int64_t cap = int64_t(sms) * 32;
@@ -469,11 +463,7 @@ int32_t launch_quantize(const In* w, int64_t out, int64_t in, int64_t G, Outputs
             case 16: quantize_team_kernel<MODE, 1, 2, In><<<grid, 256, 0, stream>>>(w, lanes, o); break;
             case 32: quantize_team_kernel<MODE, 1, 4, In><<<grid, 256, 0, stream>>>(w, lanes, o); break;
             case 64: quantize_team_kernel<MODE, 2, 4, In><<<grid, 256, 0, stream>>>(w, lanes, o); break;
-            case 128:
-                if (variant == 1) quantize_team_kernel<MODE, 4, 4, In, false><<<grid, 256, 0, stream>>>(w, lanes, o);
-                else if (variant == 2) quantize_team_kernel<MODE, 2, 8, In, false><<<grid, 256, 0, stream>>>(w, lanes, o);
-                else quantize_team_kernel<MODE, 4, 4, In><<<grid, 256, 0, stream>>>(w, lanes, o);
-                break;
+            case 128: quantize_team_kernel<MODE, 4, 4, In><<<grid, 256, 0, stream>>>(w, lanes, o); break;
             default: quantize_team_kernel<MODE, 8, 4, In><<<grid, 256, 0, stream>>>(w, lanes, o); break;
         }
         return launched("quantize (team kernel)");
