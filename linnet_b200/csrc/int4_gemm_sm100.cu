@@ -11,17 +11,21 @@
 // One persistent block per multiprocessor, 22 warps with fixed roles:
 //   warps 0-3   epilogue: tensor memory -> registers (tcgen05.ld) -> bf16 -> Y
 //   warp  4     TMA producer: two 128 x 64 boxes of X per stage (SWIZZLE_128B)
-//   warp  5     MMA issuer: one thread issues tcgen05.mma (128 x 128 x 16, bf16 -> f32)
-//   warps 6-21  dequantizers (two groups of 8 taking stages in turn): packed nibbles -> registers -> the exact bf16 weight
-//               ((q - zero) * scale, one rounding, as the reference) -> the 128-byte
-//               swizzled K-major layout the MMA reads from shared memory
-// A block tile is 256 rows of X by 128 rows of W: every dequantized 128 x 64 weight
-// tile feeds two accumulators (2 x 128 columns of tensor memory), which halves the
-// dequantization work per flop; the accumulators are double-buffered (4 x 128 = all
-// 512 columns) so the epilogue of one tile overlaps the main loop of the next.
-// Stages: 4 x (32 KB of X + 16 KB of W) of shared memory, mbarrier full/empty pairs.
-// Every wait on an mbarrier is bounded: on expiry the block raises an error flag in
-// global memory, stops issuing work, still releases its tensor memory and returns.
+//   warp  5     MMA issuer: one thread issues tcgen05.mma (128 x bn x 16, bf16 -> f32)
+//   warps 6-21  dequantizers, two threads a row of W: packed nibbles -> registers -> the
+//               exact bf16 weight ((q - zero) * scale, one rounding, as the reference) ->
+//               the 128-byte swizzled K-major layout the MMA reads from shared memory
+// A block tile is 256 rows of X by bn rows of W: every dequantized bn x 64 weight tile
+// feeds two accumulators, which halves the dequantization work per flop.  Two kernels:
+//   general (BN = 256): bn is any multiple of 16 from 64 to 256, chosen per launch so that
+//     the tiles fill the multiprocessors' last round; 2 x bn columns of tensor memory used
+//     once per tile; stages of 32 KB of X + bn x 128 bytes of W, as many as fit 192 KB;
+//   128-wide (BN = 128): accumulators double-buffered (4 x 128 = all 512 columns) so the
+//     epilogue of a tile overlaps the next tile's products, the dequantizers as two groups
+//     of 8 warps taking stages in turn; it runs the K-split case (few rows, narrow weight).
+// mbarrier full/empty pairs per stage.  Every wait on an mbarrier is bounded: on expiry the
+// block raises an error flag in global memory, stops issuing work, still releases its
+// tensor memory and returns.
 #include <cstdlib>
 
 #include "mma.cuh"
@@ -37,29 +41,22 @@ constexpr int kEpilogueWarps = 4, kTmaWarp = 4, kMmaWarp = 5, kFirstDequantWarp 
 constexpr int kAllDequantWarps = 16;
 constexpr int kThreads = (kFirstDequantWarp + kAllDequantWarps) * 32;  // 704
 constexpr uint32_t kTmemColumns = 512;
+constexpr int kRing = 192 * 1024;  // shared memory of the stages
+constexpr int kMaxStages = 5;
+constexpr int kTileFixed = 120;  // a tile's time is as that of its width plus this many columns
 constexpr int kPrefetch = 4;  // stages of packed weights each dequantizer thread keeps in flight
 
-// The tile's width BN (rows of W = columns of Y) decides how often X is re-read from L2:
-// every X element is loaded once per BN output columns.  At BN = 128 the X tiles alone
-// need ~6 TB/s of L2 bandwidth at the tensor cores' speed and the kernel is L2-bound
-// (measured ~0.8 PFLOP/s); BN = 256 halves that.
-//   BN = 128: 4 stages of 48 KB, accumulators double-buffered (2 x 2 x 128 columns), the
-//             dequantizers work as two groups of 8 warps taking stages in turn;
-//   BN = 256: 3 stages of 64 KB, 2 x 256 columns used once per tile (the epilogue of a
-//             tile does not overlap the next tile's products), all 16 dequantizer warps
-//             fill every stage.
+// The tile's width (rows of W = columns of Y) decides how often X is re-read from L2: every
+// X element is loaded once per tile width of output columns, 32 KB a stage whatever the
+// width, so narrow tiles are bound by that traffic and wide ones by the products.
 template <int BN>
 struct Shape {
-    static constexpr int kStages = BN == 128 ? 4 : 3;
-    static constexpr int kStageBytes = 2 * kATile + BN * kBK * 2;
     static constexpr int kAccBufs = BN == 128 ? 2 : 1;
     static constexpr int kDequantGroups = BN == 128 ? 2 : 1;
     static constexpr int kDequantWarps = kAllDequantWarps / kDequantGroups;  // warps per stage
-    static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(BN >> 3) << 17) |
-                                       (uint32_t(kBM >> 4) << 24);
-    static constexpr size_t kSmem = size_t(kStages) * kStageBytes + 1024 + 256;
+    static constexpr size_t kSmem = size_t(kRing) + 1024 + 256;
 };
-constexpr int kMaxStages = 4;
+
 
 struct GemmArgs {
     const uint8_t* packed;  // [N, K/2]
@@ -67,7 +64,10 @@ struct GemmArgs {
     const uint8_t* zero;    // [N, K/G]
     uint16_t* y;            // [M, N] bf16
     int M, K, N, G;
-    int m_tiles, n_tiles;   // tiles of 256 rows of X, of BN rows of W
+    int m_tiles, n_tiles;   // tiles of 256 rows of X, of bn rows of W
+    int bn;                 // rows of W per tile: BN, or for BN = 256 any multiple of 16 up to it
+    int vec;                // y can be written 16 bytes at a time (N % 8 == 0, y aligned)
+    int stages, stage_bytes;  // of the ring: 2 x 16 KB of X and bn x 128 bytes of W each
     int k_splits;           // > 1: a cluster of k_splits blocks shares one tile, each a slice of K
 };
 
@@ -76,9 +76,6 @@ struct GemmArgs {
 __device__ int g_gemm_error = 0;
 
 using namespace umma;
-
-// (The kind::f16 instruction descriptor is Shape<BN>::kIdesc: f32 accumulator, bf16 A and
-// B, both K-major, M = 128, N = BN.)
 
 struct Pipeline {  // shared-memory barriers and the tensor-memory base address
     uint64_t full_a[kMaxStages];   // TMA bytes of X landed
@@ -93,14 +90,18 @@ template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
     using S = Shape<BN>;
-    constexpr int kStages = S::kStages, kStageBytes = S::kStageBytes, kAccBufs = S::kAccBufs;
+    constexpr int kAccBufs = S::kAccBufs;
+    const int stages = a.stages;
+    const uint32_t stage_bytes = uint32_t(a.stage_bytes);
     constexpr int kDequantGroups = S::kDequantGroups, kDequantWarps = S::kDequantWarps;
-    constexpr uint32_t kIdesc = S::kIdesc;
     constexpr int kBN = BN;
+    // kind::f16 instruction descriptor: f32 accumulator, bf16 A and B, both K-major, M = 128, N = bn
+    const int bn = BN == 128 ? 128 : a.bn;
+    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(bn >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // The swizzled tiles need 1024-byte alignment.
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    Pipeline* pipe = reinterpret_cast<Pipeline*>(smem + kStages * kStageBytes);
+    Pipeline* pipe = reinterpret_cast<Pipeline*>(smem + kRing);
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int tiles = a.m_tiles * a.n_tiles;
     // Few rows and a narrow weight leave most multiprocessors without a tile; then a cluster
@@ -113,9 +114,9 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
     const int ks_begin = split * k_per_split, ks_end = min(a.K / kBK, ks_begin + k_per_split);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < stages; ++s) {
             mbar_init(&pipe->full_a[s], 1);
-            mbar_init(&pipe->full_b[s], kDequantWarps);
+            mbar_init(&pipe->full_b[s], bn / 16);  // the warps that fill a stage: two threads a row
             mbar_init(&pipe->empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -139,26 +140,28 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
     if (warp == kTmaWarp) {
         // ---- producer of X -------------------------------------------------------
         if (lane == 0) {
-            uint32_t it = 0;  // stage uses so far
+            int s = 0;            // ring slot of the next stage
+            uint32_t lap = 0;     // times the ring has been gone round
             bool ok = true;
             for (int tile = tile_first; tile < tiles && ok; tile += tile_stride) {
                 const int m0 = (tile % a.m_tiles) * (2 * kBM);
                 const bool two = m0 + kBM < a.M;
-                for (int ks = ks_begin; ks < ks_end && ok; ++ks, ++it) {
-                    const int s = it % kStages;
-                    if (it >= kStages) ok = mbar_wait(&pipe->empty[s], ((it / kStages) - 1) & 1, &g_gemm_error, 1);
+                for (int ks = ks_begin; ks < ks_end && ok; ++ks) {
+                    if (lap > 0) ok = mbar_wait(&pipe->empty[s], (lap - 1) & 1, &g_gemm_error, 1);
                     if (!ok) break;
-                    uint8_t* dst = smem + s * kStageBytes;
+                    uint8_t* dst = smem + s * stage_bytes;
                     mbar_expect_tx(&pipe->full_a[s], two ? 2 * kATile : kATile);
                     tma_load_2d(dst, &x_map, ks * kBK, m0, &pipe->full_a[s]);
                     if (two) tma_load_2d(dst + kATile, &x_map, ks * kBK, m0 + kBM, &pipe->full_a[s]);
+                    if (++s == stages) s = 0, ++lap;
                 }
             }
         }
     } else if (warp == kMmaWarp) {
         // ---- MMA issuer ----------------------------------------------------------
         if (lane == 0) {
-            uint32_t it = 0, t = 0;
+            uint32_t t = 0, lap = 0;
+            int s = 0;
             bool ok = true;
             for (int tile = tile_first; tile < tiles && ok; tile += tile_stride, ++t) {
                 const int m0 = (tile % a.m_tiles) * (2 * kBM);
@@ -167,22 +170,21 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
                 if (t >= uint32_t(kAccBufs))
                     ok = mbar_wait(&pipe->acc_empty[buf], ((t / kAccBufs) - 1) & 1, &g_gemm_error, 2);
                 tc_fence_after();
-                for (int ks = ks_begin; ks < ks_end && ok; ++ks, ++it) {
-                    const int s = it % kStages;
-                    const uint32_t parity = (it / kStages) & 1;
-                    ok = mbar_wait(&pipe->full_a[s], parity, &g_gemm_error, 3) &&
-                         mbar_wait(&pipe->full_b[s], parity, &g_gemm_error, 4);
+                for (int ks = ks_begin; ks < ks_end && ok; ++ks) {
+                    ok = mbar_wait(&pipe->full_a[s], lap & 1, &g_gemm_error, 3) &&
+                         mbar_wait(&pipe->full_b[s], lap & 1, &g_gemm_error, 4);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t base = smem_u32(smem + s * kStageBytes);
+                    const uint32_t base = smem_u32(smem + s * stage_bytes);
 #pragma unroll
                     for (int kk = 0; kk < kBK / 16; ++kk) {
                         const uint64_t b_desc = smem_desc(base + 2 * kATile + kk * 32);
                         const uint32_t acc = (ks > ks_begin || kk > 0) ? 1u : 0u;
-                        umma_bf16(tmem + buf * (2 * kBN), smem_desc(base + kk * 32), b_desc, kIdesc, acc);
-                        if (two) umma_bf16(tmem + buf * (2 * kBN) + kBN, smem_desc(base + kATile + kk * 32), b_desc, kIdesc, acc);
+                        umma_bf16(tmem + buf * (2 * kBN), smem_desc(base + kk * 32), b_desc, idesc, acc);
+                        if (two) umma_bf16(tmem + buf * (2 * kBN) + kBN, smem_desc(base + kATile + kk * 32), b_desc, idesc, acc);
                     }
                     umma_commit(&pipe->empty[s]);  // frees the stage when these MMAs retire
+                    if (++s == stages) s = 0, ++lap;
                 }
                 if (ok) umma_commit(&pipe->acc_full[buf]);
             }
@@ -193,50 +195,64 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
         const int group_id = (threadIdx.x - kFirstDequantWarp * 32) / (kDequantWarps * 32);
         const int row = d >> 1, half = d & 1;                // W row of the tile, 32-input half
         const int groups = a.K / a.G;
+        const int spg = a.G / kBK;                           // stages a quantization group lasts
+        // Everything that repeats per stage is kept as a running value (stage, parity, group,
+        // addresses): the loop body is the dequantization and little else.
+        // This thread's four 16-byte pieces of a stage's W tile, swizzled: piece i is chunk
+        // (4 half + i) ^ (row & 7) of the 128-byte row, which is the first one with i * 16
+        // XORed into its address (stages and rows start on multiples of 128).
+        const uint32_t piece0 = smem_u32(smem) + 2 * kATile + row * 128 + (((half * 4) ^ (row & 7)) * 16);
         uint32_t it = 0;
-        bool ok = true;
+        bool ok = d < 2 * bn;  // a narrower tile leaves the last warps without a row
         for (int tile = tile_first; tile < tiles && ok; tile += tile_stride) {
-            const int n = min((tile / a.m_tiles) * kBN + row, a.N - 1);  // ragged tile: clamp
-            const uint8_t* src = a.packed + size_t(n) * (a.K / 2) + half * 16;
-            const uint16_t* srow = a.scale + size_t(n) * groups;
-            const uint8_t* zrow = a.zero + size_t(n) * groups;
+            const int n = min((tile / a.m_tiles) * bn + row, a.N - 1);  // ragged tile: clamp
+            // this group's first stage of the tile, its use number, ring slot and the parity of
+            // the slot's previous use
+            const int skip = int((group_id + kDequantGroups - it % kDequantGroups) % kDequantGroups);
+            int ks = ks_begin + skip;
+            uint32_t mine = it + uint32_t(skip);
+            int s = int(mine % uint32_t(stages));
+            uint32_t parity = ((mine / uint32_t(stages)) + 1) & 1;
             // With few rows the weights stream from HBM exactly once, and what bounds the
             // kernel is how many bytes each multiprocessor keeps in flight: the loads of this
             // thread's next kPrefetch stages are always outstanding (16 bytes each, 512 or
             // 256 threads a stage), so the HBM latency hides behind several stages of work.
-            auto fetch = [&](int ks, uint4& q, uint32_t& sc, uint32_t& bias) {
-                q = __ldg(reinterpret_cast<const uint4*>(src + size_t(ks) * (kBK / 2)));
-                const int grp = (ks * kBK) / a.G;
-                // raw values only: any arithmetic here would make the thread wait for these two
+            const uint8_t* fsrc = a.packed + size_t(n) * (a.K / 2) + half * 16 + size_t(ks) * (kBK / 2);
+            const uint16_t* fscale = a.scale + size_t(n) * groups + ks / spg;
+            const uint8_t* fzero = a.zero + size_t(n) * groups + ks / spg;
+            int fks = ks, fwithin = ks % spg;
+            auto fetch = [&](uint4& q, uint32_t& sc, uint32_t& bias) {
+                // raw values only: any arithmetic here would make the thread wait for these
                 // loads at once instead of when the stage is dequantized, kPrefetch stages later
-                sc = __ldg(srow + grp);
-                bias = __ldg(zrow + grp);
+                q = __ldg(reinterpret_cast<const uint4*>(fsrc));
+                sc = __ldg(fscale);
+                bias = __ldg(fzero);
+                fsrc += kDequantGroups * (kBK / 2);
+                fks += kDequantGroups;
+                fwithin += kDequantGroups;
+#pragma unroll
+                for (int r = 0; r < kDequantGroups; ++r)
+                    if (fwithin >= spg) fwithin -= spg, ++fscale, ++fzero;
             };
-            const int first = ks_begin + int((group_id + kDequantGroups - it % kDequantGroups) % kDequantGroups);
             uint4 q_ring[kPrefetch];
             uint32_t sc_ring[kPrefetch], bias_ring[kPrefetch];
 #pragma unroll
             for (int u = 0; u < kPrefetch; ++u) {
                 q_ring[u] = make_uint4(0, 0, 0, 0);
                 sc_ring[u] = bias_ring[u] = 0;
-                if (first + u * kDequantGroups < ks_end) fetch(first + u * kDequantGroups, q_ring[u], sc_ring[u], bias_ring[u]);
+                if (fks < ks_end) fetch(q_ring[u], sc_ring[u], bias_ring[u]);
             }
-            for (int ks0 = first; ks0 < ks_end && ok; ks0 += kPrefetch * kDequantGroups) {
+            while (ks < ks_end && ok) {
 #pragma unroll
                 for (int u = 0; u < kPrefetch; ++u) {
-                    const int ks = ks0 + u * kDequantGroups;
-                    if (ks >= ks_end || !ok) break;
-                    const uint32_t mine = it + uint32_t(ks - ks_begin);  // this stage's use number
-                    const int s = mine % kStages;
+                    if (ks >= ks_end) break;
                     const uint4 q = q_ring[u];
-                    const uint32_t sc = sc_ring[u] * 0x00010001u;               // (scale, scale)
+                    const uint32_t sc = sc_ring[u] * 0x00010001u;                    // (scale, scale)
                     const uint32_t bias = 0x43004300u + bias_ring[u] * 0x00010001u;  // (128 + zero) twice
-                    if (ks + kPrefetch * kDequantGroups < ks_end)
-                        fetch(ks + kPrefetch * kDequantGroups, q_ring[u], sc_ring[u], bias_ring[u]);
-                    if (mine >= uint32_t(kStages))
-                        ok = mbar_wait(&pipe->empty[s], ((mine / kStages) - 1) & 1, &g_gemm_error, 5);
+                    if (fks < ks_end) fetch(q_ring[u], sc_ring[u], bias_ring[u]);
+                    if (mine >= uint32_t(stages)) ok = mbar_wait(&pipe->empty[s], parity, &g_gemm_error, 5);
                     if (!ok) break;
-                    uint8_t* tile_b = smem + s * kStageBytes + 2 * kATile + row * 128;
+                    const uint32_t stage = uint32_t(s) * stage_bytes;
                     const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
@@ -248,17 +264,19 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
                         f[3] = lop3_and_or(w[i] >> 12, 0x000F000Fu, 0x43004300u);
 #pragma unroll
                         for (int e = 0; e < 4; ++e) f[e] = sub_mul<__nv_bfloat16>(f[e], bias, sc);
-                        uint4 out;  // natural order (k0,k1) (k2,k3) (k4,k5) (k6,k7)
-                        out.x = __byte_perm(f[0], f[1], 0x5410);
-                        out.y = __byte_perm(f[2], f[3], 0x5410);
-                        out.z = __byte_perm(f[0], f[1], 0x7632);
-                        out.w = __byte_perm(f[2], f[3], 0x7632);
-                        const int chunk = half * 4 + i;  // 16-byte chunk of the 128-byte row
-                        *reinterpret_cast<uint4*>(tile_b + ((chunk ^ (row & 7)) * 16)) = out;
+                        // natural order (k0,k1) (k2,k3) (k4,k5) (k6,k7)
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"((stage + piece0) ^ uint32_t(i * 16)),
+                                     "r"(__byte_perm(f[0], f[1], 0x5410)), "r"(__byte_perm(f[2], f[3], 0x5410)),
+                                     "r"(__byte_perm(f[0], f[1], 0x7632)), "r"(__byte_perm(f[2], f[3], 0x7632))
+                                     : "memory");
                     }
                     fence_proxy_async();  // generic-proxy stores -> visible to the tensor core
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&pipe->full_b[s]);
+                    ks += kDequantGroups;
+                    mine += kDequantGroups;
+                    s += kDequantGroups;
+                    if (s >= stages) s -= stages, parity ^= 1;
                 }
             }
             it += uint32_t(ks_end - ks_begin);
@@ -269,25 +287,27 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
         bool ok = true;
         for (int tile = tile_first; tile < tiles && ok; tile += tile_stride, ++t) {
             const int m0 = (tile % a.m_tiles) * (2 * kBM);
-            const int n0 = (tile / a.m_tiles) * kBN;
+            const int n0 = (tile / a.m_tiles) * bn;
             const uint32_t buf = t % kAccBufs;
             ok = mbar_wait(&pipe->acc_full[buf], (t / kAccBufs) & 1, &g_gemm_error, 6);
             if (!ok || splits > 1) break;  // a K slice: the cluster adds the slices below
             tc_fence_after();
 #pragma unroll 1
             for (int acc = 0; acc < 2; ++acc) {
-                const int m = m0 + acc * kBM + warp * 32 + lane;
                 if (m0 + acc * kBM >= a.M) break;  // second accumulator unused (warp-uniform)
+                const int m = m0 + acc * kBM + warp * 32 + lane;
 #pragma unroll 1
-                for (int c0 = 0; c0 < kBN; c0 += 32) {
+                for (int c0 = 0; c0 < bn; c0 += 32) {
                     uint32_t v[32];
                     const uint32_t taddr = tmem + (uint32_t(warp * 32) << 16) + buf * (2 * kBN) + acc * kBN + c0;
-                    tmem_load_32(v, taddr);
+                    tmem_load_32(v, taddr);  // (past bn: columns of the allocation nothing wrote; not stored)
                     if (m < a.M) {
                         uint16_t* dst = a.y + size_t(m) * a.N + n0 + c0;
-                        if (n0 + c0 + 32 <= a.N && (a.N % 8) == 0) {
+                        const int live = min(min(bn - c0, a.N - n0 - c0), 32);  // columns of this chunk that exist
+                        if (a.vec) {  // bn, n0 and N are multiples of 8: 16-byte pieces are whole or absent
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
+                                if (8 * j >= live) break;
                                 uint4 o;
                                 o.x = Half16<__nv_bfloat16>::pack(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
                                 o.y = Half16<__nv_bfloat16>::pack(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
@@ -298,8 +318,7 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
                         } else {
 #pragma unroll
                             for (int j = 0; j < 32; ++j)
-                                if (n0 + c0 + j < a.N)
-                                    dst[j] = Half16<__nv_bfloat16>::from_float(__uint_as_float(v[j]));
+                                if (j < live) dst[j] = Half16<__nv_bfloat16>::from_float(__uint_as_float(v[j]));
                         }
                     }
                 }
@@ -395,12 +414,25 @@ extern "C" int32_t b200q_int4_gemm(const void* x, const uint8_t* packed, const v
                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     B200Q_REQUIRE(made == CUDA_SUCCESS, "int4_gemm: cuTensorMapEncodeTiled failed (%d)", int(made));
 
-    // Tile width: 256 unless the narrower tile's better fit to the SM count outweighs its
-    // L2-bound main loop (a 256-wide tile takes about 1.25x the time of a 128-wide one).
+    // Tile width.  Every block takes ceil(tiles / blocks) tiles one after another, so the time is
+    // that count times a tile's time; a tile's time grows with its width w as w + kTileFixed
+    // (measured at 2048 rows: 256 columns take 1.26 x the time of 176), so the width that fills
+    // the last round of tiles best wins: 176 for 2048 x 6144 (280 tiles, two rounds, against
+    // 192 tiles of 256 that need two rounds as well), 224 for N = 28672, 240 for N = 4096.
+    // The 128-wide kernel (double-buffered accumulators) takes about 0.8 of a 256-wide tile's
+    // time per tile: the general kernel at the same width is never slower by this estimate, so
+    // the 128-wide kernel is left with the K-split case below.
     const int sms = sm_count();
     const int m_tiles = int((rows + 2 * kBM - 1) / (2 * kBM));
-    const int64_t tiles128 = int64_t(m_tiles) * ((out + 127) / 128), tiles256 = int64_t(m_tiles) * ((out + 255) / 256);
-    const double cost128 = double((tiles128 + sms - 1) / sms), cost256 = 1.25 * double((tiles256 + sms - 1) / sms);
+    const int64_t tiles128 = int64_t(m_tiles) * ((out + 127) / 128);
+    const double cost128 = 0.8 * (256 + kTileFixed) * double((tiles128 + sms - 1) / sms);
+    int bn = 256;
+    double cost256 = 0.0;
+    for (int width = 256; width >= 64; width -= 16) {
+        const int64_t count = int64_t(m_tiles) * ((out + width - 1) / width);
+        const double cost = double(width + kTileFixed) * double((count + sms - 1) / sms);
+        if (width == 256 || cost < cost256) bn = width, cost256 = cost;
+    }
     // Up to 128 rows over a narrow weight: split K over a cluster while the tiles alone would
     // leave more than half of the multiprocessors idle (every slice keeps >= 2 steps of 64).
     int k_splits = 1;
@@ -411,9 +443,19 @@ extern "C" int32_t b200q_int4_gemm(const void* x, const uint8_t* packed, const v
         while (k_splits > 1 && (k_splits - 1) * ((ksteps + k_splits - 1) / k_splits) >= ksteps) k_splits /= 2;
     }
     const bool wide = k_splits == 1 && cost256 <= cost128;
-    GemmArgs a{packed, static_cast<const uint16_t*>(scale), zero, static_cast<uint16_t*>(y),
-               int(rows), int(in), int(out), int(group), m_tiles, int(wide ? (out + 255) / 256 : (out + 127) / 128),
-               k_splits};
+    GemmArgs a;
+    a.packed = packed;
+    a.scale = static_cast<const uint16_t*>(scale);
+    a.zero = zero;
+    a.y = static_cast<uint16_t*>(y);
+    a.M = int(rows), a.K = int(in), a.N = int(out), a.G = int(group);
+    a.bn = wide ? bn : 128;
+    a.m_tiles = m_tiles;
+    a.n_tiles = int((out + a.bn - 1) / a.bn);
+    a.k_splits = k_splits;
+    a.vec = out % 8 == 0 && aligned(y, 16);
+    a.stage_bytes = 2 * kATile + a.bn * (kBK * 2);
+    a.stages = kRing / a.stage_bytes < kMaxStages ? kRing / a.stage_bytes : kMaxStages;
     const int tiles = a.m_tiles * a.n_tiles;
     const int grid = k_splits > 1 ? tiles * k_splits : (tiles < sms ? tiles : sms);
     cudaStream_t s = static_cast<cudaStream_t>(stream);

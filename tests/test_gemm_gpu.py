@@ -47,6 +47,12 @@ def close(got, want, what):
     # up to 128 rows over a narrow weight: K split over a cluster of 2, 4 or 8 blocks
     (64, 4096, 4096, 128), (64, 14336, 512, 128), (100, 1024, 200, 64), (33, 640, 130, 64),
     (128, 1152, 256, 128), (17, 448, 130, 64),
+    # weights wide enough for the tile width to be chosen by how the tiles fill the multiprocessors
+    # (80, 96, 112, 144, 160, 192, 208, 240, 256 rows of W a tile on 148 of them), ragged last
+    # tiles, one output width that is no multiple of 8 (element stores), one single-row-block case
+    (130, 128, 9480, 64), (130, 192, 11848, 64), (300, 128, 7112, 128), (300, 192, 9480, 64),
+    (300, 128, 10664, 64), (520, 128, 8632, 128), (520, 192, 9416, 64), (520, 128, 10984, 64),
+    (520, 128, 11768, 128), (300, 128, 10666, 64), (40, 256, 11848, 64),
 ])
 def test_gemm_matches_oracle(rows, depth, out, group):
     packed, scale, zero, gen = random_int4(out, depth, group, rows + depth + out)
