@@ -68,6 +68,7 @@ struct GemmArgs {
     int bn;                 // rows of W per tile: BN, or for BN = 256 any multiple of 16 up to it
     int vec;                // y can be written 16 bytes at a time (N % 8 == 0, y aligned)
     int stages, stage_bytes;  // of the ring: 2 x 16 KB of X and bn x 128 bytes of W each
+    int group_shift;          // log2 of the stages a quantization group lasts
     int k_splits;           // > 1: a cluster of k_splits blocks shares one tile, each a slice of K
 };
 
@@ -112,6 +113,7 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
     const int tile_first = blockIdx.x / splits, tile_stride = gridDim.x / splits;
     const int k_per_split = (a.K / kBK + splits - 1) / splits;
     const int ks_begin = split * k_per_split, ks_end = min(a.K / kBK, ks_begin + k_per_split);
+    const int span = ks_end - ks_begin;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) {
@@ -170,7 +172,7 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
                 if (t >= uint32_t(kAccBufs))
                     ok = mbar_wait(&pipe->acc_empty[buf], ((t / kAccBufs) - 1) & 1, &g_gemm_error, 2);
                 tc_fence_after();
-                for (int ks = ks_begin; ks < ks_end && ok; ++ks) {
+                for (int j = 0; j < span && ok; ++j) {
                     ok = mbar_wait(&pipe->full_a[s], lap & 1, &g_gemm_error, 3) &&
                          mbar_wait(&pipe->full_b[s], lap & 1, &g_gemm_error, 4);
                     if (!ok) break;
@@ -179,7 +181,7 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
 #pragma unroll
                     for (int kk = 0; kk < kBK / 16; ++kk) {
                         const uint64_t b_desc = smem_desc(base + 2 * kATile + kk * 32);
-                        const uint32_t acc = (ks > ks_begin || kk > 0) ? 1u : 0u;
+                        const uint32_t acc = (j > 0 || kk > 0) ? 1u : 0u;
                         umma_bf16(tmem + buf * (2 * kBN), smem_desc(base + kk * 32), b_desc, idesc, acc);
                         if (two) umma_bf16(tmem + buf * (2 * kBN) + kBN, smem_desc(base + kATile + kk * 32), b_desc, idesc, acc);
                     }
@@ -193,69 +195,73 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
         // ---- dequantizers --------------------------------------------------------
         const int d = (threadIdx.x - kFirstDequantWarp * 32) % (kDequantWarps * 32);  // (row, half) of a stage
         const int group_id = (threadIdx.x - kFirstDequantWarp * 32) / (kDequantWarps * 32);
-        const int row = d >> 1, half = d & 1;                // W row of the tile, 32-input half
+        // Two threads a row of W: each takes kWords words of 8 weights of every stage.
+        constexpr int kWords = 4, kDepth = kPrefetch;
+        const int row = d / 2, part = d % 2;
         const int groups = a.K / a.G;
-        const int spg = a.G / kBK;                           // stages a quantization group lasts
-        // Everything that repeats per stage is kept as a running value (stage, parity, group,
+        // Everything that repeats per stage is kept as a running value (stage, lap, group,
         // addresses): the loop body is the dequantization and little else.
-        // This thread's four 16-byte pieces of a stage's W tile, swizzled: piece i is chunk
-        // (4 half + i) ^ (row & 7) of the 128-byte row, which is the first one with i * 16
+        // This thread's 16-byte pieces of a stage's W tile, swizzled: piece i is chunk
+        // (kWords part + i) ^ (row & 7) of the 128-byte row, which is the first one with i * 16
         // XORed into its address (stages and rows start on multiples of 128).
-        const uint32_t piece0 = smem_u32(smem) + 2 * kATile + row * 128 + (((half * 4) ^ (row & 7)) * 16);
+        const uint32_t piece0 = smem_u32(smem) + 2 * kATile + row * 128 + (((part * kWords) ^ (row & 7)) * 16);
         uint32_t it = 0;
         bool ok = d < 2 * bn;  // a narrower tile leaves the last warps without a row
         for (int tile = tile_first; tile < tiles && ok; tile += tile_stride) {
             const int n = min((tile / a.m_tiles) * bn + row, a.N - 1);  // ragged tile: clamp
-            // this group's first stage of the tile, its use number, ring slot and the parity of
-            // the slot's previous use
+            // this group's first stage of the tile, its ring slot and the times the ring has been
+            // gone round before it
             const int skip = int((group_id + kDequantGroups - it % kDequantGroups) % kDequantGroups);
-            int ks = ks_begin + skip;
-            uint32_t mine = it + uint32_t(skip);
+            int todo = (span - skip + kDequantGroups - 1) / kDequantGroups;  // stages of this tile still to fill
+            int ahead = todo;                                                // ... still to fetch
+            int ks = ks_begin + skip;                                        // first of them
+            const uint32_t mine = it + uint32_t(skip);
             int s = int(mine % uint32_t(stages));
-            uint32_t parity = ((mine / uint32_t(stages)) + 1) & 1;
+            uint32_t lap = mine / uint32_t(stages);
             // With few rows the weights stream from HBM exactly once, and what bounds the
             // kernel is how many bytes each multiprocessor keeps in flight: the loads of this
-            // thread's next kPrefetch stages are always outstanding (16 bytes each, 512 or
-            // 256 threads a stage), so the HBM latency hides behind several stages of work.
-            const uint8_t* fsrc = a.packed + size_t(n) * (a.K / 2) + half * 16 + size_t(ks) * (kBK / 2);
-            const uint16_t* fscale = a.scale + size_t(n) * groups + ks / spg;
-            const uint8_t* fzero = a.zero + size_t(n) * groups + ks / spg;
-            int fks = ks, fwithin = ks % spg;
-            auto fetch = [&](uint4& q, uint32_t& sc, uint32_t& bias) {
+            // thread's next kDepth stages are always outstanding, so the HBM latency hides
+            // behind several stages of work.
+            // (32-bit offsets from the arguments' pointers: the packed weight is under 4 GB; a
+            // quantization group lasts a power-of-two number of stages)
+            const uint32_t row_at = uint32_t(n) * uint32_t(a.K / 2) + part * (4 * kWords);
+            const uint32_t group_at = uint32_t(n) * uint32_t(groups);
+            auto fetch = [&](uint32_t (&q)[kWords], uint32_t& sc, uint32_t& bias) {
                 // raw values only: any arithmetic here would make the thread wait for these
-                // loads at once instead of when the stage is dequantized, kPrefetch stages later
-                q = __ldg(reinterpret_cast<const uint4*>(fsrc));
-                sc = __ldg(fscale);
-                bias = __ldg(fzero);
-                fsrc += kDequantGroups * (kBK / 2);
-                fks += kDequantGroups;
-                fwithin += kDequantGroups;
-#pragma unroll
-                for (int r = 0; r < kDequantGroups; ++r)
-                    if (fwithin >= spg) fwithin -= spg, ++fscale, ++fzero;
+                // loads at once instead of when the stage is dequantized, kDepth stages later
+                const uint8_t* src = a.packed + (row_at + uint32_t(ks) * (kBK / 2));
+                const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
+                q[0] = v.x, q[1] = v.y, q[2] = v.z, q[3] = v.w;
+                const uint32_t group = group_at + (uint32_t(ks) >> a.group_shift);
+                sc = __ldg(a.scale + group);
+                bias = __ldg(a.zero + group);
+                --ahead;
+                ks += kDequantGroups;
             };
-            uint4 q_ring[kPrefetch];
-            uint32_t sc_ring[kPrefetch], bias_ring[kPrefetch];
+            uint32_t q_ring[kDepth][kWords];
+            uint32_t sc_ring[kDepth], bias_ring[kDepth];
 #pragma unroll
-            for (int u = 0; u < kPrefetch; ++u) {
-                q_ring[u] = make_uint4(0, 0, 0, 0);
+            for (int u = 0; u < kDepth; ++u) {
+#pragma unroll
+                for (int i = 0; i < kWords; ++i) q_ring[u][i] = 0;
                 sc_ring[u] = bias_ring[u] = 0;
-                if (fks < ks_end) fetch(q_ring[u], sc_ring[u], bias_ring[u]);
+                if (ahead > 0) fetch(q_ring[u], sc_ring[u], bias_ring[u]);
             }
-            while (ks < ks_end && ok) {
+            while (todo > 0 && ok) {
 #pragma unroll
-                for (int u = 0; u < kPrefetch; ++u) {
-                    if (ks >= ks_end) break;
-                    const uint4 q = q_ring[u];
+                for (int u = 0; u < kDepth; ++u) {
+                    if (todo <= 0) break;
+                    uint32_t w[kWords];
+#pragma unroll
+                    for (int i = 0; i < kWords; ++i) w[i] = q_ring[u][i];
                     const uint32_t sc = sc_ring[u] * 0x00010001u;                    // (scale, scale)
                     const uint32_t bias = 0x43004300u + bias_ring[u] * 0x00010001u;  // (128 + zero) twice
-                    if (fks < ks_end) fetch(q_ring[u], sc_ring[u], bias_ring[u]);
-                    if (mine >= uint32_t(stages)) ok = mbar_wait(&pipe->empty[s], parity, &g_gemm_error, 5);
+                    if (ahead > 0) fetch(q_ring[u], sc_ring[u], bias_ring[u]);
+                    if (lap > 0) ok = mbar_wait(&pipe->empty[s], (lap - 1) & 1, &g_gemm_error, 5);
                     if (!ok) break;
                     const uint32_t stage = uint32_t(s) * stage_bytes;
-                    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
+                    for (int i = 0; i < kWords; ++i) {
                         // (k0,k4) (k1,k5) (k2,k6) (k3,k7): magic + q, then exactly (q - zero) * scale
                         uint32_t f[4];
                         f[0] = lop3_and_or(w[i], 0x000F000Fu, 0x43004300u);
@@ -273,13 +279,12 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
                     fence_proxy_async();  // generic-proxy stores -> visible to the tensor core
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&pipe->full_b[s]);
-                    ks += kDequantGroups;
-                    mine += kDequantGroups;
+                    --todo;
                     s += kDequantGroups;
-                    if (s >= stages) s -= stages, parity ^= 1;
+                    if (s >= stages) s -= stages, ++lap;
                 }
             }
-            it += uint32_t(ks_end - ks_begin);
+            it += uint32_t(span);
         }
     } else {
         // ---- epilogue (warps 0-3; warp w owns tensor-memory lanes 32w .. 32w+31) ---
@@ -384,6 +389,8 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
 bool int4_gemm_supports(int64_t rows, int64_t in, int64_t out, int64_t group, int32_t dtype,
                         const void* x, const void* y) {
     return dtype == B200Q_BF16 && rows > 0 && in % kBK == 0 && group % kBK == 0 && in >= kBK &&
+           ((group / kBK) & (group / kBK - 1)) == 0 &&
+           out * (in / 2) < (int64_t(1) << 32) &&
            (in * 2) % 16 == 0 && aligned(x, 16) && aligned(y, 2) && out > 0;
 }
 
@@ -397,7 +404,7 @@ extern "C" int32_t b200q_int4_gemm(const void* x, const uint8_t* packed, const v
     const int32_t ok = check_int4_args("int4_gemm", x, packed, scale, zero, y, rows, in, out, group, dtype);
     if (ok != B200Q_OK || rows == 0) return ok;
     B200Q_REQUIRE(int4_gemm_supports(rows, in, out, group, dtype, x, y),
-                  "int4_gemm: needs bf16, inputs and group multiples of %d (got in=%lld group=%lld)", kBK,
+                  "int4_gemm: needs bf16, inputs a multiple of %d, a group of that many times a power of two, a packed weight under 4 GB (got in=%lld group=%lld)", kBK,
                   (long long)in, (long long)group);
     B200Q_REQUIRE(rows < (int64_t(1) << 30), "int4_gemm: too many rows");
     EncodeTiled encode = encode_tiled();
@@ -454,6 +461,8 @@ extern "C" int32_t b200q_int4_gemm(const void* x, const uint8_t* packed, const v
     a.n_tiles = int((out + a.bn - 1) / a.bn);
     a.k_splits = k_splits;
     a.vec = out % 8 == 0 && aligned(y, 16);
+    a.group_shift = 0;
+    while ((int64_t(kBK) << a.group_shift) < group) ++a.group_shift;
     a.stage_bytes = 2 * kATile + a.bn * (kBK * 2);
     a.stages = kRing / a.stage_bytes < kMaxStages ? kRing / a.stage_bytes : kMaxStages;
     const int tiles = a.m_tiles * a.n_tiles;
