@@ -98,9 +98,6 @@ template <int BN>
 struct Shape8 {
     static constexpr int kStages = BN == 128 ? 6 : 4;
     static constexpr int kStageBytes = kBM * kBK + BN * kBK;
-    // int32 accumulator, signed 8-bit A and B, both K-major, M = 128, N = BN
-    static constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (uint32_t(BN >> 3) << 17) |
-                                       (uint32_t(kBM >> 4) << 24);
     static constexpr uint32_t kTmemColumns = 2 * BN;  // two accumulators of BN columns
     static constexpr size_t kSmem = size_t(kStages) * kStageBytes + 1024 + 256;
 };
@@ -111,7 +108,9 @@ struct MmArgs {
     uint16_t* y;           // [M, N]
     int M, K, N;
     int m_tiles, n_tiles;
+    int bn;                // rows of W per tile: BN, or for BN = 256 any multiple of 16 up to it
     int f16;               // output type: 0 bf16, 1 f16
+    int vec;               // y can be written 16 bytes at a time (N % 8 == 0, y aligned)
 };
 
 struct Pipe8 {
@@ -134,6 +133,11 @@ int8_mm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int tiles = a.m_tiles * a.n_tiles;
     const int ksteps = a.K / kBK;
+    // The tile's width is a run-time value (the W map's box has that many rows): the layout in
+    // shared and tensor memory stays that of BN.
+    const int bn = BN == 128 ? 128 : a.bn;
+    // int32 accumulator, signed 8-bit A and B, both K-major, M = 128, N = bn
+    const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | (uint32_t(bn >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -166,13 +170,13 @@ int8_mm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
             bool ok = true;
             // tiles ordered with the row block fastest: blocks that share a weight tile run together
             for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile % a.m_tiles) * kBM, n0 = (tile / a.m_tiles) * BN;
+                const int m0 = (tile % a.m_tiles) * kBM, n0 = (tile / a.m_tiles) * bn;
                 for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
                     const int s = it % kStages;
                     if (it >= uint32_t(kStages)) ok = mbar_wait(&pipe->empty[s], ((it / kStages) - 1) & 1, error, 11);
                     if (!ok) break;
                     uint8_t* dst = smem + s * kStageBytes;
-                    mbar_expect_tx(&pipe->full[s], kStageBytes);
+                    mbar_expect_tx(&pipe->full[s], (kBM + bn) * kBK);
                     tma_load_2d(dst, &x_map, ks * kBK, m0, &pipe->full[s]);
                     tma_load_2d(dst + kBM * kBK, &w_map, ks * kBK, n0, &pipe->full[s]);
                 }
@@ -195,7 +199,7 @@ int8_mm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
 #pragma unroll
                     for (int kk = 0; kk < kBK / 32; ++kk)  // 32 bytes of K per instruction
                         umma_i8(tmem + buf * BN, smem_desc(base + kk * 32), smem_desc(base + kBM * kBK + kk * 32),
-                                S::kIdesc, (ks > 0 || kk > 0) ? 1u : 0u);
+                                idesc, (ks > 0 || kk > 0) ? 1u : 0u);
                     umma_commit(&pipe->empty[s]);  // frees the stage when these MMAs retire
                 }
                 if (ok) umma_commit(&pipe->acc_full[buf]);
@@ -206,7 +210,7 @@ int8_mm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
         uint32_t t = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++t) {
-            const int m0 = (tile % a.m_tiles) * kBM, n0 = (tile / a.m_tiles) * BN;
+            const int m0 = (tile % a.m_tiles) * kBM, n0 = (tile / a.m_tiles) * bn;
             const uint32_t buf = t & 1;
             ok = mbar_wait(&pipe->acc_full[buf], (t / 2) & 1, error, 14);
             if (!ok) break;
@@ -214,22 +218,24 @@ int8_mm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
             const int m = m0 + warp * 32 + lane;
             const float xs = m < a.M ? __ldg(a.x_scale + m) : 0.0f;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = 0; c0 < bn; c0 += 32) {
                 uint32_t v[32];
-                tmem_load_32(v, tmem + (uint32_t(warp * 32) << 16) + buf * BN + c0);
+                tmem_load_32(v, tmem + (uint32_t(warp * 32) << 16) + buf * BN + c0);  // (past bn: not stored)
                 if (m < a.M) {
                     uint16_t* dst = a.y + size_t(m) * a.N + n0 + c0;
+                    const int live = min(min(bn - c0, a.N - n0 - c0), 32);  // columns of this chunk that exist
                     uint16_t out[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const int n = n0 + c0 + j;
-                        const float ws = n < a.N ? __ldg(a.w_scale + n) : 0.0f;
+                        const float ws = j < live ? __ldg(a.w_scale + n) : 0.0f;
                         const float r = __fmul_rn(__fmul_rn(float(int32_t(v[j])), xs), ws);
                         out[j] = a.f16 ? Half16<__half>::from_float(r) : Half16<__nv_bfloat16>::from_float(r);
                     }
-                    if (n0 + c0 + 32 <= a.N && (a.N % 8) == 0) {
+                    if (a.vec) {  // bn, n0 and N are multiples of 8: 16-byte pieces are whole or absent
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
+                            if (8 * j >= live) break;
                             uint4 o;
                             o.x = uint32_t(out[8 * j + 0]) | (uint32_t(out[8 * j + 1]) << 16);
                             o.y = uint32_t(out[8 * j + 2]) | (uint32_t(out[8 * j + 3]) << 16);
@@ -240,7 +246,7 @@ int8_mm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
                     } else {
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
-                            if (n0 + c0 + j < a.N) dst[j] = out[j];
+                            if (j < live) dst[j] = out[j];
                     }
                 }
             }
@@ -311,14 +317,25 @@ extern "C" int32_t b200q_int8_mm(const int8_t* xq, const int8_t* w, const float*
     const int m_tiles = int((rows + kBM - 1) / kBM);
     // 256-wide tiles halve the traffic of x when there are enough tiles to go round
     const bool wide = int64_t(m_tiles) * ((out + 255) / 256) >= sms;
-    const int bn = wide ? 256 : 128;
+    // ... and of the wide tiles (144 to 256 rows of W in steps of 16) the width that fills the
+    // blocks' last round best: every block takes ceil(tiles / blocks) tiles in turn, and a tile's
+    // time goes about as its width plus 64 columns.
+    int bn = wide ? 256 : 128;
+    if (wide) {
+        double best = 0.0;
+        for (int width = 256; width >= 144; width -= 16) {
+            const int64_t count = int64_t(m_tiles) * ((out + width - 1) / width);
+            const double cost = double(width + 64) * double((count + sms - 1) / sms);
+            if (width == 256 || cost < best) bn = width, best = cost;
+        }
+    }
     CUtensorMap x_map, w_map;
     int32_t status = make_map(&x_map, xq, rows, in, kBM, "int8_mm");
     if (status != B200Q_OK) return status;
     status = make_map(&w_map, w, out, in, bn, "int8_mm");
     if (status != B200Q_OK) return status;
     MmArgs a{x_scale, w_scale, static_cast<uint16_t*>(y), int(rows), int(in), int(out), m_tiles,
-             int((out + bn - 1) / bn), dtype == B200Q_F16 ? 1 : 0};
+             int((out + bn - 1) / bn), bn, dtype == B200Q_F16 ? 1 : 0, (out % 8 == 0 && aligned(y, 16)) ? 1 : 0};
     const int tiles = a.m_tiles * a.n_tiles;
     const int grid = tiles < sms ? tiles : sms;
     cudaStream_t s = static_cast<cudaStream_t>(stream);

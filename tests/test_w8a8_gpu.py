@@ -36,6 +36,9 @@ def test_int8_rows_is_exact(rows, depth, dtype):
 @pytest.mark.parametrize(("rows", "depth", "out"), [
     (33, 128, 16), (64, 512, 72), (128, 4096, 4096), (129, 1024, 272), (300, 4096, 1000), (2048, 4096, 6144),
     (2048, 14336, 4096), (1, 256, 48),
+    # wide tiles whose width is chosen by how the tiles fill the multiprocessors (224, 240 rows of W
+    # on 148 of them), ragged last tiles, an output width that is no multiple of 8
+    (2048, 256, 14336), (1200, 128, 5001), (1500, 128, 9000),
 ])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_int8_mm_is_exact(rows, depth, out, dtype):
