@@ -448,11 +448,6 @@ bool run_tma(const GemvArgs& a, cudaStream_t stream, int32_t* status, const Norm
               norm ? norm->eps : 0.0f, word};
     size_t smem = 0;
     const int sms = sm_count();
-    static const int force_kb = getenv("B200Q_KB") ? atoi(getenv("B200Q_KB")) : 0;
-    if (force_kb == 4 && tma_plan<1, 16, 4>(p, a.G, &smem)) {
-        *status = launch_tma<T, 1, 16, 4, false>(p, a.packed, smem, sms, stream);
-        return true;
-    }
     if (tma_plan<1, 16, 8>(p, a.G, &smem)) {
         *status = launch_tma<T, 1, 16, 8, false>(p, a.packed, smem, sms, stream);
         return true;
