@@ -119,8 +119,10 @@ int32_t b200q_int4_linear_ex(const void* x, const uint8_t* packed, const void* s
                              int64_t out, int64_t group, int32_t dtype, int32_t flags,
                              void* stream);
 
-/* The prefill kernel alone: TMA + tcgen05/TMEM dequant-GEMM (bf16; `in` and `group`
- * multiples of 64; any rows and out). */
+/* The prefill kernel alone: TMA + tcgen05/TMEM dequant-GEMM (bf16; `in` a multiple of 64,
+ * `group` 64 times a power of two, a packed weight under 4 GB; any rows and out;
+ * B200Q_ERROR otherwise: b200q_int4_linear sends such shapes to the decode kernels in
+ * passes). */
 int32_t b200q_int4_gemm(const void* x, const uint8_t* packed, const void* scale,
                         const uint8_t* zero, void* y, int64_t rows, int64_t in,
                         int64_t out, int64_t group, int32_t dtype, void* stream);
