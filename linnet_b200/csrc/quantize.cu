@@ -156,8 +156,9 @@ __device__ __forceinline__ int int8_level(float v, float scale, float inv_scale)
 
 // Adding 1.5 * 2^23 to |t| < 2^22 rounds t to an integer, half to even, in the sum's low bits.
 constexpr float kRound = 12582912.0f;
-// A quotient this close to a half-integer (or larger) is rounded by the true division.
-constexpr float kTie = 0.4999f;
+// A quotient within 2e-4 of a half-integer is rounded by the true division; the test is on the
+// squared distance from the nearest integer (0.4998^2).
+constexpr float kTie2 = 0.2498f;
 
 __device__ __forceinline__ void store_scale(void* dst, int dtype, int64_t i, float s) {
     if (dst == nullptr) return;
@@ -178,25 +179,36 @@ __device__ __forceinline__ void store_scale(void* dst, int dtype, int64_t i, flo
 // INSIDE: the group's range straddles zero (low < 0 < high), so its zero point is not clipped
 // and every t lies in [-0.5, 15.5]: away from ties (the only case kept here) it rounds into
 // 0..15 without the clip.
+// The arithmetic runs two weights an instruction (fma / add .f32x2 of sm_100, each half an IEEE
+// operation of its own): weight j is paired with weight j + 4, so that the packing sums of the
+// low and the high four levels are the two halves of one chain.
 template <bool INSIDE = false>
 __device__ __forceinline__ uint32_t pack8_int4(const Chunk& c, float step, float zero, float inv) {
-    float q[8];
-    float worst = 0.0f;  // largest distance of a t from its integer
+    const float2 inv2 = make_float2(inv, inv), zero2 = make_float2(zero, zero);
+    const float2 up = make_float2(kRound, kRound), down = make_float2(-kRound, -kRound);
+    const float2 minus = make_float2(-1.0f, -1.0f), sixteen = make_float2(16.0f, 16.0f);
+    float2 q[4];
+    float worst = 0.0f;  // largest squared distance of a t from its integer
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const float t = __fmaf_rn(c.v[j], inv, zero);
-        const float r = __fsub_rn(__fadd_rn(t, kRound), kRound);
-        worst = fmaxf(worst, fabsf(__fsub_rn(t, r)));
-        q[j] = INSIDE ? r : fminf(fmaxf(r, 0.0f), 15.0f);
+    for (int j = 0; j < 4; ++j) {
+        const float2 t = __ffma2_rn(make_float2(c.v[j], c.v[j + 4]), inv2, zero2);
+        const float2 r = __fadd2_rn(__fadd2_rn(t, up), down);
+        const float2 d = __ffma2_rn(r, minus, t);  // t - r (the product is exact)
+        const float2 dd = __fmul2_rn(d, d);
+        worst = max3(worst, dd.x, dd.y);
+        q[j] = INSIDE ? r : make_float2(fminf(fmaxf(r.x, 0.0f), 15.0f), fminf(fmaxf(r.y, 0.0f), 15.0f));
     }
-    if (!(worst < kTie)) {
+    if (!(worst < kTie2)) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) q[j] = float(int4_level(c.v[j], step, inv, zero));
+        for (int j = 0; j < 4; ++j)
+            q[j] = make_float2(float(int4_level(c.v[j], step, inv, zero)), float(int4_level(c.v[j + 4], step, inv, zero)));
     }
     // four levels are one exact f32 sum; 2^23 + sum has them in its low 16 bits
-    const float lo = __fmaf_rn(q[3], 4096.0f, __fmaf_rn(q[2], 256.0f, __fmaf_rn(q[1], 16.0f, q[0])));
-    const float hi = __fmaf_rn(q[7], 4096.0f, __fmaf_rn(q[6], 256.0f, __fmaf_rn(q[5], 16.0f, q[4])));
-    return __byte_perm(__float_as_uint(__fadd_rn(lo, 8388608.0f)), __float_as_uint(__fadd_rn(hi, 8388608.0f)), 0x5410);
+    float2 sum = __ffma2_rn(q[3], sixteen, q[2]);
+    sum = __ffma2_rn(sum, sixteen, q[1]);
+    sum = __ffma2_rn(sum, sixteen, q[0]);
+    sum = __fadd2_rn(sum, make_float2(8388608.0f, 8388608.0f));
+    return __byte_perm(__float_as_uint(sum.x), __float_as_uint(sum.y), 0x5410);
 }
 __device__ __forceinline__ uint32_t pack8_int4(const Chunk& c, float step, float zero) {
     return pack8_int4<false>(c, step, zero, __frcp_rn(step));
@@ -205,16 +217,27 @@ __device__ __forceinline__ uint32_t pack8_int4(const Chunk& c, float step, float
 // Eight levels clip(round(v / scale), -127, 127) as bytes: kRound + level has the level's
 // two's complement in its low byte.
 __device__ __forceinline__ uint2 pack8_int8(const Chunk& c, float scale, float inv) {
+    // Two weights an instruction, as in pack8_int4.  No clip here: the scale is the group's own
+    // largest magnitude / 127, so |t| <= 127.3 for every finite group; a quotient that is out
+    // of range all the same (a subnormal scale, a non-finite weight) shows in the largest
+    // squared level and takes the division with the near ties.
+    const float2 inv2 = make_float2(inv, inv), up = make_float2(kRound, kRound), down = make_float2(-kRound, -kRound);
+    const float2 minus = make_float2(-1.0f, -1.0f);
     uint32_t b[8];
-    float worst = 0.0f;
+    float worst = 0.0f, largest = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const float t = __fmul_rn(c.v[j], inv);
-        const float s = __fadd_rn(t, kRound);
-        worst = fmaxf(worst, fabsf(__fsub_rn(t, __fsub_rn(s, kRound))));
-        b[j] = __float_as_uint(fminf(fmaxf(s, kRound - 127.0f), kRound + 127.0f));
+    for (int j = 0; j < 8; j += 2) {
+        const float2 t = __fmul2_rn(make_float2(c.v[j], c.v[j + 1]), inv2);
+        const float2 s = __fadd2_rn(t, up);
+        const float2 r = __fadd2_rn(s, down);      // the level
+        const float2 d = __ffma2_rn(r, minus, t);  // t - r
+        const float2 dd = __fmul2_rn(d, d), rr = __fmul2_rn(r, r);
+        worst = max3(worst, dd.x, dd.y);
+        largest = max3(largest, rr.x, rr.y);
+        b[j] = __float_as_uint(s.x);
+        b[j + 1] = __float_as_uint(s.y);
     }
-    if (!(worst < kTie)) {
+    if (!(worst < kTie2) || !(largest <= 127.0f * 127.0f)) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) b[j] = uint32_t(int8_level(c.v[j], scale, inv));
     }
