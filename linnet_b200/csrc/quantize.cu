@@ -156,9 +156,9 @@ __device__ __forceinline__ int int8_level(float v, float scale, float inv_scale)
 
 // Adding 1.5 * 2^23 to |t| < 2^22 rounds t to an integer, half to even, in the sum's low bits.
 constexpr float kRound = 12582912.0f;
-// A quotient within 2e-4 of a half-integer is rounded by the true division; the test is on the
-// squared distance from the nearest integer (0.4998^2).
-constexpr float kTie2 = 0.2498f;
+// A quotient within 1e-4 of a half-integer is rounded by the true division; the test is on the
+// squared distance from the nearest integer (0.4999^2 = 0.24990001).
+constexpr float kTie2 = 0.2499f;
 
 __device__ __forceinline__ void store_scale(void* dst, int dtype, int64_t i, float s) {
     if (dst == nullptr) return;
@@ -187,21 +187,23 @@ __device__ __forceinline__ uint32_t pack8_int4(const Chunk& c, float step, float
     const float2 inv2 = make_float2(inv, inv), zero2 = make_float2(zero, zero);
     const float2 up = make_float2(kRound, kRound), down = make_float2(-kRound, -kRound);
     const float2 minus = make_float2(-1.0f, -1.0f), sixteen = make_float2(16.0f, 16.0f);
-    float2 q[4];
+    float2 q[4], dd[4];
     float worst = 0.0f;  // largest squared distance of a t from its integer
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const float2 t = __ffma2_rn(make_float2(c.v[j], c.v[j + 4]), inv2, zero2);
         const float2 r = __fadd2_rn(__fadd2_rn(t, up), down);
         const float2 d = __ffma2_rn(r, minus, t);  // t - r (the product is exact)
-        const float2 dd = __fmul2_rn(d, d);
-        worst = max3(worst, dd.x, dd.y);
+        dd[j] = __fmul2_rn(d, d);
+        worst = max3(worst, dd[j].x, dd[j].y);
         q[j] = INSIDE ? r : make_float2(fminf(fmaxf(r.x, 0.0f), 15.0f), fminf(fmaxf(r.y, 0.0f), 15.0f));
     }
-    if (!(worst < kTie2)) {
+    if (!(worst < kTie2)) {  // rare (one chunk in 600), but a warp takes it when any lane does: only the near ties
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-            q[j] = make_float2(float(int4_level(c.v[j], step, inv, zero)), float(int4_level(c.v[j + 4], step, inv, zero)));
+        for (int j = 0; j < 4; ++j) {
+            if (!(dd[j].x < kTie2)) q[j].x = float(int4_level(c.v[j], step, inv, zero));
+            if (!(dd[j].y < kTie2)) q[j].y = float(int4_level(c.v[j + 4], step, inv, zero));
+        }
     }
     // four levels are one exact f32 sum; 2^23 + sum has them in its low 16 bits
     float2 sum = __ffma2_rn(q[3], sixteen, q[2]);
