@@ -77,6 +77,19 @@ def dram_traffic(key: str) -> dict | None:
     return json.loads(path.read_text()).get(key)
 
 
+def quantize_traffic(weights: int) -> dict:
+    """DRAM bytes of one step of the quantize workload (both formats of `weights` weights): the
+    per-weight traffic of the two kernels' ncu captures on 8192 x 8192 (it grows in proportion
+    to the weights: every weight is read once and its level written once) times the weights."""
+    found = [dram_traffic("quantize_int4_g128_8192x8192"), dram_traffic("quantize_int8_channel_8192x8192")]
+    if not all(found):
+        return {"traffic": None}
+    per_weight = sum(f["bytes_per_launch"] for f in found) / (8192 * 8192)
+    return {"traffic": per_weight * weights,
+            "traffic_source": "per-weight DRAM bytes of the two kernels' ncu captures on 8192 x 8192 "
+                              "(profiles/dram_traffic.json), times this step's weights"}
+
+
 class Clocks:
     """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
 
@@ -617,7 +630,7 @@ def run_quantize(args, rank: int, world: int, device: torch.device, barrier, red
                      "peak_kind": peak_kind, "algorithmic_bytes_per_step_per_gpu": b4 + b8,
                      "int4_g128": {"GB/s": b4 / (ms4 / 1e3) / 1e9, "frac": b4 / (ms4 / 1e3) / 1e9 / hbm},
                      "int8_channel": {"GB/s": b8 / (ms8 / 1e3) / 1e9, "frac": b8 / (ms8 / 1e3) / 1e9 / hbm},
-                     "traffic": None},
+                     **quantize_traffic(sum(out * depth for _n, out, depth in shard))},
         "parity": checked,
         "e2e": {"value": (b4 + b8) / (e2e_ms / 1e3) / 1e9 * world, "unit": "GB/s", "ms_per_step": e2e_ms,
                 "trials_ms_per_step": e2e_trials, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
