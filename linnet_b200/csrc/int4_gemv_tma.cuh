@@ -28,7 +28,11 @@
 //   * the block stages ALL activations once: [rows x K] 16-bit values, permuted to the
 //     (k, k+4) pairing of the A fragments and stored as B fragments of mma.m16n8k16, with the
 //     per-group sums X beside them;
-//   * the warps of a tile add up their partial sums in the stages they have just emptied,
+//   * a warp hands a stage back to the producer the moment it has read the item in it, so the
+//     ring only holds what is being read or is on its way (a block whose share of W is larger
+//     than the ring would otherwise wait, round after round, for the stages of the round
+//     before);
+//   * the warps of a tile add up their partial sums in a small shared-memory area of their own,
 //     behind a named barrier of their own: no thread-block cluster, no atomics, no global scratch.
 //
 // Every wait on a shared-memory barrier is bounded: after about a second the waiting warp
@@ -68,7 +72,7 @@ struct TmaArgs {
 // Offsets (bytes) of the shared-memory regions: ring of stages, barriers, per-warp scales
 // and zero points, B fragments of the activations, their group sums.
 struct TmaLayout {
-    uint32_t bars, sz, xs, xsum, total;
+    uint32_t bars, sz, xs, xsum, red, total;
     uint32_t xrow;    // bytes of one activation row in xs (padded so that rows g, g+1 fall on different banks)
     int xpairs;       // pairs of rows in xsum
 };
@@ -82,7 +86,8 @@ __host__ __device__ inline TmaLayout tma_layout(int M, int K, int stages) {
     l.xrow = uint32_t(groups) * 256 + (M > 1 ? 64 : 0);
     l.xpairs = (M + 1) / 2;
     l.xsum = l.xs + uint32_t(M) * l.xrow;
-    l.total = l.xsum + uint32_t(l.xpairs) * groups * 8 + 128;  // + the sums of squares of the fused norm
+    l.red = (l.xsum + uint32_t(l.xpairs) * groups * 8 + 128 + 15u) & ~15u;  // (+ 128: the sums of squares of the fused norm)
+    l.total = l.red + 2u * WARPS * (16 * MB * 8 * 4);  // the warps' partial sums of a tile, two rounds' worth
     return l;
 }
 
@@ -352,7 +357,7 @@ int4_gemv_tma_kernel(const __grid_constant__ CUtensorMap wmap, const TmaArgs a) 
     const int s_step = active % S;  // a full round's items between two of this warp's
     const int s_last = (min(a.tpc, t1 - t0 - (rounds - 1) * a.tpc) * a.wpt) % S;  // the last round's
     const uint32_t ready = ready0 + warp * 8;
-    for (int tile = t0 + ts; tile < t1; tile += a.tpc) {
+    for (int tile = t0 + ts, round = 0; tile < t1; tile += a.tpc, ++round) {
         float acc[MB][2][4];
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb)
@@ -467,43 +472,39 @@ int4_gemv_tma_kernel(const __grid_constant__ CUtensorMap wmap, const TmaArgs a) 
                     }
                 }
             }
-            if (o + 1 < a.opc) {  // hand the stage back; the tile's last one carries the partial sums first
-                __syncwarp();
-                if (lane == 0) bar_arrive(empty0 + s_mine * 8);
-            }
+            __syncwarp();  // every lane has read the item: the stage goes back to the producer at once
+            if (lane == 0) bar_arrive(empty0 + s_mine * 8);
         }
         const bool last_tile = tile + a.tpc >= t1;
         if (last_tile && a.overlap && !a.early) pdl_launch_dependents();
 
-        // The tile's partial sums meet in the stages its warps have just read: each warp writes
-        // 16 x MP floats into its own, the tile's first warp adds them up, stores y and hands
-        // all the stages back to the producer.
-        __syncwarp();
+        // The tile's partial sums meet in a small area of their own (16 x MP floats a warp, two
+        // rounds' worth: a warp can only write a buffer again after the tile's first warp has
+        // passed the next round's barrier, that is after it has read this round's): the tile's
+        // first warp adds them up and stores y.
+        const uint32_t red = smem0 + lay.red + uint32_t(round & 1) * (WARPS * 16 * MP * 4);
+        {
+            const uint32_t dst0 = red + uint32_t(warp) * (16 * MP * 4);
 #pragma unroll
-        for (int mb = 0; mb < MB; ++mb) {
-            const uint32_t dst = stage_addr + (g * MP + mb * 8 + 2 * t) * 4;
-            sts32f(dst, acc[mb][0][0] + (EXACT ? acc[mb][1][0] : 0.0f));
-            sts32f(dst + 4, acc[mb][0][1] + (EXACT ? acc[mb][1][1] : 0.0f));
-            sts32f(dst + 8 * MP * 4, acc[mb][0][2] + (EXACT ? acc[mb][1][2] : 0.0f));
-            sts32f(dst + 8 * MP * 4 + 4, acc[mb][0][3] + (EXACT ? acc[mb][1][3] : 0.0f));
+            for (int mb = 0; mb < MB; ++mb) {
+                const uint32_t dst = dst0 + (g * MP + mb * 8 + 2 * t) * 4;
+                sts32f(dst, acc[mb][0][0] + (EXACT ? acc[mb][1][0] : 0.0f));
+                sts32f(dst + 4, acc[mb][0][1] + (EXACT ? acc[mb][1][1] : 0.0f));
+                sts32f(dst + 8 * MP * 4, acc[mb][0][2] + (EXACT ? acc[mb][1][2] : 0.0f));
+                sts32f(dst + 8 * MP * 4 + 4, acc[mb][0][3] + (EXACT ? acc[mb][1][3] : 0.0f));
+            }
         }
-        umma::fence_proxy_async();  // these writes come before the TMA unit's next ones to the stage
         if (a.wpt > 1) named_barrier(1 + ts, a.wpt * 32);
         else __syncwarp();
         if (part == 0) {
             for (int e = lane; e < 16 * M; e += 32) {
                 const int row = e % 16, m = e / 16;
                 float sum = 0.0f;
-                for (int w = 0; w < a.wpt; ++w) {  // the siblings' stages follow this warp's round the ring
-                    const int sw = s_mine + w < S ? s_mine + w : s_mine + w - S;
-                    sum += lds32f(smem0 + uint32_t(sw) * kItem + (row * MP + m) * 4);
-                }
+                for (int w = 0; w < a.wpt; ++w)  // the tile's warps are this one and the wpt - 1 after it
+                    sum += lds32f(red + uint32_t(warp + w) * (16 * MP * 4) + (row * MP + m) * 4);
                 const int nrow = tile * 16 + row;
                 if (nrow < N) y[size_t(m) * N + nrow] = H::from_float(sum);
             }
-            __syncwarp();
-            if (lane < a.wpt) bar_arrive(empty0 + (s_mine + lane < S ? s_mine + lane :
-                                                          s_mine + lane - S) * 8);
         }
     }
 }
@@ -525,8 +526,7 @@ inline bool tma_plan(TmaArgs& a, int G, size_t* smem) {
     const TmaLayout fixed = tma_layout<MB, WARPS, KB>(a.M, a.K, 0);
     const long budget = 226L * 1024 - long(fixed.total);
     long stages = (budget - 2 * WARPS * 8 - 16) / (KB * 1024 + 8);
-    // The stages of a tile's last items go back to the producer together, so the ring must hold
-    // more than one tile's worth of warps; and a shallow ring is another kernel's shape.
+    // A shallow ring is another kernel's shape (and every warp of a tile wants a stage of its own).
     if (stages < 4 || stages <= a.wpt) return false;
     if (stages > 96) stages = 96;
     a.stages = int(stages);
