@@ -79,7 +79,9 @@ def _one_shot(rank: int, world: int, dev: torch.device) -> dict:
     big = torch.randn(ONE_SHOT_BYTES // 2 + 8, device=dev, generator=gen).to(torch.bfloat16)
     wide = torch.randn(1000, device=dev, generator=gen)
     report["covers"] = (one.covers(big), one.covers(wide), one.covers(wide[:8].to(torch.bfloat16)))
-    close = bool(torch.allclose(one(big).float(), expected(big).float(), rtol=2e-2, atol=2e-2))
+    # (the library adds in bf16 in an order of its own: every one of its world - 1 roundings can be
+    # off by 2^-9 of a running sum, the kernel's one rounding by 2^-9 of the total)
+    close = bool(torch.allclose(one(big).float(), expected(big).float(), rtol=2e-2, atol=1e-2 * world))
     close &= bool(torch.allclose(one(wide), sum_f32(wide, world), rtol=1e-5, atol=1e-5))
     report["library_close"] = close
     # 500 calls in a row, each on the last one's result scaled back: nothing drifts or sticks
@@ -200,4 +202,6 @@ def test_peer_reduce_matches_nccl_route(tmp_path, world):
         assert report["one_shot_error"] == 0
         assert report["one_shot_exact"], "OneShot differs from the rank-ordered f32 sum"
         assert report["covers"] == (False, False, True)
-        assert report["library_close"] and report["many_calls_equal"] and report["graph_equal"]
+        assert report["library_close"], "a message past the one-shot limit differs from the library's sum"
+        assert report["many_calls_equal"], "500 calls in a row drifted"
+        assert report["graph_equal"], "a captured chain of calls differs from the eager chain"
