@@ -12,7 +12,8 @@ Prints ONE JSON line.  Workloads:
   HBM), recorded once into a CUDA graph and replayed.  Every number is the median of 5 trials
   of `--steps` replays each.  `value` calls the plain entry point; `chained_early` is the same
   chain with B200Q_EARLY_DEPENDENTS, the flag a caller sets when the next kernel is another
-  product (which this chain is).  With N ranks every rank runs this on its own GPU and weight
+  product (which this chain is); `isolated` times one launch alone, from the host and, under
+  `in_stream_order`, on the device (the chain with B200Q_NO_OVERLAP).  With N ranks every rank runs this on its own GPU and weight
   sets (`value` is the sum).  The line also carries `decode`: tokens/s of a Llama-3.1-8B-shaped
   int4 decoder step, tensor-parallel over the N ranks (linnet_b200/decoder.py), at batch 1, 8
   and 64, and `other_configs` (int8 GEMV, prefill GEMM against dequantize + library GEMM,
@@ -251,7 +252,7 @@ def run_gemv(args, rank: int, world: int, device: torch.device, barrier, reduce_
     results: dict[str, dict] = {}
     clocks = None
 
-    def chain(x: torch.Tensor, early: bool) -> torch.cuda.CUDAGraph:
+    def chain(x: torch.Tensor, early: bool, overlap: bool = True) -> torch.cuda.CUDAGraph:
         for p, s, z in sets[:2]:
             kernels.int4_linear(x, p, s, z, early=early)  # warm: module load, attribute set-up
         torch.cuda.synchronize()
@@ -259,7 +260,7 @@ def run_gemv(args, rank: int, world: int, device: torch.device, barrier, reduce_
         with torch.cuda.graph(graph, stream=stream):
             for i in range(LAUNCHES_PER_STEP):
                 p, s, z = sets[i % WEIGHT_SETS]
-                kernels.int4_linear(x, p, s, z, early=early)
+                kernels.int4_linear(x, p, s, z, early=early, overlap=overlap)
         return graph
 
     with torch.cuda.stream(stream):
@@ -278,6 +279,11 @@ def run_gemv(args, rank: int, world: int, device: torch.device, barrier, reduce_
             del graph
         graph = chain(xs[args.rows], True)
         results["early"] = time_replays(graph, args.steps, 3, barrier, reduce_max)
+        del graph
+        # the same chain in plain stream order: every launch starts when the one before it has
+        # finished (no early start, no weight fetch under the predecessor)
+        graph = chain(xs[args.rows], False, overlap=False)
+        results["serial"] = time_replays(graph, args.steps, 3, barrier, reduce_max)
         del graph
 
         # One launch at a time with the stream drained in between: no overlap with a neighbour,
@@ -361,8 +367,11 @@ def run_gemv(args, rank: int, world: int, device: torch.device, barrier, reduce_
         "per_rows": {str(m): rate(results[str(m)]["ms_per_step"], m) for m in (1, 4, 16)},
         "chained_early": rate(results["early"]["ms_per_step"], args.rows),
         "isolated": {"us_per_launch": isolated_us, "GB/s": gemv_bytes(args.rows) / isolated_us / 1e3,
-                     "how": "one launch between two events, the stream drained before each; median over "
-                            f"{3 * WEIGHT_SETS} launches visiting the weight sets in turn"},
+                     "how": "one launch between two events, the stream drained before each (the host's launch "
+                            f"latency is inside); median over {3 * WEIGHT_SETS} launches visiting the weight sets in turn",
+                     "in_stream_order": {**rate(results["serial"]["ms_per_step"], args.rows),
+                                         "how": "the 64-launch graph with B200Q_NO_OVERLAP: every launch starts when "
+                                                "the one before it has finished, on the device's own clock"}},
         "e2e": {"value": gemv_bytes(rows) * LAUNCHES_PER_STEP / (e2e_ms / 1e3) / 1e9 * world,
                 "unit": "GB/s", "ms_per_step": e2e_ms, "trials_ms_per_step": e2e_trials,
                 "h2d_bytes_per_step": rows * K_IN * 2, "d2h_bytes_per_step": rows * N_OUT * 2,

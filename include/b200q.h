@@ -108,8 +108,13 @@ int32_t b200q_int4_gemv(const void* x, const uint8_t* packed, const void* scale,
  *     reference's generated source do), formed while the kernel stages its activations: the
  *     SwiGLU of a decoder layer without a launch of its own.  Taken for one or two rows,
  *     groups of 128 and the default numerics; B200Q_UNAVAILABLE otherwise (the caller then
- *     forms the input itself).  No counterpart in the reference. */
-enum { B200Q_EXACT_WEIGHTS = 1, B200Q_EARLY_DEPENDENTS = 2, B200Q_SWIGLU_INPUT = 4 };
+ *     forms the input itself).  No counterpart in the reference.
+ *   B200Q_NO_OVERLAP   the one- and two-row kernel is launched in plain stream order: it starts
+ *     when everything before it in the stream has finished, instead of starting early and
+ *     fetching weights while the kernel before it still runs (programmatic dependent launch,
+ *     the default).  For callers that want plain stream order, and for timing the kernel
+ *     without a neighbour's overlap.  No counterpart in the reference. */
+enum { B200Q_EXACT_WEIGHTS = 1, B200Q_EARLY_DEPENDENTS = 2, B200Q_SWIGLU_INPUT = 4, B200Q_NO_OVERLAP = 8 };
 int32_t b200q_int4_gemv_ex(const void* x, const uint8_t* packed, const void* scale,
                            const uint8_t* zero, void* y, int64_t rows, int64_t in,
                            int64_t out, int64_t group, int32_t dtype, int32_t flags,

@@ -12,7 +12,7 @@ LIBRARY = Path(__file__).resolve().parent / "libb200q.so"
 
 OK, ERROR, UNAVAILABLE = 0, 1, 2
 F32, BF16, F16 = 0, 1, 2
-EXACT_WEIGHTS, EARLY_DEPENDENTS, SWIGLU_INPUT = 1, 2, 4
+EXACT_WEIGHTS, EARLY_DEPENDENTS, SWIGLU_INPUT, NO_OVERLAP = 1, 2, 4, 8
 
 # name -> argument types, exactly the prototypes of include/b200q.h
 PROTOTYPES: dict[str, list] = {

@@ -43,7 +43,7 @@ struct GemvArgs {
     int kblocks;            // K / 128
     int kb_per_cta;         // k-blocks each block of a cluster handles
     int ksplit;             // blocks per cluster (along grid.y)
-    int flags;              // B200Q_EXACT_WEIGHTS | B200Q_EARLY_DEPENDENTS
+    int flags;              // B200Q_EXACT_WEIGHTS | B200Q_EARLY_DEPENDENTS | B200Q_SWIGLU_INPUT | B200Q_NO_OVERLAP
 };
 
 // How the zero point and scale reach the product.
@@ -442,8 +442,8 @@ bool run_tma(const GemvArgs& a, cudaStream_t stream, int32_t* status, const Norm
     if (a.G != 128 || a.M > 2 || size_t(a.N) * size_t(a.K / 2) >= (size_t(1) << 40)) return false;
     int* word = gemm_error_word();
     if (word == nullptr) return false;
-    TmaArgs p{a.x, a.scale, a.zero, a.y, a.M, a.K, a.N, (a.N + 15) / 16, 1, 1, 1, 0, 1,
-              (a.flags & B200Q_EARLY_DEPENDENTS) ? 1 : 0, (a.flags & B200Q_SWIGLU_INPUT) ? 1 : 0,
+    TmaArgs p{a.x, a.scale, a.zero, a.y, a.M, a.K, a.N, (a.N + 15) / 16, 1, 1, 1, 0,
+              (a.flags & B200Q_NO_OVERLAP) ? 0 : 1, (a.flags & B200Q_EARLY_DEPENDENTS) ? 1 : 0, (a.flags & B200Q_SWIGLU_INPUT) ? 1 : 0,
               norm ? norm->delta : nullptr, norm ? norm->weight : nullptr, norm ? norm->x_out : nullptr,
               norm ? norm->eps : 0.0f, word};
     size_t smem = 0;
@@ -537,7 +537,7 @@ extern "C" int32_t b200q_int4_gemv_ex(const void* x, const uint8_t* packed, cons
                                       void* stream) {
     const int32_t ok = check_int4_args("int4_gemv", x, packed, scale, zero, y, rows, in, out, group, dtype);
     if (ok != B200Q_OK || rows == 0) return ok;
-    B200Q_REQUIRE((flags & ~(B200Q_EXACT_WEIGHTS | B200Q_EARLY_DEPENDENTS | B200Q_SWIGLU_INPUT)) == 0,
+    B200Q_REQUIRE((flags & ~(B200Q_EXACT_WEIGHTS | B200Q_EARLY_DEPENDENTS | B200Q_SWIGLU_INPUT | B200Q_NO_OVERLAP)) == 0,
                   "int4_gemv: unknown flag bits %d", flags);
     GemvArgs a{x, packed, scale, zero, y, 0, int(in), int(out), int(group), int(in / 128), 0, 1, flags};
     cudaStream_t s = static_cast<cudaStream_t>(stream);

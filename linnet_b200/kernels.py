@@ -83,7 +83,7 @@ def int4_numerics() -> str:
 
 def _int4_linear(x: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor,
                  zero: torch.Tensor, out: torch.Tensor | None = None, early: bool = False,
-                 swiglu: bool = False) -> torch.Tensor:
+                 swiglu: bool = False, overlap: bool = True) -> torch.Tensor:
     rows, depth = x.shape
     if swiglu:
         depth //= 2
@@ -108,7 +108,8 @@ def _int4_linear(x: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor,
             raise ValueError(f"int4_linear: out must be a contiguous [{rows}, {width}] {x.dtype} tensor on {device}")
         y = out
     with _Device(device):
-        flags = (_lib.EXACT_WEIGHTS if _exact_weights else 0) | (_lib.EARLY_DEPENDENTS if early else 0)
+        flags = ((_lib.EXACT_WEIGHTS if _exact_weights else 0) | (_lib.EARLY_DEPENDENTS if early else 0)
+                 | (0 if overlap else _lib.NO_OVERLAP))
         lib = _lib.load()
         if swiglu:
             # the kernel that forms silu(gate) * up while it stages its input, where it takes the
@@ -145,7 +146,7 @@ def _(x, packed, scale, zero):
 
 def int4_linear(x: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor,
                 zero: torch.Tensor, out: torch.Tensor | None = None, early: bool = False,
-                swiglu: bool = False) -> torch.Tensor:
+                swiglu: bool = False, overlap: bool = True) -> torch.Tensor:
     """`F.linear(x, W)` for `x` [rows, In] (bf16 or f16) and the group-wise 4-bit weight
     of `std.quant::linear_int4_groups`: `packed` [Out, Groups, Group/2] u8 (even value
     low), `scale` and `zero` [Out, Groups].  Any row count: up to 16 rows stream the
@@ -155,10 +156,12 @@ def int4_linear(x: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor,
     kernel in the stream is another product of the same input, which may start prefetching its
     weights at once (`B200Q_EARLY_DEPENDENTS`).  `swiglu` (eager calls only): `x` is
     [rows, 2 In] and the product's input is `silu(x[:, :In]) * x[:, In:]`, formed inside the
-    product for one and two rows (`B200Q_SWIGLU_INPUT`) and by `glue.silu_mul` otherwise."""
-    if out is None and not early and not swiglu and torch.compiler.is_compiling():
+    product for one and two rows (`B200Q_SWIGLU_INPUT`) and by `glue.silu_mul` otherwise.
+    `overlap=False` (eager calls only): the one- and two-row kernel starts in plain stream order
+    instead of early (`B200Q_NO_OVERLAP`)."""
+    if out is None and not early and not swiglu and overlap and torch.compiler.is_compiling():
         return _int4_linear_op(x, packed, scale, zero)
-    return _int4_linear(x, packed, scale, zero, out, early, swiglu)
+    return _int4_linear(x, packed, scale, zero, out, early, swiglu, overlap)
 
 
 def int4_linear_norm(x: torch.Tensor, delta: torch.Tensor | None, norm_weight: torch.Tensor, eps: float,

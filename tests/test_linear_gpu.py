@@ -227,6 +227,18 @@ def test_int4_swiglu_input(rows, depth, out, dtype):
     close_int4(folded, act.cpu(), packed, scale, zero, f"swiglu rows={rows} depth={depth}")
 
 
+def test_int4_plain_stream_order_is_the_same_product():
+    """`overlap=False` (B200Q_NO_OVERLAP) only changes when the one-row kernel starts."""
+    from linnet_b200 import kernels
+
+    packed, scale, zero, gen = random_int4(1000, 4096, 128, torch.bfloat16, 21)
+    x = torch.randn(1, 4096, generator=gen).to(torch.bfloat16).cuda()
+    p, s, z = packed.cuda(), scale.cuda(), zero.cuda()
+    want = kernels.int4_linear(x, p, s, z)
+    for _ in range(3):
+        assert torch.equal(kernels.int4_linear(x, p, s, z, overlap=False), want)
+
+
 def test_int4_dequantize_is_exact():
     """`_int4_weight`: bit-for-bit the reference's arithmetic
     (python/linnet/tests/test_quant_groups.py:151-162)."""
