@@ -437,7 +437,7 @@ def stub_kernels() -> None:
     from linnet_b200 import int4, kernels, quantized
     from oracle import linear_oracle as lo
 
-    def int4_linear(x, packed, scale, zero, out=None, early=False, swiglu=False):
+    def int4_linear(x, packed, scale, zero, out=None, early=False, swiglu=False, overlap=True):
         if swiglu:
             half = x.shape[-1] // 2
             x = torch.nn.functional.silu(x[..., :half]) * x[..., half:]
